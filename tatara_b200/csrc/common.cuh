@@ -1,0 +1,117 @@
+// Shared declarations of the sm_100a NNUE training-step library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TB_MAX_BUCKETS 9  // kMaxSupportedNumBuckets of the reference (native_kernels.cu:9)
+#define TB_MAX_L1 32
+#define TB_MAX_L2 64
+#define TB_TILE_M 32      // positions per dense tile; a tile never mixes LayerStack buckets
+
+// One tile of positions for the bucket-grouped dense kernels: positions order[start .. start+count).
+// bucket == num_buckets marks positions whose bucket id is out of range (their per-bucket layers
+// output zero, dense_mm_bucket.rs:45-73).
+struct TileDesc {
+    int start;
+    int count;
+    int bucket;
+    int pad;
+};
+
+struct LossParams {
+    int kind;  // 0 sigmoid, 1 wrm
+    float scale;
+    float nnue2score, in_scaling, in_offset, target_offset, target_scaling;
+    float lambda;
+    float norm;  // per-position gradient normaliser
+};
+
+struct OptScalars {
+    float lr, step_size, decay, beta1, beta2, eps, min_w, max_w, alpha;
+    int denom;
+    int lerp;  // apply the Ranger look-ahead interpolation after the update
+};
+
+// One small parameter group for the batched optimizer kernel.
+struct SmallGroup {
+    float *w, *m, *v, *slow;
+    const float* grad;
+    int n;
+    float lr, decay, min_w, max_w;
+};
+#define TB_MAX_SMALL_GROUPS 12
+// passed to the kernel by value (kernel parameter space), so no per-step upload is needed
+struct SmallGroups {
+    SmallGroup g[TB_MAX_SMALL_GROUPS];
+    int n;
+};
+
+static __device__ __forceinline__ float crelu01(float x) { return x < 0.0f ? 0.0f : (x > 1.0f ? 1.0f : x); }
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- launchers (each returns the number of kernels it launched) --------------------------------
+
+// ft_kernels.cu
+// mode: 0 raw gather-sum, 1 LayerStack pairwise (+bias, CReLU, product, scale), 2 Simple CReLU, 3 Simple SCReLU
+int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
+                      const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
+                      int B, int F, int N, int A, float scale, int n_persp);
+int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
+                         int N, int n_persp, int* counts /*[2][N]*/, int* offsets /*[2][N+1]*/,
+                         int* cursor /*[2][N]*/, int* lists /*[2][B*A]*/);
+int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
+                       const int* lists, int B, int A, int N, int F, int n_persp, float* grad);
+int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F);
+int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F);
+
+// dense_kernels.cu
+// tiles has room for max_tiles tiles followed by the work units; n_tiles is {tile count, unit count}
+int launch_bucket_sort(cudaStream_t s, const int* bucket /*may be NULL*/, int B, int nb, int* order,
+                       TileDesc* tiles, int* n_tiles, int* seg_start /*[nb+2]*/, int max_tiles);
+int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
+                      const int* n_tiles, int max_tiles, const float* wb /*[nb][l1][K] or NULL*/,
+                      const float* bb, const float* ws /*[K][l1]*/, const float* bs, float* y /*[B][l1]*/,
+                      int l1, int nb);
+int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
+                           const float* wdl, const float* l2_w, const float* l2_b, const float* l3_w,
+                           const float* l3_b, LossParams lp, int B, int l1, int l2, int nb, float* net_output,
+                           float* dy, float* dl1_total, float* l2_input, float* dl2_out, float* l2_acted,
+                           double* loss_partials, double* loss_acc, int backward);
+int launch_tail_simple(cudaStream_t s, const float* l1_pre, const float* score, const float* wdl,
+                       const float* l2_w, const float* l2_b, const float* l3_w, const float* l3_b, LossParams lp,
+                       int act, int B, int l1, int l2, float* net_output, float* dy, float* dl1_pre,
+                       float* l1_acted, float* dl2_pre, float* l2_acted, double* loss_partials,
+                       double* loss_acc, int backward);
+// per-bucket reductions of the small layers: out[g][cell] = sum over the positions of bucket g
+int launch_small_wgrad_layerstack(cudaStream_t s, const int* order, const int* seg_start, int B, int l1, int l2,
+                                  int nb, const float* l2_input, const float* dl2_out, const float* l2_acted,
+                                  const float* dy, const float* dl1_total, float* partials, float* l2_w_grad,
+                                  float* l2_b_grad, float* l3_w_grad, float* l3_b_grad, float* l1_b_grad,
+                                  float* l1s_b_grad);
+int launch_small_wgrad_simple(cudaStream_t s, const int* order, const int* seg_start, int B, int l1, int l2,
+                              const float* l1_acted, const float* dl2_pre, const float* l2_acted, const float* dy,
+                              const float* dl1_pre, float* partials, float* l2_w_grad, float* l2_b_grad,
+                              float* l3_w_grad, float* l3_b_grad, float* l1_b_grad);
+// L1 weight gradient: LayerStack writes gw_bucket [nb][l1][K] and gw_shared [K][l1]; Simple only gw_shared.
+int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, const int* order,
+                    const TileDesc* tiles, const int* n_tiles, int max_tiles, int l1, int nb, float* partials,
+                    float* gw_bucket, float* gw_shared);
+// L1 input gradient fused with the FT activation gradient; writes dft of both perspectives and the
+// FT bias gradient.
+int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int* order, const TileDesc* tiles,
+                           const int* n_tiles, int max_tiles, const float* wb, const float* ws,
+                           const float* pre_stm, const float* pre_nstm, const float* ft_bias, float scale,
+                           int B, int F, int l1, int nb, float* dft_stm, float* dft_nstm, float* bias_partials,
+                           float* ft_b_grad, int n_ctas);
+
+// opt_kernels.cu
+int launch_radam(cudaStream_t s, float* w, float* m, float* v, const float* g, float* slow, int64_t n,
+                 OptScalars sc);
+int launch_radam_small(cudaStream_t s, const SmallGroups& groups, int max_n, OptScalars sc);
+// factorised FT table: per virtual row v, updates the real rows kb*pi+v, reduces their gradients into the
+// virtual row, updates it and writes the folded forward table.
+int launch_radam_factorized(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb,
+                            int N, int pi, int F, OptScalars sc);

@@ -1,0 +1,847 @@
+// Hidden-layer kernels: bucket grouping of the batch, the L1 contraction (per-bucket + shared, or the
+// Simple architecture's single matrix), the fused tail (L1 activation .. L2 .. L3 .. loss and its
+// backward to the L1 output), the small-layer weight gradients, the L1 weight gradient and the fused
+// L1 input gradient + FT activation gradient.
+//
+// Positions are never physically permuted.  `order` lists the positions grouped by LayerStack bucket
+// (stable), `tiles` cuts it into runs of at most TB_TILE_M positions of one bucket; kernels gather
+// rows through `order` and write results back at the position's own row.
+#include "common.cuh"
+
+#define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
+#define L1_SQR_SCALE (127.0f / 128.0f)
+#define UNIT_TILES 16  // tiles per work unit of the L1 weight-gradient kernel
+
+// ------------------------------------------------------------------------------------------------
+// bucket grouping: stable counting sort of the positions by bucket id, one block.
+// Replaces count_buckets / exclusive_scan_aligned / scatter_bucket_perm / permute_rows_f32
+// (native_kernels.cu:1858-1973); out-of-range bucket ids form a last group of their own.
+// units[]: runs of at most UNIT_TILES tiles of one bucket, stored behind the tiles as TileDesc
+// {first tile, tile count, bucket}.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_bucket_sort(const int* __restrict__ bucket, int B, int nb,
+                                                       int* __restrict__ order, TileDesc* __restrict__ tiles,
+                                                       int* __restrict__ n_tiles, int* __restrict__ seg_start,
+                                                       TileDesc* __restrict__ units, int* __restrict__ n_units) {
+    __shared__ int s_warp[32];
+    __shared__ int s_cnt[TB_MAX_BUCKETS + 1];
+    __shared__ int s_base[TB_MAX_BUCKETS + 2];
+    __shared__ int s_tile_base[TB_MAX_BUCKETS + 2];
+    __shared__ int s_unit_base[TB_MAX_BUCKETS + 2];
+    const int K = nb + 1;
+    const int per = (B + blockDim.x - 1) / blockDim.x;
+    const int beg = min((int)threadIdx.x * per, B), end = min(beg + per, B);
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int cnt[TB_MAX_BUCKETS + 1];
+    int excl[TB_MAX_BUCKETS + 1];
+#pragma unroll
+    for (int k = 0; k <= TB_MAX_BUCKETS; ++k) cnt[k] = 0;
+    for (int i = beg; i < end; ++i) {
+        int k = bucket ? bucket[i] : 0;
+        if ((unsigned)k >= (unsigned)nb) k = nb;
+#pragma unroll
+        for (int q = 0; q <= TB_MAX_BUCKETS; ++q) cnt[q] += (q == k);
+    }
+#pragma unroll
+    for (int k = 0; k <= TB_MAX_BUCKETS; ++k) {
+        if (k < K) {
+            int incl = cnt[k];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                int t = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += t;
+            }
+            if (lane == 31) s_warp[w] = incl;
+            __syncthreads();
+            if (w == 0) {
+                int t = s_warp[lane];
+                int ti = t;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    int u = __shfl_up_sync(0xffffffffu, ti, d);
+                    if (lane >= d) ti += u;
+                }
+                s_warp[lane] = ti - t;
+                if (lane == 31) s_cnt[k] = ti;
+            }
+            __syncthreads();
+            excl[k] = s_warp[w] + incl - cnt[k];
+            __syncthreads();
+        }
+    }
+    if (threadIdx.x == 0) {
+        int run = 0, trun = 0, urun = 0;
+        for (int k = 0; k < K; ++k) {
+            s_base[k] = run;
+            s_tile_base[k] = trun;
+            s_unit_base[k] = urun;
+            seg_start[k] = run;
+            run += s_cnt[k];
+            const int nt = (s_cnt[k] + TB_TILE_M - 1) / TB_TILE_M;
+            trun += nt;
+            urun += (nt + UNIT_TILES - 1) / UNIT_TILES;
+        }
+        s_base[K] = run;
+        s_tile_base[K] = trun;
+        s_unit_base[K] = urun;
+        seg_start[K] = run;
+        *n_tiles = trun;
+        *n_units = urun;
+    }
+    __syncthreads();
+    int run[TB_MAX_BUCKETS + 1];
+#pragma unroll
+    for (int k = 0; k <= TB_MAX_BUCKETS; ++k) run[k] = (k < K) ? s_base[k] + excl[k] : 0;
+    for (int i = beg; i < end; ++i) {
+        int k = bucket ? bucket[i] : 0;
+        if ((unsigned)k >= (unsigned)nb) k = nb;
+        int dst = 0;
+#pragma unroll
+        for (int q = 0; q <= TB_MAX_BUCKETS; ++q)
+            if (q == k) dst = run[q]++;
+        order[dst] = i;
+    }
+    for (int k = 0; k < K; ++k) {
+        const int c = s_cnt[k];
+        const int nt = (c + TB_TILE_M - 1) / TB_TILE_M;
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+            TileDesc d;
+            d.start = s_base[k] + t * TB_TILE_M;
+            d.count = min(TB_TILE_M, c - t * TB_TILE_M);
+            d.bucket = k;
+            d.pad = 0;
+            tiles[s_tile_base[k] + t] = d;
+        }
+        const int nu = (nt + UNIT_TILES - 1) / UNIT_TILES;
+        for (int u = threadIdx.x; u < nu; u += blockDim.x) {
+            TileDesc d;
+            d.start = s_tile_base[k] + u * UNIT_TILES;
+            d.count = min(UNIT_TILES, nt - u * UNIT_TILES);
+            d.bucket = k;
+            d.pad = 0;
+            units[s_unit_base[k] + u] = d;
+        }
+    }
+}
+
+int launch_bucket_sort(cudaStream_t s, const int* bucket, int B, int nb, int* order, TileDesc* tiles,
+                       int* n_tiles, int* seg_start, int max_tiles) {
+    // units live behind the tiles: tiles[max_tiles .. ), n_units behind n_tiles
+    k_bucket_sort<<<1, 1024, 0, s>>>(bucket, B, nb, order, tiles, n_tiles, seg_start, tiles + max_tiles, n_tiles + 1);
+    return 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// L1 forward.  y[pos, o] = (bb[g, o] + sum_k x[pos, k] wb[g, o, k]) + (bs[o] + sum_k x[pos, k] ws[k, o])
+// (dense_mm_bucket.rs:45-73 + dense_mm.rs:37-54 + elementwise add, trainer_layerstack.rs:2373-2530).
+// Without buckets (Simple) only the second term exists.  One block per tile, K in chunks of 64.
+// ------------------------------------------------------------------------------------------------
+template <bool HAS_BUCKET>
+__global__ void __launch_bounds__(256) k_l1_forward(const float* __restrict__ x, int K, const int* __restrict__ order,
+                                                     const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
+                                                     const float* __restrict__ wb, const float* __restrict__ bb,
+                                                     const float* __restrict__ ws, const float* __restrict__ bs,
+                                                     float* __restrict__ y, int l1, int nb) {
+    if ((int)blockIdx.x >= *n_tiles) return;
+    const TileDesc td = tiles[blockIdx.x];
+    __shared__ float xs[TB_TILE_M][65];
+    __shared__ float wbs[TB_MAX_L1][65];
+    __shared__ float wss[64][TB_MAX_L1 + 1];
+    __shared__ int s_pos[TB_TILE_M];
+    const int tid = threadIdx.x;
+    if (tid < TB_TILE_M) s_pos[tid] = tid < td.count ? order[td.start + tid] : -1;
+    const int p = tid >> 3, og = tid & 7;
+    const bool use_b = HAS_BUCKET && td.bucket < nb;
+    float accb[4] = {0.f, 0.f, 0.f, 0.f}, accs[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < K; k0 += 64) {
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int e = tid + 256 * j;
+            const int r = e >> 6, c = e & 63;
+            const int pos = s_pos[r];
+            xs[r][c] = pos >= 0 ? x[(size_t)pos * K + k0 + c] : 0.f;
+        }
+        if (use_b)
+            for (int e = tid; e < l1 * 64; e += 256) {
+                const int o = e >> 6, c = e & 63;
+                wbs[o][c] = wb[((size_t)td.bucket * l1 + o) * K + k0 + c];
+            }
+        for (int e = tid; e < 64 * l1; e += 256) {
+            const int kk = e / l1, o = e - kk * l1;
+            wss[kk][o] = ws[(size_t)k0 * l1 + e];
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < 64; ++kk) {
+            const float xv = xs[p][kk];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int o = og + 8 * j;
+                if (o < l1) {
+                    if (use_b) accb[j] += xv * wbs[o][kk];
+                    accs[j] += xv * wss[kk][o];
+                }
+            }
+        }
+    }
+    const int pos = s_pos[p];
+    if (pos < 0) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int o = og + 8 * j;
+        if (o < l1) {
+            const float ys = bs[o] + accs[j];
+            if (HAS_BUCKET) {
+                const float yb = use_b ? bb[td.bucket * l1 + o] + accb[j] : 0.f;
+                y[(size_t)pos * l1 + o] = yb + ys;
+            } else {
+                y[(size_t)pos * l1 + o] = ys;
+            }
+        }
+    }
+}
+
+int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
+                      const int* n_tiles, int max_tiles, const float* wb, const float* bb, const float* ws,
+                      const float* bs, float* y, int l1, int nb) {
+    if (wb)
+        k_l1_forward<true><<<max_tiles, 256, 0, s>>>(x, K, order, tiles, n_tiles, wb, bb, ws, bs, y, l1, nb);
+    else
+        k_l1_forward<false><<<max_tiles, 256, 0, s>>>(x, K, order, tiles, n_tiles, wb, bb, ws, bs, y, l1, nb);
+    return 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// loss (pointwise/loss_wdl.rs:63-88, pointwise/loss_wrm.rs:99-180 default path)
+// ------------------------------------------------------------------------------------------------
+static __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+static __device__ __forceinline__ float loss_point(const LossParams& lp, float out, float score, float wdl, float* dy) {
+    if (lp.kind == 0) {
+        const float p = sigmoidf_(out * lp.scale);
+        const float ys = sigmoidf_(score * lp.scale);
+        const float y = lp.lambda * wdl + (1.0f - lp.lambda) * ys;
+        const float err = p - y;
+        *dy = 2.0f * err * p * (1.0f - p) * lp.scale * lp.norm;
+        return err;
+    }
+    const float pt = (score - lp.target_offset) / lp.target_scaling;
+    const float pmt = (-score - lp.target_offset) / lp.target_scaling;
+    const float target_wrm = 0.5f * (1.0f + sigmoidf_(pt) - sigmoidf_(pmt));
+    const float target = lp.lambda * wdl + (1.0f - lp.lambda) * target_wrm;
+    const float scorenet = out * lp.nnue2score;
+    const float q = sigmoidf_((scorenet - lp.in_offset) / lp.in_scaling);
+    const float qm = sigmoidf_((-scorenet - lp.in_offset) / lp.in_scaling);
+    const float qf = 0.5f * (1.0f + q - qm);
+    const float err = qf - target;
+    *dy = err * (lp.nnue2score / lp.in_scaling) * (q * (1.0f - q) + qm * (1.0f - qm)) * lp.norm;
+    return err;
+}
+
+// sum of err^2 over the block in f64, one partial per block (fixed order: no atomics)
+static __device__ __forceinline__ void block_loss_partial(double v, double* partials) {
+    __shared__ double s_w[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_down_sync(0xffffffffu, v, d);
+    if (lane == 0) s_w[w] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        const int nw = (blockDim.x + 31) >> 5;
+        for (int i = 0; i < nw; ++i) t += s_w[i];
+        partials[blockIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_reduce_double(const double* __restrict__ partials, int n, double* __restrict__ out) {
+    __shared__ double s[256];
+    double t = 0.0;
+    for (int i = threadIdx.x; i < n; i += 256) t += partials[i];
+    s[threadIdx.x] = t;
+    __syncthreads();
+    for (int d = 128; d > 0; d >>= 1) {
+        if ((int)threadIdx.x < d) s[threadIdx.x] += s[threadIdx.x + d];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *out = s[0];
+}
+
+// ------------------------------------------------------------------------------------------------
+// LayerStack tail, one thread per position (trainer_layerstack.rs:2530-2717 forward,
+// :2976-3325 backward): l1_total -> main / skip -> sqr, concat, CReLU -> L2 -> CReLU -> L3 -> + skip ->
+// loss, then back to dl1_total.  Keeps l2_input, dl2_out, l2_acted for the weight gradients.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_tail_layerstack(const float* __restrict__ l1_total, const int* __restrict__ bucket,
+                                                          const float* __restrict__ score, const float* __restrict__ wdl,
+                                                          const float* __restrict__ l2_w, const float* __restrict__ l2_b,
+                                                          const float* __restrict__ l3_w, const float* __restrict__ l3_b,
+                                                          LossParams lp, int B, int l1, int l2, int nb,
+                                                          float* __restrict__ net_output, float* __restrict__ dy_out,
+                                                          float* __restrict__ dl1_total, float* __restrict__ l2_input_o,
+                                                          float* __restrict__ dl2_out_o, float* __restrict__ l2_acted_o,
+                                                          double* __restrict__ loss_partials, int backward) {
+    extern __shared__ float s_w[];
+    const int l1e = l1 - 1, l2in = 2 * l1e;
+    float* sw2 = s_w;                      // [nb][l2][l2in]
+    float* sb2 = sw2 + nb * l2 * l2in;     // [nb][l2]
+    float* sw3 = sb2 + nb * l2;            // [nb][l2]
+    float* sb3 = sw3 + nb * l2;            // [nb]
+    for (int i = threadIdx.x; i < nb * l2 * l2in; i += blockDim.x) sw2[i] = l2_w[i];
+    for (int i = threadIdx.x; i < nb * l2; i += blockDim.x) { sb2[i] = l2_b[i]; sw3[i] = l3_w[i]; }
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) sb3[i] = l3_b[i];
+    __syncthreads();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    double e2 = 0.0;
+    if (b < B) {
+        const int g = bucket[b];
+        const bool valid = (unsigned)g < (unsigned)nb;
+        float pre[2 * TB_MAX_L1], in[2 * TB_MAX_L1], d2[TB_MAX_L2], a2[TB_MAX_L2];
+        float mainv[TB_MAX_L1];
+        for (int i = 0; i < l1e; ++i) {
+            const float m = l1_total[(size_t)b * l1 + i];
+            mainv[i] = m;
+            pre[i] = m * m * L1_SQR_SCALE;
+            pre[l1e + i] = m;
+        }
+        const float skip = l1_total[(size_t)b * l1 + l1e];
+        for (int i = 0; i < l2in; ++i) in[i] = crelu01(pre[i]);
+        float l3 = 0.f;
+        if (valid) {
+            for (int o = 0; o < l2; ++o) {
+                const float* wr = sw2 + ((size_t)g * l2 + o) * l2in;
+                float sum = sb2[g * l2 + o];
+                for (int i = 0; i < l2in; ++i) sum += in[i] * wr[i];
+                d2[o] = sum;
+            }
+            for (int o = 0; o < l2; ++o) a2[o] = crelu01(d2[o]);
+            l3 = sb3[g];
+            for (int o = 0; o < l2; ++o) l3 += a2[o] * sw3[g * l2 + o];
+        } else {
+            for (int o = 0; o < l2; ++o) { d2[o] = 0.f; a2[o] = 0.f; }
+        }
+        const float out = l3 + skip;
+        float dyv;
+        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
+        e2 = (double)err * (double)err;
+        net_output[b] = out;
+        dy_out[b] = dyv;
+        if (backward) {
+            float dl2o[TB_MAX_L2];
+            for (int o = 0; o < l2; ++o) {
+                const float da = valid ? dyv * sw3[g * l2 + o] : 0.f;
+                dl2o[o] = (d2[o] > 0.f && d2[o] < 1.0f) ? da : 0.f;
+            }
+            for (int i = 0; i < l2in; ++i) {
+                float sum = 0.f;
+                if (valid)
+                    for (int o = 0; o < l2; ++o) sum += dl2o[o] * sw2[((size_t)g * l2 + o) * l2in + i];
+                // crelu_grad on l2_pre, then concat split: first half is d(sqr), second half d(main)
+                pre[i] = (pre[i] > 0.f && pre[i] < 1.0f) ? sum : 0.f;
+            }
+            for (int i = 0; i < l1e; ++i) {
+                const float from_sqr = 2.0f * mainv[i] * L1_SQR_SCALE * pre[i];
+                dl1_total[(size_t)b * l1 + i] = pre[l1e + i] + from_sqr;
+            }
+            dl1_total[(size_t)b * l1 + l1e] = dyv;
+            for (int i = 0; i < l2in; ++i) l2_input_o[(size_t)b * l2in + i] = in[i];
+            for (int o = 0; o < l2; ++o) {
+                dl2_out_o[(size_t)b * l2 + o] = dl2o[o];
+                l2_acted_o[(size_t)b * l2 + o] = a2[o];
+            }
+        }
+    }
+    block_loss_partial(e2, loss_partials);
+}
+
+int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
+                           const float* wdl, const float* l2_w, const float* l2_b, const float* l3_w,
+                           const float* l3_b, LossParams lp, int B, int l1, int l2, int nb, float* net_output,
+                           float* dy, float* dl1_total, float* l2_input, float* dl2_out, float* l2_acted,
+                           double* loss_partials, double* loss_acc, int backward) {
+    const int l2in = 2 * (l1 - 1);
+    const size_t smem = sizeof(float) * ((size_t)nb * l2 * l2in + 2 * (size_t)nb * l2 + nb);
+    cudaFuncSetAttribute(k_tail_layerstack, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    const int blocks = ceil_div(B, 128);
+    k_tail_layerstack<<<blocks, 128, smem, s>>>(l1_total, bucket, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, B, l1, l2, nb,
+                                               net_output, dy, dl1_total, l2_input, dl2_out, l2_acted, loss_partials, backward);
+    k_reduce_double<<<1, 256, 0, s>>>(loss_partials, blocks, loss_acc);
+    return 2;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Simple tail (trainer_simple.rs:1281-1508 forward, :1560-1765 backward): l1_pre -> act -> L2 -> act ->
+// L3 -> loss and back to dl1_pre.  l2_w is [l1][l2], l3_w [l2].
+// ------------------------------------------------------------------------------------------------
+static __device__ __forceinline__ float act_fwd(int act, float x) {
+    const float a = crelu01(x);
+    return act == 0 ? a : a * a;
+}
+static __device__ __forceinline__ float act_grad(int act, float x, float up) {
+    if (act == 0) return (x > 0.f && x < 1.0f) ? up : 0.f;
+    const float a = crelu01(x);
+    return up * ((a > 0.f && a < 1.0f) ? 2.0f * a : 0.f);
+}
+
+__global__ void __launch_bounds__(128) k_tail_simple(const float* __restrict__ l1_pre, const float* __restrict__ score,
+                                                      const float* __restrict__ wdl, const float* __restrict__ l2_w,
+                                                      const float* __restrict__ l2_b, const float* __restrict__ l3_w,
+                                                      const float* __restrict__ l3_b, LossParams lp, int act, int B, int l1,
+                                                      int l2, float* __restrict__ net_output, float* __restrict__ dy_out,
+                                                      float* __restrict__ dl1_pre, float* __restrict__ l1_acted_o,
+                                                      float* __restrict__ dl2_pre_o, float* __restrict__ l2_acted_o,
+                                                      double* __restrict__ loss_partials, int backward) {
+    extern __shared__ float s_w[];
+    float* sw2 = s_w;            // [l1][l2]
+    float* sb2 = sw2 + l1 * l2;  // [l2]
+    float* sw3 = sb2 + l2;       // [l2]
+    for (int i = threadIdx.x; i < l1 * l2; i += blockDim.x) sw2[i] = l2_w[i];
+    for (int i = threadIdx.x; i < l2; i += blockDim.x) { sb2[i] = l2_b[i]; sw3[i] = l3_w[i]; }
+    __syncthreads();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    double e2 = 0.0;
+    if (b < B) {
+        float x1[TB_MAX_L1 * 2], a1[TB_MAX_L1 * 2], x2[TB_MAX_L2], a2[TB_MAX_L2];
+        for (int i = 0; i < l1; ++i) { x1[i] = l1_pre[(size_t)b * l1 + i]; a1[i] = act_fwd(act, x1[i]); }
+        for (int o = 0; o < l2; ++o) {
+            float sum = sb2[o];
+            for (int i = 0; i < l1; ++i) sum += a1[i] * sw2[i * l2 + o];
+            x2[o] = sum;
+            a2[o] = act_fwd(act, sum);
+        }
+        float out = l3_b[0];
+        for (int o = 0; o < l2; ++o) out += a2[o] * sw3[o];
+        float dyv;
+        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
+        e2 = (double)err * (double)err;
+        net_output[b] = out;
+        dy_out[b] = dyv;
+        if (backward) {
+            float d2[TB_MAX_L2];
+            for (int o = 0; o < l2; ++o) d2[o] = act_grad(act, x2[o], dyv * sw3[o]);
+            for (int i = 0; i < l1; ++i) {
+                float sum = 0.f;
+                for (int o = 0; o < l2; ++o) sum += d2[o] * sw2[i * l2 + o];
+                dl1_pre[(size_t)b * l1 + i] = act_grad(act, x1[i], sum);
+                l1_acted_o[(size_t)b * l1 + i] = a1[i];
+            }
+            for (int o = 0; o < l2; ++o) {
+                dl2_pre_o[(size_t)b * l2 + o] = d2[o];
+                l2_acted_o[(size_t)b * l2 + o] = a2[o];
+            }
+        }
+    }
+    block_loss_partial(e2, loss_partials);
+}
+
+int launch_tail_simple(cudaStream_t s, const float* l1_pre, const float* score, const float* wdl,
+                       const float* l2_w, const float* l2_b, const float* l3_w, const float* l3_b, LossParams lp,
+                       int act, int B, int l1, int l2, float* net_output, float* dy, float* dl1_pre,
+                       float* l1_acted, float* dl2_pre, float* l2_acted, double* loss_partials,
+                       double* loss_acc, int backward) {
+    const size_t smem = sizeof(float) * ((size_t)l1 * l2 + 2 * (size_t)l2);
+    const int blocks = ceil_div(B, 128);
+    k_tail_simple<<<blocks, 128, smem, s>>>(l1_pre, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, act, B, l1, l2, net_output, dy,
+                                           dl1_pre, l1_acted, dl2_pre, l2_acted, loss_partials, backward);
+    k_reduce_double<<<1, 256, 0, s>>>(loss_partials, blocks, loss_acc);
+    return 2;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Weight gradients of the small layers (L2, L3, their biases and the L1 biases), per bucket segment.
+// cells of a segment: [0, R*C): sum_b U[b][cell / C] * V[b][cell % C]      (L2 weight)
+//                     then l2: sum_b Bsrc[b][o]                           (L2 bias)
+//                     then l2: sum_b l2_acted[b][o] * dy[b]               (L3 weight)
+//                     then 1 : sum_b dy[b]                                (L3 bias)
+//                     then l1: sum_b dl1[b][o]                            (L1 bias)
+// grid (segments, SPLIT): block (g, s) reduces the s-th slice of segment g into partials; a second
+// kernel adds the SPLIT partials in order.  No atomics: results do not depend on scheduling.
+// (dense_mm_bucket.rs:112-161; native_kernels.cu:2591-2744 use register accumulators + atomics.)
+// ------------------------------------------------------------------------------------------------
+#define SW_CMAX 5
+__global__ void __launch_bounds__(1024) k_small_wgrad(const int* __restrict__ order, const int* __restrict__ seg_start,
+                                                       const float* __restrict__ U, int dimU, const float* __restrict__ V,
+                                                       int dimV, const float* __restrict__ Bsrc, const float* __restrict__ l2_acted,
+                                                       int l2, const float* __restrict__ dy, const float* __restrict__ dl1,
+                                                       int l1, float* __restrict__ partials, int n_cells) {
+    extern __shared__ float s_stage[];
+    const int g = blockIdx.x, sp = blockIdx.y;
+    const int SW_SPLIT = gridDim.y;
+    const int sbeg = seg_start[g], send = seg_start[g + 1];
+    const int len = send - sbeg;
+    const int per = (len + SW_SPLIT - 1) / SW_SPLIT;
+    const int beg = sbeg + min(sp * per, len), end = sbeg + min((sp + 1) * per, len);
+    float* sU = s_stage;              // [32][dimU]
+    float* sV = sU + 32 * dimU;       // [32][dimV]
+    float* sB = sV + 32 * dimV;       // [32][l2]
+    float* sA = sB + 32 * l2;         // [32][l2]
+    float* sD = sA + 32 * l2;         // [32][l1]
+    float* sY = sD + 32 * l1;         // [32]
+    __shared__ int s_pos[32];
+    const int nW = dimU * dimV;
+    float acc[SW_CMAX];
+#pragma unroll
+    for (int j = 0; j < SW_CMAX; ++j) acc[j] = 0.f;
+    for (int r0 = beg; r0 < end; r0 += 32) {
+        const int cnt = min(32, end - r0);
+        __syncthreads();
+        if (threadIdx.x < 32) s_pos[threadIdx.x] = (int)threadIdx.x < cnt ? (order ? order[r0 + threadIdx.x] : r0 + threadIdx.x) : -1;
+        __syncthreads();
+        for (int e = threadIdx.x; e < 32 * dimU; e += blockDim.x) { const int r = e / dimU, c = e - r * dimU; const int p = s_pos[r]; sU[e] = p >= 0 ? U[(size_t)p * dimU + c] : 0.f; }
+        for (int e = threadIdx.x; e < 32 * dimV; e += blockDim.x) { const int r = e / dimV, c = e - r * dimV; const int p = s_pos[r]; sV[e] = p >= 0 ? V[(size_t)p * dimV + c] : 0.f; }
+        for (int e = threadIdx.x; e < 32 * l2; e += blockDim.x) {
+            const int r = e / l2, c = e - r * l2; const int p = s_pos[r];
+            sB[e] = p >= 0 ? Bsrc[(size_t)p * l2 + c] : 0.f;
+            sA[e] = p >= 0 ? l2_acted[(size_t)p * l2 + c] : 0.f;
+        }
+        for (int e = threadIdx.x; e < 32 * l1; e += blockDim.x) { const int r = e / l1, c = e - r * l1; const int p = s_pos[r]; sD[e] = p >= 0 ? dl1[(size_t)p * l1 + c] : 0.f; }
+        if (threadIdx.x < 32) { const int p = s_pos[threadIdx.x]; sY[threadIdx.x] = p >= 0 ? dy[p] : 0.f; }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < SW_CMAX; ++j) {
+            const int cell = threadIdx.x + j * 1024;
+            if (cell >= n_cells) continue;
+            float a = acc[j];
+            if (cell < nW) {
+                const int u = cell / dimV, v = cell - u * dimV;
+                for (int r = 0; r < cnt; ++r) a += sU[r * dimU + u] * sV[r * dimV + v];
+            } else if (cell < nW + l2) {
+                const int o = cell - nW;
+                for (int r = 0; r < cnt; ++r) a += sB[r * l2 + o];
+            } else if (cell < nW + 2 * l2) {
+                const int o = cell - nW - l2;
+                for (int r = 0; r < cnt; ++r) a += sA[r * l2 + o] * sY[r];
+            } else if (cell == nW + 2 * l2) {
+                for (int r = 0; r < cnt; ++r) a += sY[r];
+            } else {
+                const int o = cell - nW - 2 * l2 - 1;
+                for (int r = 0; r < cnt; ++r) a += sD[r * l1 + o];
+            }
+            acc[j] = a;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < SW_CMAX; ++j) {
+        const int cell = threadIdx.x + j * 1024;
+        if (cell < n_cells) partials[((size_t)g * SW_SPLIT + sp) * n_cells + cell] = acc[j];
+    }
+}
+
+// n_seg segments (the last one holds positions with an out-of-range bucket when has_invalid).
+__global__ void k_small_wgrad_final(const float* __restrict__ partials, int n_seg, int has_invalid, int SW_SPLIT, int n_cells, int nW,
+                                    int l2, int l1, float* __restrict__ gw2, float* __restrict__ gb2, float* __restrict__ gw3,
+                                    float* __restrict__ gb3, float* __restrict__ gb1, float* __restrict__ gb1_shared) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n_real = has_invalid ? n_seg - 1 : n_seg;
+    if (i < n_real * n_cells) {
+        const int g = i / n_cells, cell = i - g * n_cells;
+        float sum = 0.f;
+        for (int sp = 0; sp < SW_SPLIT; ++sp) sum += partials[((size_t)g * SW_SPLIT + sp) * n_cells + cell];
+        if (cell < nW) gw2[(size_t)g * nW + cell] = sum;
+        else if (cell < nW + l2) gb2[g * l2 + (cell - nW)] = sum;
+        else if (cell < nW + 2 * l2) gw3[g * l2 + (cell - nW - l2)] = sum;
+        else if (cell == nW + 2 * l2) gb3[g] = sum;
+        else gb1[g * l1 + (cell - nW - 2 * l2 - 1)] = sum;
+    }
+    if (gb1_shared && i < l1) {
+        // shared L1 bias: every position contributes, also those with an out-of-range bucket
+        float tot = 0.f;
+        const int cell = nW + 2 * l2 + 1 + i;
+        for (int g = 0; g < n_seg; ++g) {
+            float sum = 0.f;
+            for (int sp = 0; sp < SW_SPLIT; ++sp) sum += partials[((size_t)g * SW_SPLIT + sp) * n_cells + cell];
+            tot += sum;
+        }
+        gb1_shared[i] = tot;
+    }
+}
+
+static int small_wgrad(cudaStream_t s, const int* order, const int* seg_start, int n_seg, int has_invalid, int split,
+                       const float* U, int dimU, const float* V, int dimV, const float* Bsrc, const float* l2_acted,
+                       int l2, const float* dy, const float* dl1, int l1, float* partials, float* gw2, float* gb2,
+                       float* gw3, float* gb3, float* gb1, float* gb1_shared) {
+    const int nW = dimU * dimV;
+    const int n_cells = nW + 2 * l2 + 1 + l1;
+    const size_t smem = sizeof(float) * 32 * ((size_t)dimU + dimV + 2 * l2 + l1 + 1);
+    cudaFuncSetAttribute(k_small_wgrad, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    k_small_wgrad<<<dim3(n_seg, split), 1024, smem, s>>>(order, seg_start, U, dimU, V, dimV, Bsrc, l2_acted, l2, dy, dl1,
+                                                          l1, partials, n_cells);
+    const int n = n_seg * n_cells;
+    k_small_wgrad_final<<<ceil_div(n > l1 ? n : l1, 256), 256, 0, s>>>(partials, n_seg, has_invalid, split, n_cells, nW, l2, l1, gw2,
+                                                                      gb2, gw3, gb3, gb1, gb1_shared);
+    return 2;
+}
+
+int launch_small_wgrad_layerstack(cudaStream_t s, const int* order, const int* seg_start, int B, int l1, int l2,
+                                  int nb, const float* l2_input, const float* dl2_out, const float* l2_acted,
+                                  const float* dy, const float* dl1_total, float* partials, float* l2_w_grad,
+                                  float* l2_b_grad, float* l3_w_grad, float* l3_b_grad, float* l1_b_grad,
+                                  float* l1s_b_grad) {
+    (void)B;
+    // L2 weight cell (o, i) = sum dl2_out[b][o] * l2_input[b][i]
+    return small_wgrad(s, order, seg_start, nb + 1, 1, 16, dl2_out, l2, l2_input, 2 * (l1 - 1), dl2_out, l2_acted, l2, dy,
+                       dl1_total, l1, partials, l2_w_grad, l2_b_grad, l3_w_grad, l3_b_grad, l1_b_grad, l1s_b_grad);
+}
+
+int launch_small_wgrad_simple(cudaStream_t s, const int* order, const int* seg_start, int B, int l1, int l2,
+                              const float* l1_acted, const float* dl2_pre, const float* l2_acted, const float* dy,
+                              const float* dl1_pre, float* partials, float* l2_w_grad, float* l2_b_grad,
+                              float* l3_w_grad, float* l3_b_grad, float* l1_b_grad) {
+    (void)B;
+    // L2 weight cell (i, o) = sum l1_acted[b][i] * dl2_pre[b][o]; the whole batch is one segment
+    return small_wgrad(s, order, seg_start, 1, 0, 128, l1_acted, l1, dl2_pre, l2, dl2_pre, l2_acted, l2, dy, dl1_pre, l1,
+                       partials, l2_w_grad, l2_b_grad, l3_w_grad, l3_b_grad, l1_b_grad, nullptr);
+}
+
+// ------------------------------------------------------------------------------------------------
+// L1 weight gradient.  gw_bucket[g][o][k] = sum over positions of bucket g of dl1[b][o] * x[b][k]
+// (dense_mm_bucket.rs:112-135); gw_shared[k][o] = the same sum over every position (dense_mm.rs:75-92),
+// obtained as the sum of the per-bucket results.  Work unit = up to UNIT_TILES tiles of one bucket;
+// block (column chunk of 128, unit) writes partials[unit][o][k]; the second kernel adds the units of
+// each bucket in order.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_l1_wgrad(const float* __restrict__ x, int K, const float* __restrict__ dl1,
+                                                   const int* __restrict__ order, const TileDesc* __restrict__ tiles,
+                                                   const TileDesc* __restrict__ units, const int* __restrict__ n_units, int l1,
+                                                   float* __restrict__ partials) {
+    const int u = blockIdx.y;
+    if (u >= *n_units) return;
+    const TileDesc ud = units[u];
+    __shared__ float sdl[TB_TILE_M][TB_MAX_L1];
+    __shared__ int s_pos[TB_TILE_M];
+    const int col = blockIdx.x * 128 + (threadIdx.x & 127);
+    const int oh = threadIdx.x >> 7;
+    float acc[TB_MAX_L1 / 2];
+#pragma unroll
+    for (int j = 0; j < TB_MAX_L1 / 2; ++j) acc[j] = 0.f;
+    for (int t = ud.start; t < ud.start + ud.count; ++t) {
+        const TileDesc td = tiles[t];
+        __syncthreads();
+        if (threadIdx.x < TB_TILE_M) s_pos[threadIdx.x] = (int)threadIdx.x < td.count ? order[td.start + threadIdx.x] : -1;
+        __syncthreads();
+        for (int e = threadIdx.x; e < TB_TILE_M * l1; e += 256) {
+            const int r = e / l1, o = e - r * l1;
+            const int p = s_pos[r];
+            sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
+        }
+        __syncthreads();
+        for (int r0 = 0; r0 < td.count; r0 += 4) {
+            float xv[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int p = r0 + q < td.count ? s_pos[r0 + q] : -1;
+                xv[q] = p >= 0 ? __ldg(x + (size_t)p * K + col) : 0.f;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (r0 + q < td.count) {
+#pragma unroll
+                    for (int j = 0; j < TB_MAX_L1 / 2; ++j) {
+                        const int o = oh + 2 * j;
+                        if (o < l1) acc[j] += sdl[r0 + q][o] * xv[q];
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < TB_MAX_L1 / 2; ++j) {
+        const int o = oh + 2 * j;
+        if (o < l1) partials[((size_t)u * l1 + o) * K + col] = acc[j];
+    }
+}
+
+__global__ void __launch_bounds__(256) k_l1_wgrad_final(const float* __restrict__ partials, const TileDesc* __restrict__ units,
+                                                         const int* __restrict__ n_units, int K, int l1, int nb,
+                                                         float* __restrict__ gw_bucket, float* __restrict__ gw_shared) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= l1 * K) return;
+    const int o = i / K, k = i - o * K;
+    const int nu = *n_units;
+    float total = 0.f;
+    int u = 0;
+    for (int g = 0; g <= nb; ++g) {
+        float sum = 0.f;
+        while (u < nu && units[u].bucket == g) {
+            sum += partials[((size_t)u * l1 + o) * K + k];
+            ++u;
+        }
+        if (gw_bucket && g < nb) gw_bucket[((size_t)g * l1 + o) * K + k] = sum;
+        total += sum;
+    }
+    gw_shared[(size_t)k * l1 + o] = total;
+}
+
+int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, const int* order,
+                    const TileDesc* tiles, const int* n_tiles, int max_tiles, int l1, int nb, float* partials,
+                    float* gw_bucket, float* gw_shared) {
+    const TileDesc* units = tiles + max_tiles;
+    const int* n_units = n_tiles + 1;
+    const int max_units = max_tiles / UNIT_TILES + TB_MAX_BUCKETS + 2;
+    k_l1_wgrad<<<dim3(K / 128, max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+    k_l1_wgrad_final<<<ceil_div(l1 * K, 256), 256, 0, s>>>(partials, units, n_units, K, l1, nb, gw_bucket, gw_shared);
+    return 2;
+}
+
+// ------------------------------------------------------------------------------------------------
+// L1 input gradient fused with the FT activation gradient.
+//   d[b, c] = sum_o dl1[b, o] * (wb[g, o, c] + ws[c, o])          (never written to memory)
+// LayerStack (mode 1): c = persp*F/2 + r is the pair (r, r + F/2) of one perspective,
+//   dft[b, r]       = 0 < xa < 1 ? d * crelu(xb) * scale : 0      xa = pre[b, r] + bias[r]
+//   dft[b, r + F/2] = 0 < xb < 1 ? d * crelu(xa) * scale : 0      xb = pre[b, r + F/2] + bias[r + F/2]
+//   (ft_post_perspective.rs:92-129 on the sum of the two L1 input gradients, native_kernels.cu:2260)
+// Simple (mode 2 CReLU / 3 SCReLU): c = persp*F + col, pre already holds the biased value,
+//   dft[b, col] = act'(pre[b, col]) * d                            (native_kernels.cu:1452-1497)
+// The FT bias gradient is accumulated per block in registers and written as one partial row per block.
+// grid (n_ctas, 2 perspectives, column chunks); a block walks the tiles t = blockIdx.x, += gridDim.x and
+// keeps the effective weights of the current bucket in shared memory.
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict__ dl1, const int* __restrict__ order,
+                                                          const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
+                                                          const float* __restrict__ wb, const float* __restrict__ ws,
+                                                          const float* __restrict__ pre_stm, const float* __restrict__ pre_nstm,
+                                                          const float* __restrict__ ft_bias, float scale, int F, int l1, int nb,
+                                                          int CW, float* __restrict__ dft_stm, float* __restrict__ dft_nstm,
+                                                          float* __restrict__ bias_partials) {
+    extern __shared__ float s_weff[];  // [l1][CW]
+    __shared__ float sdl[TB_TILE_M][TB_MAX_L1];
+    __shared__ int s_pos[TB_TILE_M];
+    const int persp = blockIdx.y;
+    const int chunk = blockIdx.z;
+    const int half = F >> 1;
+    const int Kin = MODE == 1 ? F : 2 * F;                        // row length of the L1 input
+    const int cbase = (MODE == 1 ? persp * half : persp * F) + chunk * CW;  // first L1 input column of this block
+    const int wcol = chunk * CW + 4 * threadIdx.x;                // column inside the perspective
+    const float* __restrict__ pre = persp ? pre_nstm : pre_stm;
+    float* __restrict__ dft = persp ? dft_nstm : dft_stm;
+    const int nt = *n_tiles;
+    int cur_bucket = -1;
+    float4 bacc0 = make_float4(0.f, 0.f, 0.f, 0.f), bacc1 = bacc0;
+    float4 bias0 = make_float4(0.f, 0.f, 0.f, 0.f), bias1 = bias0;
+    if (MODE == 1) {
+        bias0 = *reinterpret_cast<const float4*>(ft_bias + wcol);
+        bias1 = *reinterpret_cast<const float4*>(ft_bias + half + wcol);
+    }
+    for (int t = blockIdx.x; t < nt; t += gridDim.x) {
+        const TileDesc td = tiles[t];
+        __syncthreads();
+        if (td.bucket != cur_bucket) {
+            cur_bucket = td.bucket;
+            const bool use_b = wb != nullptr && td.bucket < nb;
+            for (int e = threadIdx.x; e < l1 * CW; e += blockDim.x) {
+                const int o = e / CW, c = e - o * CW;
+                float v = ws[(size_t)(cbase + c) * l1 + o];
+                if (use_b) v = wb[((size_t)td.bucket * l1 + o) * Kin + cbase + c] + v;
+                s_weff[e] = v;
+            }
+        }
+        for (int i = threadIdx.x; i < TB_TILE_M; i += blockDim.x) s_pos[i] = i < td.count ? order[td.start + i] : -1;
+        __syncthreads();
+        for (int e = threadIdx.x; e < TB_TILE_M * l1; e += blockDim.x) {
+            const int r = e / l1, o = e - r * l1;
+            const int p = s_pos[r];
+            sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
+        }
+        __syncthreads();
+        for (int r0 = 0; r0 < td.count; r0 += 2) {
+            float4 xa[2], xb[2];
+            int pp[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
+                if (pp[q] >= 0) {
+                    xa[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + wcol);
+                    if (MODE == 1) xb[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + half + wcol);
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                if (pp[q] < 0) continue;
+                float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int o = 0; o < l1; ++o) {
+                    const float g = sdl[r0 + q][o];
+                    const float4 w4 = *reinterpret_cast<const float4*>(s_weff + o * CW + 4 * threadIdx.x);
+                    d.x += g * w4.x; d.y += g * w4.y; d.z += g * w4.z; d.w += g * w4.w;
+                }
+                if (MODE == 1) {
+                    const float4 a = make_float4(xa[q].x + bias0.x, xa[q].y + bias0.y, xa[q].z + bias0.z, xa[q].w + bias0.w);
+                    const float4 b = make_float4(xb[q].x + bias1.x, xb[q].y + bias1.y, xb[q].z + bias1.z, xb[q].w + bias1.w);
+                    float4 ga, gb;
+                    ga.x = (a.x > 0.f && a.x < 1.f) ? d.x * crelu01(b.x) * scale : 0.f;
+                    ga.y = (a.y > 0.f && a.y < 1.f) ? d.y * crelu01(b.y) * scale : 0.f;
+                    ga.z = (a.z > 0.f && a.z < 1.f) ? d.z * crelu01(b.z) * scale : 0.f;
+                    ga.w = (a.w > 0.f && a.w < 1.f) ? d.w * crelu01(b.w) * scale : 0.f;
+                    gb.x = (b.x > 0.f && b.x < 1.f) ? d.x * crelu01(a.x) * scale : 0.f;
+                    gb.y = (b.y > 0.f && b.y < 1.f) ? d.y * crelu01(a.y) * scale : 0.f;
+                    gb.z = (b.z > 0.f && b.z < 1.f) ? d.z * crelu01(a.z) * scale : 0.f;
+                    gb.w = (b.w > 0.f && b.w < 1.f) ? d.w * crelu01(a.w) * scale : 0.f;
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = ga;
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + half + wcol) = gb;
+                    bacc0.x += ga.x; bacc0.y += ga.y; bacc0.z += ga.z; bacc0.w += ga.w;
+                    bacc1.x += gb.x; bacc1.y += gb.y; bacc1.z += gb.z; bacc1.w += gb.w;
+                } else {
+                    const float4 x = xa[q];
+                    float4 g;
+                    if (MODE == 2) {
+                        g.x = (x.x > 0.f && x.x < 1.f) ? d.x : 0.f;
+                        g.y = (x.y > 0.f && x.y < 1.f) ? d.y : 0.f;
+                        g.z = (x.z > 0.f && x.z < 1.f) ? d.z : 0.f;
+                        g.w = (x.w > 0.f && x.w < 1.f) ? d.w : 0.f;
+                    } else {
+                        const float4 a = make_float4(crelu01(x.x), crelu01(x.y), crelu01(x.z), crelu01(x.w));
+                        g.x = d.x * ((a.x > 0.f && a.x < 1.f) ? 2.0f * a.x : 0.f);
+                        g.y = d.y * ((a.y > 0.f && a.y < 1.f) ? 2.0f * a.y : 0.f);
+                        g.z = d.z * ((a.z > 0.f && a.z < 1.f) ? 2.0f * a.z : 0.f);
+                        g.w = d.w * ((a.w > 0.f && a.w < 1.f) ? 2.0f * a.w : 0.f);
+                    }
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = g;
+                    bacc0.x += g.x; bacc0.y += g.y; bacc0.z += g.z; bacc0.w += g.w;
+                }
+            }
+        }
+    }
+    // one partial row per (block, perspective): [n_ctas][2][F]
+    float* bp = bias_partials + ((size_t)blockIdx.x * 2 + persp) * F;
+    *reinterpret_cast<float4*>(bp + wcol) = bacc0;
+    if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
+}
+
+__global__ void k_bias_partials_reduce(const float* __restrict__ partials, int n_rows, int F, float* __restrict__ out) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= F) return;
+    // stm partials of every block first, then nstm: the accumulation order of the two
+    // ft_post_perspective_grad calls
+    float sum = 0.f;
+    for (int p = 0; p < 2; ++p)
+        for (int r = 0; r < n_rows; ++r) sum += partials[((size_t)r * 2 + p) * F + c];
+    out[c] = sum;
+}
+
+int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int* order, const TileDesc* tiles,
+                           const int* n_tiles, int max_tiles, const float* wb, const float* ws,
+                           const float* pre_stm, const float* pre_nstm, const float* ft_bias, float scale,
+                           int B, int F, int l1, int nb, float* dft_stm, float* dft_nstm, float* bias_partials,
+                           float* ft_b_grad, int n_ctas) {
+    (void)B;
+    (void)max_tiles;
+    const int work_cols = mode == 1 ? F / 2 : F;
+    int n_chunks = 1;
+    while ((size_t)(work_cols / n_chunks) * l1 * 4 > 64 * 1024 || work_cols / n_chunks > 1024) n_chunks *= 2;
+    const int CW = work_cols / n_chunks;
+    const size_t smem = (size_t)CW * l1 * sizeof(float);
+    dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
+    if (mode == 1) {
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        k_l1_dgrad_ftgrad<1><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);
+    } else if (mode == 2) {
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        k_l1_dgrad_ftgrad<2><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);
+    } else {
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        k_l1_dgrad_ftgrad<3><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);
+    }
+    k_bias_partials_reduce<<<ceil_div(F, 256), 256, 0, s>>>(bias_partials, n_ctas, F, ft_b_grad);
+    return 2;
+}

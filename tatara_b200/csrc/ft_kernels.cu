@@ -1,0 +1,420 @@
+// Sparse feature-transformer kernels: forward gather-sum (fused with the FT activation), inverse
+// index, backward segmented reduce, factorizer reduce / fold.
+//
+// Layout: the FT table is row-major [rows, F] f32 (w[f*F + c], native_kernels.cu:162-200); every
+// per-position tensor is row-major [B, F].  F is a multiple of 128, so rows are 512-byte aligned and
+// every access below is a 128-bit vector.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------------
+// forward: one (position, perspective) item per group of F/8 threads.  Thread `lane` owns the float4
+// at column 4*lane and its pair partner at column F/2 + 4*lane, so that the pairwise product of the
+// LayerStack activation never leaves the thread.  Rows are added in slot order with plain f32 adds:
+// the sums are bit-identical to sparse_ft_forward_cpu (sparse/sparse_ft_forward.rs:54-78).
+// ------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ table, const int* __restrict__ idx_stm,
+                                                     const int* __restrict__ idx_nstm, const int* __restrict__ nnz,
+                                                     const float* __restrict__ bias, float* __restrict__ pre_stm,
+                                                     float* __restrict__ pre_nstm, float* __restrict__ combined,
+                                                     int B, int F, int N, int A, float scale, int ipc) {
+    extern __shared__ int s_idx[];  // [ipc][A]
+    const int tpi = F >> 3;
+    const int il = threadIdx.x / tpi;
+    const int lane = threadIdx.x - il * tpi;
+    const int persp = blockIdx.y;
+    const int* __restrict__ idx = persp ? idx_nstm : idx_stm;
+    const int item0 = blockIdx.x * ipc;
+
+    for (int i = threadIdx.x; i < ipc * A; i += blockDim.x) {
+        const int li = i / A, a = i - li * A;
+        const int it = item0 + li;
+        int v = -1;
+        if (it < B && a < nnz[it]) v = idx[(size_t)it * A + a];
+        if ((unsigned)v >= (unsigned)N) v = -1;  // padding and out-of-range indices are skipped
+        s_idx[i] = v;
+    }
+    __syncthreads();
+    const int item = item0 + il;
+    if (item >= B) return;
+    int n = nnz[item];
+    n = n < 0 ? 0 : (n > A ? A : n);
+    const int* my = s_idx + il * A;
+    const float4* __restrict__ t4 = reinterpret_cast<const float4*>(table);
+    const int row4 = F >> 2;
+    const int c0 = lane, c1 = lane + tpi;
+
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+    for (int a0 = 0; a0 < n; a0 += 8) {
+        float4 va[8], vb[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int f = (a0 + u < n) ? my[a0 + u] : -1;
+            if (f >= 0) {
+                const float4* r = t4 + (size_t)f * row4;
+                va[u] = __ldg(r + c0);
+                vb[u] = __ldg(r + c1);
+            } else {
+                va[u] = make_float4(0.f, 0.f, 0.f, 0.f);  // x + 0.0 == x: a skipped slot leaves the sum unchanged
+                vb[u] = va[u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            acc0.x += va[u].x; acc0.y += va[u].y; acc0.z += va[u].z; acc0.w += va[u].w;
+            acc1.x += vb[u].x; acc1.y += vb[u].y; acc1.z += vb[u].z; acc1.w += vb[u].w;
+        }
+    }
+
+    float4* pre = reinterpret_cast<float4*>(persp ? pre_nstm : pre_stm) + (size_t)item * row4;
+    if (MODE == 0) {
+        pre[c0] = acc0;
+        pre[c1] = acc1;
+    } else if (MODE == 1) {
+        // ft_post_perspective_fwd (layerstack/ft_post_perspective.rs:57-83): the raw sums are kept for the
+        // backward pass, combined[b, persp*F/2 + r] = crelu(x_r + b_r) * crelu(x_{r+F/2} + b_{r+F/2}) * scale
+        pre[c0] = acc0;
+        pre[c1] = acc1;
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias) + c0);
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + c1);
+        float4 o;
+        o.x = crelu01(acc0.x + b0.x) * crelu01(acc1.x + b1.x) * scale;
+        o.y = crelu01(acc0.y + b0.y) * crelu01(acc1.y + b1.y) * scale;
+        o.z = crelu01(acc0.z + b0.z) * crelu01(acc1.z + b1.z) * scale;
+        o.w = crelu01(acc0.w + b0.w) * crelu01(acc1.w + b1.w) * scale;
+        reinterpret_cast<float4*>(combined)[(size_t)item * row4 + persp * tpi + c0] = o;
+    } else {
+        // simple_ft_post_fused_{crelu,screlu} (native_kernels.cu:1406-1450): the biased value replaces the
+        // raw sum, combined[b, persp*F + c] = act(x)
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias) + c0);
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + c1);
+        float4 x0 = make_float4(acc0.x + b0.x, acc0.y + b0.y, acc0.z + b0.z, acc0.w + b0.w);
+        float4 x1 = make_float4(acc1.x + b1.x, acc1.y + b1.y, acc1.z + b1.z, acc1.w + b1.w);
+        pre[c0] = x0;
+        pre[c1] = x1;
+        float4 a0 = make_float4(crelu01(x0.x), crelu01(x0.y), crelu01(x0.z), crelu01(x0.w));
+        float4 a1 = make_float4(crelu01(x1.x), crelu01(x1.y), crelu01(x1.z), crelu01(x1.w));
+        if (MODE == 3) {
+            a0.x *= a0.x; a0.y *= a0.y; a0.z *= a0.z; a0.w *= a0.w;
+            a1.x *= a1.x; a1.y *= a1.y; a1.z *= a1.z; a1.w *= a1.w;
+        }
+        float4* comb = reinterpret_cast<float4*>(combined) + (size_t)item * (2 * row4) + persp * row4;
+        comb[c0] = a0;
+        comb[c1] = a1;
+    }
+}
+
+int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
+                      const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
+                      int B, int F, int N, int A, float scale, int n_persp) {
+    if (B <= 0) return 0;
+    const int tpi = F / 8;
+    int ipc = 256 / tpi;
+    if (ipc < 1) ipc = 1;
+    dim3 grid(ceil_div(B, ipc), n_persp), block(ipc * tpi);
+    size_t smem = (size_t)ipc * A * sizeof(int);
+    switch (mode) {
+        case 0: k_ft_forward<0><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
+        case 1: k_ft_forward<1><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
+        case 2: k_ft_forward<2><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
+        default: k_ft_forward<3><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
+    }
+    return 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// inverse index: for every feature the list of positions that hold it (the counting sort of
+// native_kernels.cu:1630-1765: histogram, exclusive scan, ranked scatter).
+// ------------------------------------------------------------------------------------------------
+__global__ void k_feat_count(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
+                             const int* __restrict__ nnz, int B, int A, int N, int n_persp, int* __restrict__ counts) {
+    const long long total = (long long)n_persp * B * A;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int p = (int)(i / ((long long)B * A));
+        const long long r = i - (long long)p * B * A;
+        const int b = (int)(r / A), a = (int)(r - (long long)b * A);
+        if (a >= nnz[b]) continue;
+        const int f = (p ? idx_nstm : idx_stm)[r];
+        if ((unsigned)f < (unsigned)N) atomicAdd(counts + (size_t)p * N + f, 1);
+    }
+}
+
+// one block per perspective: offsets[p][0..N] = exclusive prefix sum of counts[p][0..N)
+__global__ void __launch_bounds__(1024) k_feat_scan(const int* __restrict__ counts, int N, int* __restrict__ offsets,
+                                                     int* __restrict__ cursor) {
+    __shared__ int warp_tot[32];
+    __shared__ int carry;
+    const int p = blockIdx.x;
+    const int* c = counts + (size_t)p * N;
+    int* o = offsets + (size_t)p * (N + 1);
+    int* cur = cursor + (size_t)p * N;
+    const int per = (N + blockDim.x - 1) / blockDim.x;
+    const int beg = threadIdx.x * per;
+    const int end = min(beg + per, N);
+    int sum = 0;
+    for (int i = beg; i < end; ++i) sum += c[i];
+    // block-wide exclusive scan of `sum`
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += t;
+    }
+    if (lane == 31) warp_tot[w] = incl;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    if (w == 0) {
+        int t = lane < (blockDim.x >> 5) ? warp_tot[lane] : 0;
+        int ti = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int u = __shfl_up_sync(0xffffffffu, ti, d);
+            if (lane >= d) ti += u;
+        }
+        warp_tot[lane] = ti - t;  // exclusive warp offsets
+        if (lane == 31) carry = ti;
+    }
+    __syncthreads();
+    int run = warp_tot[w] + incl - sum;
+    for (int i = beg; i < end; ++i) {
+        o[i] = run;
+        cur[i] = run;
+        run += c[i];
+    }
+    if (threadIdx.x == 0) o[N] = carry;
+}
+
+__global__ void k_feat_fill(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
+                            const int* __restrict__ nnz, int B, int A, int N, int n_persp, int* __restrict__ cursor,
+                            int* __restrict__ lists) {
+    const long long total = (long long)n_persp * B * A;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int p = (int)(i / ((long long)B * A));
+        const long long r = i - (long long)p * B * A;
+        const int b = (int)(r / A), a = (int)(r - (long long)b * A);
+        if (a >= nnz[b]) continue;
+        const int f = (p ? idx_nstm : idx_stm)[r];
+        if ((unsigned)f < (unsigned)N) {
+            const int pos = atomicAdd(cursor + (size_t)p * N + f, 1);
+            lists[(size_t)p * B * A + pos] = b;
+        }
+    }
+}
+
+// The ranked scatter above leaves every list in arrival order.  The two kernels below sort each list
+// ascending, so that the backward sums always run in position order (deterministic results).
+// Short lists (<= 64 entries): one warp ranks its entries against each other through shuffles.
+// Long lists: queued, then one block per list marks the positions in a shared-memory bitmap and reads
+// the set bits back in order; a list that names a position twice (only possible when the caller's
+// index row repeats a feature) falls back to ranking by counting.
+__global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict__ offsets, int N, int n_persp, int B, int A,
+                                                           int* __restrict__ lists, int* __restrict__ long_queue,
+                                                           int* __restrict__ long_count) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_persp * N) return;
+    const int p = warp / N, f = warp - p * N;
+    const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
+    const int len = end - beg;
+    if (len < 2) return;
+    if (len > 64) {
+        if (lane == 0) long_queue[atomicAdd(long_count, 1)] = warp;
+        return;
+    }
+    int* L = lists + (size_t)p * B * A + beg;
+    const int v0 = lane < len ? L[lane] : 0x7fffffff;
+    const int v1 = lane + 32 < len ? L[lane + 32] : 0x7fffffff;
+    int r0 = 0, r1 = 0;
+    for (int j = 0; j < len; ++j) {
+        const int u = __shfl_sync(0xffffffffu, j < 32 ? v0 : v1, j & 31);
+        r0 += (u < v0) || (u == v0 && j < lane);
+        r1 += (u < v1) || (u == v1 && j < lane + 32);
+    }
+    __syncwarp();
+    if (lane < len) L[r0] = v0;
+    if (lane + 32 < len) L[r1] = v1;
+}
+
+__global__ void __launch_bounds__(256) k_lists_sort_long(const int* __restrict__ offsets, int N, int B, int A,
+                                                          int* __restrict__ lists, int* __restrict__ scratch,
+                                                          const int* __restrict__ long_queue,
+                                                          const int* __restrict__ long_count, int bitmap_words) {
+    extern __shared__ unsigned s_bits[];  // [bitmap_words]; 0 words: always use the counting fallback
+    __shared__ int s_warp[8];
+    __shared__ int s_total;
+    const int n_long = *long_count;
+    for (int q = blockIdx.x; q < n_long; q += gridDim.x) {
+        const int id = long_queue[q];
+        const int p = id / N, f = id - p * N;
+        const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
+        const int len = end - beg;
+        int* L = lists + (size_t)p * B * A + beg;
+        bool done = false;
+        if (bitmap_words > 0) {
+            for (int i = threadIdx.x; i < bitmap_words; i += blockDim.x) s_bits[i] = 0u;
+            __syncthreads();
+            for (int i = threadIdx.x; i < len; i += blockDim.x) {
+                const int b = L[i];
+                atomicOr(&s_bits[b >> 5], 1u << (b & 31));
+            }
+            __syncthreads();
+            const int per = (bitmap_words + blockDim.x - 1) / blockDim.x;
+            const int w0 = threadIdx.x * per, w1 = min(w0 + per, bitmap_words);
+            int cnt = 0;
+            for (int w = w0; w < w1; ++w) cnt += __popc(s_bits[w]);
+            // block exclusive scan of cnt
+            const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+            int incl = cnt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                int t = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += t;
+            }
+            if (lane == 31) s_warp[wid] = incl;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int run = 0;
+                for (int i = 0; i < 8; ++i) { int t = s_warp[i]; s_warp[i] = run; run += t; }
+                s_total = run;
+            }
+            __syncthreads();
+            if (s_total == len) {
+                int pos = s_warp[wid] + incl - cnt;
+                for (int w = w0; w < w1; ++w) {
+                    unsigned bits = s_bits[w];
+                    while (bits) {
+                        const int bit = __ffs(bits) - 1;
+                        bits &= bits - 1;
+                        L[pos++] = (w << 5) + bit;
+                    }
+                }
+                done = true;
+            }
+            __syncthreads();
+        }
+        if (!done) {
+            int* S = scratch + (size_t)p * B * A + beg;
+            for (int i = threadIdx.x; i < len; i += blockDim.x) S[i] = L[i];
+            __syncthreads();
+            for (int i = threadIdx.x; i < len; i += blockDim.x) {
+                const int v = S[i];
+                int r = 0;
+                for (int j = 0; j < len; ++j) {
+                    const int u = S[j];
+                    r += (u < v) || (u == v && j < i);
+                }
+                L[r] = v;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
+                         int N, int n_persp, int* counts, int* offsets, int* cursor, int* lists) {
+    if (B <= 0) return 0;
+    // counts holds [2][N] histogram cells followed by one counter and a queue of [2*N] long-list ids
+    int* long_count = counts + (size_t)2 * N;
+    int* long_queue = long_count + 1;
+    cudaMemsetAsync(counts, 0, sizeof(int) * ((size_t)2 * N + 1), s);
+    const long long total = (long long)n_persp * B * A;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    k_feat_count<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, counts);
+    k_feat_scan<<<n_persp, 1024, 0, s>>>(counts, N, offsets, cursor);
+    k_feat_fill<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, cursor, lists);
+    int* scratch = lists + (size_t)2 * B * A;  // the list buffer carries a second copy's worth of room
+    const long long warps = (long long)n_persp * N;
+    k_lists_sort_short<<<(int)((warps * 32 + 255) / 256), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count);
+    int words = (B + 31) / 32;
+    if ((size_t)words * 4 > 160 * 1024) words = 0;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(k_lists_sort_long, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        attr_set = true;
+    }
+    k_lists_sort_long<<<148 * 4, 256, (size_t)words * 4, s>>>(offsets, N, B, A, lists, scratch, long_queue, long_count, words);
+    return 5;
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward: one block per feature row, one thread per float4 column.  The row of the gradient is
+// written exactly once per step (stm list first, then nstm list, each in ascending position order —
+// the accumulation order of sparse_ft_backward_cpu called for stm then nstm).
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_ft_backward(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+                                                       const int* __restrict__ offsets, const int* __restrict__ lists,
+                                                       int B, int A, int N, int F, int n_persp, float* __restrict__ grad) {
+    const int f = blockIdx.x;
+    const int c = threadIdx.x;
+    const int row4 = F >> 2;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n_persp; ++p) {
+        const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
+        const int* __restrict__ L = lists + (size_t)p * B * A;
+        const float4* __restrict__ d = reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm);
+        for (int j = beg; j < end; j += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (j + u < end) {
+                    const int b = __ldg(L + j + u);
+                    v[u] = __ldg(d + (size_t)b * row4 + c);
+                } else {
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+            }
+        }
+    }
+    reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
+}
+
+int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
+                       const int* lists, int B, int A, int N, int F, int n_persp, float* grad) {
+    k_ft_backward<<<N, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
+    return 1;
+}
+
+// ft_reduce_virtual_grad (sparse/ft_factorize.rs:109-121): grad[N + v] = sum over king buckets of grad[kb*pi + v]
+__global__ void k_ft_reduce_virtual(float* __restrict__ grad, int N, int pi, int F) {
+    const int row4 = F >> 2;
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)pi * row4) return;
+    const int v = (int)(i / row4), c = (int)(i - (long long)v * row4);
+    const float4* g4 = reinterpret_cast<const float4*>(grad);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int f = v; f < N; f += pi) {
+        const float4 x = g4[(size_t)f * row4 + c];
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    reinterpret_cast<float4*>(grad)[(size_t)(N + v) * row4 + c] = acc;
+}
+
+int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F) {
+    const long long n = (long long)pi * (F / 4);
+    k_ft_reduce_virtual<<<(int)((n + 255) / 256), 256, 0, s>>>(grad, N, pi, F);
+    return 1;
+}
+
+// ft_fold_virtual (sparse/ft_factorize.rs:78-99): comb[f] = w[f] + w[N + f % pi]
+__global__ void k_ft_fold(const float* __restrict__ w, float* __restrict__ comb, int N, int pi, int F) {
+    const int row4 = F >> 2;
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)N * row4) return;
+    const int f = (int)(i / row4), c = (int)(i - (long long)f * row4);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const float4 a = w4[i];
+    const float4 b = w4[(size_t)(N + f % pi) * row4 + c];
+    reinterpret_cast<float4*>(comb)[i] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
+int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F) {
+    const long long n = (long long)N * (F / 4);
+    k_ft_fold<<<(int)((n + 255) / 256), 256, 0, s>>>(w, comb, N, pi, F);
+    return 1;
+}

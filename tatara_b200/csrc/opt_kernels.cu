@@ -1,0 +1,156 @@
+// Optimizer kernels: the RAdam / Ranger / AdamW update with weight clamp (radam_step,
+// native_kernels.cu:1291; pointwise/radam_step.rs:116-156) and the Ranger look-ahead interpolation
+// (native_kernels.cu:1842; pointwise/ranger_step.rs:52-59), fused so that every parameter and moment
+// crosses HBM once per step.  The gradient is only read: every gradient buffer is fully rewritten by
+// the next backward pass, so the reference's grad = 0 store is not needed.
+#include "common.cuh"
+
+static __device__ __forceinline__ float radam_one(float p, float& m, float& v, float g, const OptScalars& sc, float rate,
+                                                   float decay_mul) {
+    p *= decay_mul;
+    const float mi = sc.beta1 * m + (1.0f - sc.beta1) * g;
+    const float vi = sc.beta2 * v + (1.0f - sc.beta2) * g * g;
+    m = mi;
+    v = vi;
+    float val = mi;
+    if (sc.denom != 0) val /= sqrtf(vi) + sc.eps;
+    p -= rate * val;
+    p = p < sc.min_w ? sc.min_w : p;
+    p = p > sc.max_w ? sc.max_w : p;
+    return p;
+}
+
+static __device__ __forceinline__ float4 radam_four(float4 p, float4& m, float4& v, float4 g, const OptScalars& sc,
+                                                     float rate, float decay_mul) {
+    float4 r;
+    r.x = radam_one(p.x, m.x, v.x, g.x, sc, rate, decay_mul);
+    r.y = radam_one(p.y, m.y, v.y, g.y, sc, rate, decay_mul);
+    r.z = radam_one(p.z, m.z, v.z, g.z, sc, rate, decay_mul);
+    r.w = radam_one(p.w, m.w, v.w, g.w, sc, rate, decay_mul);
+    return r;
+}
+
+static __device__ __forceinline__ float4 lerp_four(float4 w, float4 s, float alpha) {
+    const float oma = 1.0f - alpha;
+    return make_float4(alpha * w.x + oma * s.x, alpha * w.y + oma * s.y, alpha * w.z + oma * s.z, alpha * w.w + oma * s.w);
+}
+
+// plain streaming update of one large group (n multiple of 4)
+__global__ void __launch_bounds__(256) k_radam(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v,
+                                                const float4* __restrict__ g, float4* __restrict__ slow, long long n4,
+                                                OptScalars sc) {
+    const float rate = sc.lr * sc.step_size;
+    const float decay_mul = 1.0f - sc.decay * rate;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        float4 mi = m[i], vi = v[i];
+        float4 p = radam_four(w[i], mi, vi, g[i], sc, rate, decay_mul);
+        m[i] = mi;
+        v[i] = vi;
+        if (sc.lerp) {
+            p = lerp_four(p, slow[i], sc.alpha);
+            slow[i] = p;
+        }
+        w[i] = p;
+    }
+}
+
+int launch_radam(cudaStream_t s, float* w, float* m, float* v, const float* g, float* slow, int64_t n, OptScalars sc) {
+    const long long n4 = n / 4;
+    long long blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (blocks < 1) blocks = 1;
+    k_radam<<<(int)blocks, 256, 0, s>>>(reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v),
+                                        reinterpret_cast<const float4*>(g), reinterpret_cast<float4*>(slow), n4, sc);
+    return 1;
+}
+
+// all small groups in one launch: grid (groups, blocks)
+__global__ void __launch_bounds__(256) k_radam_small(const __grid_constant__ SmallGroups groups, OptScalars sc) {
+    const SmallGroup gr = groups.g[blockIdx.x];
+    sc.lr = gr.lr;
+    sc.decay = gr.decay;
+    sc.min_w = gr.min_w;
+    sc.max_w = gr.max_w;
+    const float rate = sc.lr * sc.step_size;
+    const float decay_mul = 1.0f - sc.decay * rate;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < gr.n; i += gridDim.y * blockDim.x) {
+        float mi = gr.m[i], vi = gr.v[i];
+        float p = radam_one(gr.w[i], mi, vi, gr.grad[i], sc, rate, decay_mul);
+        gr.m[i] = mi;
+        gr.v[i] = vi;
+        if (sc.lerp) {
+            p = sc.alpha * p + (1.0f - sc.alpha) * gr.slow[i];
+            gr.slow[i] = p;
+        }
+        gr.w[i] = p;
+    }
+}
+
+int launch_radam_small(cudaStream_t s, const SmallGroups& groups, int max_n, OptScalars sc) {
+    int by = ceil_div(max_n, 256 * 4);
+    if (by < 1) by = 1;
+    if (by > 512) by = 512;
+    k_radam_small<<<dim3(groups.n, by), 256, 0, s>>>(groups, sc);
+    return 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Factorised FT table (N = KB * pi real rows + pi virtual rows).  One block per virtual row v, one
+// thread per float4 column:
+//   pass 1: update the KB real rows kb*pi + v and add up their gradients in kb order
+//           (ft_reduce_virtual_grad, sparse/ft_factorize.rs:109-121),
+//   then update the virtual row N + v with that sum (and store the sum as its gradient),
+//   pass 2: comb[kb*pi + v] = w[kb*pi + v] + w[N + v] (ft_fold_virtual, sparse/ft_factorize.rs:78-99);
+//           the real rows were written a moment ago by this block and are read back from L2.
+// Replaces radam_step on N_t*F elements + ft_reduce_virtual_grad + ranger_lookahead_lerp + ft_fold_virtual.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_radam_factorized(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v,
+                                                            float4* __restrict__ g, float4* __restrict__ slow,
+                                                            float4* __restrict__ comb, int N, int pi, int row4, OptScalars sc) {
+    const int vr = blockIdx.x;
+    const int c = threadIdx.x;
+    const float rate = sc.lr * sc.step_size;
+    const float decay_mul = 1.0f - sc.decay * rate;
+    const int KB = N / pi;
+    float4 gsum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int kb = 0; kb < KB; ++kb) {
+        const size_t i = (size_t)(kb * pi + vr) * row4 + c;
+        const float4 gi = g[i];
+        float4 mi = m[i], vi = v[i];
+        float4 p = radam_four(w[i], mi, vi, gi, sc, rate, decay_mul);
+        m[i] = mi;
+        v[i] = vi;
+        if (sc.lerp) {
+            p = lerp_four(p, slow[i], sc.alpha);
+            slow[i] = p;
+        }
+        w[i] = p;
+        gsum.x += gi.x; gsum.y += gi.y; gsum.z += gi.z; gsum.w += gi.w;
+    }
+    const size_t iv = (size_t)(N + vr) * row4 + c;
+    g[iv] = gsum;
+    float4 mv = m[iv], vv = v[iv];
+    float4 pv = radam_four(w[iv], mv, vv, gsum, sc, rate, decay_mul);
+    m[iv] = mv;
+    v[iv] = vv;
+    if (sc.lerp) {
+        pv = lerp_four(pv, slow[iv], sc.alpha);
+        slow[iv] = pv;
+    }
+    w[iv] = pv;
+#pragma unroll 4
+    for (int kb = 0; kb < KB; ++kb) {
+        const size_t i = (size_t)(kb * pi + vr) * row4 + c;
+        const float4 p = w[i];
+        comb[i] = make_float4(p.x + pv.x, p.y + pv.y, p.z + pv.z, p.w + pv.w);
+    }
+}
+
+int launch_radam_factorized(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb, int N,
+                            int pi, int F, OptScalars sc) {
+    k_radam_factorized<<<pi, F / 4, 0, s>>>(reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m),
+                                            reinterpret_cast<float4*>(v), reinterpret_cast<float4*>(g),
+                                            reinterpret_cast<float4*>(slow), reinterpret_cast<float4*>(comb), N, pi, F / 4, sc);
+    return 1;
+}

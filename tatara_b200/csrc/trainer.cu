@@ -1,0 +1,1036 @@
+// The trainer behind the C ABI: owns the parameter groups, the workspace, the input and loss rings and
+// drives one training step as a fixed sequence of kernels on one compute stream (inputs arrive on a
+// copy stream).  Mirrors GpuTrainer (bins/nnue_train/src/trainer_layerstack.rs) and SimpleGpuTrainer
+// (bins/nnue_train/src/trainer_simple.rs) at the level of the TrainerBackend trait.
+#include "common.cuh"
+#include "../../include/tatara_b200.h"
+
+#include <dlfcn.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
+#define CLAMP_Q (127.0f / 64.0f)         // arch.rs:138-143: i8::MAX / QB
+#define CLAMP_NONE 3.402823466e+38f      // arch.rs:145-148: f32::MAX sentinel
+#define BETA2 0.999f                     // crates/nnue-train/src/optimizer.rs:122-130 RangerParams::DEFAULT
+#define EPS 1e-8f
+#define RANGER_ALPHA 0.5f
+#define RANGER_K 6
+#define N_SMA_THRESHOLD 5.0f
+#define DGRAD_CTAS (148 * 2)
+
+namespace {
+
+thread_local std::string g_create_error;
+
+// ---- NCCL through dlopen: the library has no link-time dependency on it -----------------------------
+struct Uid { char internal[128]; };  // ncclUniqueId
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, Uid, int) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+};
+NcclApi g_nccl;
+
+bool load_nccl(std::string* err) {
+    if (g_nccl.lib) return true;
+    const char* names[] = {getenv("TATARA_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+        if (!n || !*n) continue;
+        g_nccl.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (g_nccl.lib) break;
+    }
+    if (!g_nccl.lib) { *err = "cannot load libnccl.so.2 (set TATARA_NCCL_LIB to its path)"; return false; }
+#define SYM(field, name) *(void**)(&g_nccl.field) = dlsym(g_nccl.lib, name); if (!g_nccl.field) { *err = std::string("missing symbol ") + name; g_nccl.lib = nullptr; return false; }
+    SYM(GetUniqueId, "ncclGetUniqueId")
+    SYM(CommInitRank, "ncclCommInitRank")
+    SYM(AllReduce, "ncclAllReduce")
+    SYM(CommDestroy, "ncclCommDestroy")
+    SYM(GetErrorString, "ncclGetErrorString")
+    SYM(GroupStart, "ncclGroupStart")
+    SYM(GroupEnd, "ncclGroupEnd")
+#undef SYM
+    return true;
+}
+
+struct Group {
+    std::string name;
+    int kind;  // 0 ft, 1 dense, 2 bias
+    float clamp;
+    int64_t len;
+    float *w = nullptr, *m = nullptr, *v = nullptr, *slow = nullptr, *grad = nullptr;
+};
+
+struct DevBatch {
+    int *stm = nullptr, *nstm = nullptr, *nnz = nullptr, *bucket = nullptr;
+    float *score = nullptr, *wdl = nullptr;
+    int n_pos = 0;
+    float norm = 0.f;
+};
+
+struct HostStage {
+    int *stm = nullptr, *nstm = nullptr, *nnz = nullptr, *bucket = nullptr;
+    float *score = nullptr, *wdl = nullptr;
+};
+
+enum Phase {
+    PH_SORT = 0, PH_FT_FWD, PH_L1_FWD, PH_TAIL, PH_SMALL_WGRAD, PH_L1_WGRAD, PH_L1_DGRAD, PH_INV_INDEX, PH_FT_BWD,
+    PH_ALLREDUCE, PH_OPT_FT, PH_OPT_SMALL, PH_COUNT
+};
+const char* const kPhaseNames[PH_COUNT] = {"bucket_sort", "ft_forward", "l1_forward", "tail", "small_wgrad", "l1_wgrad",
+                                           "l1_dgrad_ftgrad", "inverse_index", "ft_backward", "allreduce", "opt_ft",
+                                           "opt_small"};
+
+}  // namespace
+
+struct tb_trainer {
+    tb_config cfg;
+    std::string err;
+    cudaStream_t stream = nullptr, copy_stream = nullptr;
+    std::vector<Group> groups;
+    float* grad_arena = nullptr;
+    int64_t arena_len = 0, arena_reduce_len = 0;
+    float* comb = nullptr;
+    int Nt = 0, l1e = 0, l2in = 0, K = 0, max_tiles = 0, max_units = 0;
+    uint64_t step_count = 0;
+    // inputs
+    DevBatch ring[2], slots[TB_NUM_SLOTS];
+    HostStage stage[2];
+    cudaEvent_t ev_upload[2] = {nullptr, nullptr}, ev_consumed[2] = {nullptr, nullptr};
+    bool upload_pending[2] = {false, false}, consumed_pending[2] = {false, false};
+    uint64_t ring_step = 0;
+    // workspace
+    float *pre[2] = {nullptr, nullptr}, *dft[2] = {nullptr, nullptr}, *combined = nullptr;
+    float *l1_out = nullptr, *dl1 = nullptr, *net_output = nullptr, *dy = nullptr;
+    float *tail_a = nullptr, *tail_b = nullptr, *tail_c = nullptr;  // LS: l2_input, dl2_out, l2_acted; Simple: l1_acted, dl2_pre, l2_acted
+    double *loss_partials = nullptr, *loss_acc = nullptr;
+    int *order = nullptr, *n_tiles = nullptr, *seg_start = nullptr;
+    TileDesc* tiles = nullptr;
+    float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr;
+    int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
+    int last_n = 0;
+    // loss ring (AsyncLossRing, trainer_common.rs:909-1000)
+    double* loss_pinned[2] = {nullptr, nullptr};
+    cudaEvent_t ev_loss[2] = {nullptr, nullptr};
+    uint64_t loss_step = 0;
+    bool loss_primed = false;
+    // timing
+    cudaEvent_t ev_t0 = nullptr, ev_t1 = nullptr;
+    bool profile = false;
+    cudaEvent_t ph_start[PH_COUNT], ph_stop[PH_COUNT];
+    bool ph_used[PH_COUNT];
+    double ph_ms[PH_COUNT];
+    int64_t ph_launches[PH_COUNT];
+    int64_t launches = 0;
+    // data parallel
+    void* comm = nullptr;
+};
+
+namespace {
+
+int fail(tb_trainer* t, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (t) t->err = buf; else g_create_error = buf;
+    return code;
+}
+
+#define CU(t, call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return fail(t, e_ == cudaErrorMemoryAllocation ? TB_ERR_OUT_OF_MEMORY : TB_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); } while (0)
+
+template <typename T>
+cudaError_t dalloc(T** p, size_t n) {
+    cudaError_t e = cudaMalloc((void**)p, (n ? n : 1) * sizeof(T));
+    if (e == cudaSuccess) e = cudaMemset(*p, 0, (n ? n : 1) * sizeof(T));
+    return e;
+}
+
+Group* find_group(tb_trainer* t, const char* name) {
+    if (!name) return nullptr;
+    for (auto& g : t->groups)
+        if (g.name == name) return &g;
+    return nullptr;
+}
+
+// radam_compute_step_size_denom (pointwise/radam_step.rs:63-86) and OptimizerKind::step_size_denom
+// (crates/nnue-train/src/optimizer.rs:63-93)
+void optimizer_scalars(int kind, uint64_t step, float* step_size, int* denom, float* beta1) {
+    const float b1 = kind == TB_OPT_RANGER ? 0.99f : 0.9f;
+    *beta1 = b1;
+    if (kind == TB_OPT_ADAMW) { *step_size = 1.0f; *denom = 1; return; }
+    const float step_f = (float)step;
+    const float beta2_t = powf(BETA2, step_f);
+    const float n_sma_max = 2.0f / (1.0f - BETA2) - 1.0f;
+    const float n_sma = n_sma_max - 2.0f * step_f * beta2_t / (1.0f - beta2_t);
+    const float bc1 = 1.0f - powf(b1, step_f);
+    if (n_sma > N_SMA_THRESHOLD) {
+        const float p1 = (n_sma - 4.0f) / (n_sma_max - 4.0f);
+        const float p2 = (n_sma - 2.0f) / n_sma;
+        const float p3 = n_sma_max / (n_sma_max - 2.0f);
+        *step_size = sqrtf((1.0f - beta2_t) * p1 * p2 * p3) / bc1;
+    } else {
+        *step_size = 1.0f / bc1;
+    }
+    *denom = n_sma > N_SMA_THRESHOLD ? 1 : 0;
+}
+
+struct PhaseScope {
+    tb_trainer* t;
+    int ph;
+    PhaseScope(tb_trainer* t_, int ph_) : t(t_), ph(ph_) {
+        if (t->profile) { cudaEventRecord(t->ph_start[ph], t->stream); }
+    }
+    void done(int launches) {
+        t->launches += launches;
+        if (t->profile) {
+            cudaEventRecord(t->ph_stop[ph], t->stream);
+            t->ph_used[ph] = true;
+            t->ph_launches[ph] += launches;
+        }
+    }
+};
+
+void profile_collect(tb_trainer* t) {
+    if (!t->profile) return;
+    cudaStreamSynchronize(t->stream);
+    for (int i = 0; i < PH_COUNT; ++i)
+        if (t->ph_used[i]) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, t->ph_start[i], t->ph_stop[i]) == cudaSuccess) t->ph_ms[i] += ms;
+            t->ph_used[i] = false;
+        }
+}
+
+int check_batch(tb_trainer* t, const tb_batch* b) {
+    if (!b) return fail(t, TB_ERR_INVALID_ARGUMENT, "batch is NULL");
+    if (b->n_pos < 0) return fail(t, TB_ERR_INVALID_ARGUMENT, "batch.n_pos is negative (%d)", b->n_pos);
+    if (b->n_pos == 0) return TB_OK;
+    // trainer_layerstack.rs:79-89
+    if (b->n_pos % 16 != 0)
+        return fail(t, TB_ERR_INVALID_ARGUMENT, "batch.n_pos must be a multiple of 16 (got %d)", b->n_pos);
+    // trainer_layerstack.rs:608-621
+    if (b->n_pos > t->cfg.batch_capacity)
+        return fail(t, TB_ERR_INVALID_ARGUMENT,
+                    "batch %d exceeds workspace capacity %d (the workspace is allocated once at creation)", b->n_pos,
+                    t->cfg.batch_capacity);
+    if (!b->stm_indices || !b->nstm_indices || !b->nnz || !b->score || !b->wdl)
+        return fail(t, TB_ERR_INVALID_ARGUMENT, "batch has a NULL input array");
+    if (t->cfg.arch == TB_ARCH_LAYERSTACK && !b->bucket_idx)
+        return fail(t, TB_ERR_INVALID_ARGUMENT, "LayerStack needs batch.bucket_idx");
+    return TB_OK;
+}
+
+bool is_pinned(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeHost;
+}
+
+// Copies one host batch into a device batch on `cs`.  Pinned caller memory is copied directly; pageable
+// memory goes through the library's pinned staging buffers first.
+int upload_batch(tb_trainer* t, const tb_batch* b, DevBatch* d, HostStage* st, cudaStream_t cs) {
+    const size_t n = (size_t)b->n_pos, A = (size_t)t->cfg.max_active;
+    const bool ls = t->cfg.arch == TB_ARCH_LAYERSTACK;
+    struct Item { void* dst; const void* src; void* stage; size_t bytes; } items[6] = {
+        {d->stm, b->stm_indices, st ? st->stm : nullptr, n * A * 4}, {d->nstm, b->nstm_indices, st ? st->nstm : nullptr, n * A * 4},
+        {d->nnz, b->nnz, st ? st->nnz : nullptr, n * 4},             {d->bucket, b->bucket_idx, st ? st->bucket : nullptr, n * 4},
+        {d->score, b->score, st ? st->score : nullptr, n * 4},       {d->wdl, b->wdl, st ? st->wdl : nullptr, n * 4}};
+    for (int i = 0; i < 6; ++i) {
+        if (i == 3 && !ls) continue;
+        const void* src = items[i].src;
+        if (items[i].stage && !is_pinned(src)) {
+            memcpy(items[i].stage, src, items[i].bytes);
+            src = items[i].stage;
+        }
+        CU(t, cudaMemcpyAsync(items[i].dst, src, items[i].bytes, cudaMemcpyHostToDevice, cs));
+    }
+    d->n_pos = b->n_pos;
+    d->norm = b->per_pos_norm != 0.f ? b->per_pos_norm : 1.0f / ((float)b->n_pos * (float)t->cfg.world_size);
+    return TB_OK;
+}
+
+LossParams make_loss(const tb_loss* l, float lambda, float norm) {
+    LossParams p;
+    p.kind = l->kind;
+    p.scale = l->scale;
+    p.nnue2score = l->nnue2score;
+    p.in_scaling = l->in_scaling;
+    p.in_offset = l->in_offset;
+    p.target_offset = l->target_offset;
+    p.target_scaling = l->target_scaling;
+    p.lambda = lambda;
+    p.norm = norm;
+    return p;
+}
+
+int check_loss(tb_trainer* t, const tb_loss* l) {
+    if (!l) return fail(t, TB_ERR_INVALID_ARGUMENT, "loss is NULL");
+    if (l->kind == TB_LOSS_SIGMOID) {
+        if (!(l->scale > 0.f) || !isfinite(l->scale))
+            return fail(t, TB_ERR_INVALID_ARGUMENT, "loss scale must be finite and > 0 (got %g)", l->scale);
+        return TB_OK;
+    }
+    if (l->kind != TB_LOSS_WRM) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown loss kind %d", l->kind);
+    if (!(l->nnue2score > 0.f) || !(l->in_scaling > 0.f) || !(l->target_scaling > 0.f))
+        return fail(t, TB_ERR_INVALID_ARGUMENT, "wrm nnue2score / in_scaling / target_scaling must be > 0");
+    // LossKind::wrm_extended (crates/nnue-train/src/trainer.rs:127-137)
+    if (l->pow_exp != 2.0f || l->qp_asymmetry != 0.0f || l->weight_boost_w1 != 0.0f)
+        return fail(t, TB_ERR_UNSUPPORTED, "the extended WRM loss (pow_exp / qp_asymmetry / weight boost) is not implemented");
+    return TB_OK;
+}
+
+// ---- the step ------------------------------------------------------------------------------------------
+int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lambda, int backward) {
+    const tb_config& c = t->cfg;
+    const int B = d.n_pos, F = c.ft_out, N = c.ft_in, A = c.max_active;
+    const bool ls = c.arch == TB_ARCH_LAYERSTACK;
+    const float* table = c.ft_factorize ? t->comb : t->groups[0].w;
+    t->last_n = B;
+    { PhaseScope p(t, PH_SORT);
+      p.done(launch_bucket_sort(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
+                                t->seg_start, t->max_tiles)); }
+    { PhaseScope p(t, PH_FT_FWD);
+      const int mode = ls ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
+      p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1], t->combined,
+                               B, F, N, A, FT_POST_SCALE, 2)); }
+    const LossParams lp = make_loss(loss, lambda, d.norm);
+    if (ls) {
+        { PhaseScope p(t, PH_L1_FWD);
+          p.done(launch_l1_forward(t->stream, t->combined, F, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
+                                   t->groups[3].w, t->groups[4].w, t->groups[5].w, t->l1_out, c.l1_out, c.num_buckets)); }
+        { PhaseScope p(t, PH_TAIL);
+          p.done(launch_tail_layerstack(t->stream, t->l1_out, d.bucket, d.score, d.wdl, t->groups[6].w, t->groups[7].w,
+                                        t->groups[8].w, t->groups[9].w, lp, B, c.l1_out, c.l2_out, c.num_buckets,
+                                        t->net_output, t->dy, t->dl1, t->tail_a, t->tail_b, t->tail_c, t->loss_partials,
+                                        t->loss_acc, backward)); }
+    } else {
+        { PhaseScope p(t, PH_L1_FWD);
+          p.done(launch_l1_forward(t->stream, t->combined, 2 * F, t->order, t->tiles, t->n_tiles, t->max_tiles, nullptr, nullptr,
+                                   t->groups[2].w, t->groups[3].w, t->l1_out, c.l1_out, 0)); }
+        { PhaseScope p(t, PH_TAIL);
+          p.done(launch_tail_simple(t->stream, t->l1_out, d.score, d.wdl, t->groups[4].w, t->groups[5].w, t->groups[6].w,
+                                    t->groups[7].w, lp, c.activation, B, c.l1_out, c.l2_out, t->net_output, t->dy, t->dl1,
+                                    t->tail_a, t->tail_b, t->tail_c, t->loss_partials, t->loss_acc, backward)); }
+    }
+    return TB_OK;
+}
+
+int run_backward(tb_trainer* t, const DevBatch& d) {
+    const tb_config& c = t->cfg;
+    const int B = d.n_pos, F = c.ft_out, N = c.ft_in, A = c.max_active;
+    const bool ls = c.arch == TB_ARCH_LAYERSTACK;
+    if (ls) {
+        { PhaseScope p(t, PH_SMALL_WGRAD);
+          p.done(launch_small_wgrad_layerstack(t->stream, t->order, t->seg_start, B, c.l1_out, c.l2_out, c.num_buckets, t->tail_a,
+                                               t->tail_b, t->tail_c, t->dy, t->dl1, t->small_partials, t->groups[6].grad,
+                                               t->groups[7].grad, t->groups[8].grad, t->groups[9].grad, t->groups[3].grad,
+                                               t->groups[5].grad)); }
+        { PhaseScope p(t, PH_L1_WGRAD);
+          p.done(launch_l1_wgrad(t->stream, t->combined, F, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, c.l1_out,
+                                 c.num_buckets, t->l1w_partials, t->groups[2].grad, t->groups[4].grad)); }
+        { PhaseScope p(t, PH_L1_DGRAD);
+          p.done(launch_l1_dgrad_ftgrad(t->stream, 1, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
+                                        t->groups[4].w, t->pre[0], t->pre[1], t->groups[1].w, FT_POST_SCALE, B, F, c.l1_out,
+                                        c.num_buckets, t->dft[0], t->dft[1], t->bias_partials, t->groups[1].grad, DGRAD_CTAS)); }
+    } else {
+        { PhaseScope p(t, PH_SMALL_WGRAD);
+          p.done(launch_small_wgrad_simple(t->stream, t->order, t->seg_start, B, c.l1_out, c.l2_out, t->tail_a, t->tail_b,
+                                           t->tail_c, t->dy, t->dl1, t->small_partials, t->groups[4].grad, t->groups[5].grad,
+                                           t->groups[6].grad, t->groups[7].grad, t->groups[3].grad)); }
+        { PhaseScope p(t, PH_L1_WGRAD);
+          p.done(launch_l1_wgrad(t->stream, t->combined, 2 * F, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, c.l1_out, 0,
+                                 t->l1w_partials, nullptr, t->groups[2].grad)); }
+        { PhaseScope p(t, PH_L1_DGRAD);
+          p.done(launch_l1_dgrad_ftgrad(t->stream, c.activation == TB_ACT_CRELU ? 2 : 3, t->dl1, t->order, t->tiles, t->n_tiles,
+                                        t->max_tiles, nullptr, t->groups[2].w, t->pre[0], t->pre[1], t->groups[1].w,
+                                        FT_POST_SCALE, B, F, c.l1_out, 0, t->dft[0], t->dft[1], t->bias_partials,
+                                        t->groups[1].grad, DGRAD_CTAS)); }
+    }
+    { PhaseScope p(t, PH_INV_INDEX);
+      p.done(launch_inverse_index(t->stream, d.stm, d.nstm, d.nnz, B, A, N, 2, t->feat_counts, t->feat_offsets, t->feat_cursor,
+                                  t->feat_lists)); }
+    { PhaseScope p(t, PH_FT_BWD);
+      p.done(launch_ft_backward(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->groups[0].grad)); }
+    return TB_OK;
+}
+
+// sum of the gradient arena (and of the loss) over the data-parallel ranks
+int run_allreduce(tb_trainer* t) {
+    if (t->cfg.world_size <= 1) return TB_OK;
+    PhaseScope p(t, PH_ALLREDUCE);
+    int rc = g_nccl.GroupStart();
+    if (rc == 0) rc = g_nccl.AllReduce(t->grad_arena, t->grad_arena, (size_t)t->arena_reduce_len, /*ncclFloat*/ 7, /*ncclSum*/ 0, t->comm, t->stream);
+    if (rc == 0) rc = g_nccl.AllReduce(t->loss_acc, t->loss_acc, 1, /*ncclDouble*/ 8, 0, t->comm, t->stream);
+    const int rc2 = g_nccl.GroupEnd();
+    if (rc == 0) rc = rc2;
+    p.done(2);
+    if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString(rc));
+    return TB_OK;
+}
+
+int run_optimizer(tb_trainer* t, float lr) {
+    const tb_config& c = t->cfg;
+    const bool ls = c.arch == TB_ARCH_LAYERSTACK;
+    // step_count increments before the scalars are computed (trainer_layerstack.rs:4078-4081)
+    t->step_count += 1;
+    OptScalars sc;
+    optimizer_scalars(c.optimizer, t->step_count, &sc.step_size, &sc.denom, &sc.beta1);
+    sc.beta2 = BETA2;
+    sc.eps = EPS;
+    sc.alpha = RANGER_ALPHA;
+    sc.lerp = (c.optimizer == TB_OPT_RANGER && t->step_count % RANGER_K == 0) ? 1 : 0;
+    const float wd[3] = {c.wd_ft, ls ? c.wd_dense : c.wd_ft, ls ? c.wd_bias : c.wd_ft};
+    const float lm[3] = {c.lr_mult_ft, ls ? c.lr_mult_dense : c.lr_mult_ft, ls ? c.lr_mult_bias : c.lr_mult_ft};
+    {
+        PhaseScope p(t, PH_OPT_FT);
+        Group& g = t->groups[0];
+        sc.lr = lr * lm[0];
+        sc.decay = wd[0];
+        sc.min_w = -g.clamp;
+        sc.max_w = g.clamp;
+        if (c.ft_factorize)
+            p.done(launch_radam_factorized(t->stream, g.w, g.m, g.v, g.grad, g.slow, t->comb, c.ft_in, c.piece_inputs, c.ft_out, sc));
+        else
+            p.done(launch_radam(t->stream, g.w, g.m, g.v, g.grad, g.slow, g.len, sc));
+    }
+    {
+        PhaseScope p(t, PH_OPT_SMALL);
+        SmallGroups sg;
+        sg.n = 0;
+        int max_n = 0;
+        for (size_t i = 1; i < t->groups.size(); ++i) {
+            Group& g = t->groups[i];
+            SmallGroup& s = sg.g[sg.n++];
+            s.w = g.w; s.m = g.m; s.v = g.v; s.slow = g.slow; s.grad = g.grad;
+            s.n = (int)g.len;
+            s.lr = lr * lm[g.kind];
+            s.decay = wd[g.kind];
+            s.min_w = -g.clamp;
+            s.max_w = g.clamp;
+            if (s.n > max_n) max_n = s.n;
+        }
+        p.done(launch_radam_small(t->stream, sg, max_n, sc));
+    }
+    return TB_OK;
+}
+
+// queues the read-back of this step's loss and returns the previous one (AsyncLossRing::read_and_queue_next)
+int loss_ring_next(tb_trainer* t, double* out) {
+    const int cur = (int)(t->loss_step % 2);
+    CU(t, cudaMemcpyAsync(t->loss_pinned[cur], t->loss_acc, sizeof(double), cudaMemcpyDeviceToHost, t->stream));
+    CU(t, cudaEventRecord(t->ev_loss[cur], t->stream));
+    double returned = 0.0;
+    if (t->loss_primed) {
+        const int prev = (int)((t->loss_step + 1) % 2);
+        CU(t, cudaEventSynchronize(t->ev_loss[prev]));
+        returned = *t->loss_pinned[prev];
+    } else {
+        t->loss_primed = true;
+    }
+    t->loss_step += 1;
+    if (out) *out = returned;
+    return TB_OK;
+}
+
+int step_on(tb_trainer* t, const DevBatch& d, float lr, float lambda, const tb_loss* loss, double* loss_prev) {
+    int rc = run_forward(t, d, loss, lambda, 1);
+    if (rc == TB_OK) rc = run_backward(t, d);
+    if (rc == TB_OK) rc = run_allreduce(t);
+    if (rc == TB_OK) rc = run_optimizer(t, lr);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaGetLastError());
+    rc = loss_ring_next(t, loss_prev);
+    profile_collect(t);
+    return rc;
+}
+
+// uploads into ring slot `s` on the copy stream and makes the compute stream wait for it
+int ring_upload(tb_trainer* t, const tb_batch* b, int* slot_out) {
+    const int s = (int)(t->ring_step % 2);
+    // the previous upload from this staging slot must have left the host buffers
+    if (t->upload_pending[s]) { CU(t, cudaEventSynchronize(t->ev_upload[s])); t->upload_pending[s] = false; }
+    // the compute that read this device slot two steps ago must be done before it is overwritten
+    if (t->consumed_pending[s]) { CU(t, cudaStreamWaitEvent(t->copy_stream, t->ev_consumed[s], 0)); }
+    int rc = upload_batch(t, b, &t->ring[s], &t->stage[s], t->copy_stream);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaEventRecord(t->ev_upload[s], t->copy_stream));
+    t->upload_pending[s] = true;
+    CU(t, cudaStreamWaitEvent(t->stream, t->ev_upload[s], 0));
+    // a caller-owned pinned buffer of the OTHER slot may be reused by the caller once this call returns
+    const int o = s ^ 1;
+    if (t->upload_pending[o]) { CU(t, cudaEventSynchronize(t->ev_upload[o])); t->upload_pending[o] = false; }
+    t->ring_step += 1;
+    *slot_out = s;
+    return TB_OK;
+}
+
+void free_all(tb_trainer* t) {
+    if (!t) return;
+    if (t->stream) cudaStreamSynchronize(t->stream);
+    if (t->copy_stream) cudaStreamSynchronize(t->copy_stream);
+    if (t->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(t->comm);
+    for (auto& g : t->groups) { cudaFree(g.w); cudaFree(g.m); cudaFree(g.v); cudaFree(g.slow); }
+    cudaFree(t->grad_arena);
+    cudaFree(t->comb);
+    auto free_batch = [](DevBatch& d) { cudaFree(d.stm); cudaFree(d.nstm); cudaFree(d.nnz); cudaFree(d.bucket); cudaFree(d.score); cudaFree(d.wdl); };
+    for (auto& d : t->ring) free_batch(d);
+    for (auto& d : t->slots) free_batch(d);
+    for (auto& s : t->stage) { cudaFreeHost(s.stm); cudaFreeHost(s.nstm); cudaFreeHost(s.nnz); cudaFreeHost(s.bucket); cudaFreeHost(s.score); cudaFreeHost(s.wdl); }
+    for (int i = 0; i < 2; ++i) {
+        cudaFree(t->pre[i]); cudaFree(t->dft[i]);
+        if (t->ev_upload[i]) cudaEventDestroy(t->ev_upload[i]);
+        if (t->ev_consumed[i]) cudaEventDestroy(t->ev_consumed[i]);
+        if (t->ev_loss[i]) cudaEventDestroy(t->ev_loss[i]);
+        cudaFreeHost(t->loss_pinned[i]);
+    }
+    cudaFree(t->combined); cudaFree(t->l1_out); cudaFree(t->dl1); cudaFree(t->net_output); cudaFree(t->dy);
+    cudaFree(t->tail_a); cudaFree(t->tail_b); cudaFree(t->tail_c); cudaFree(t->loss_partials); cudaFree(t->loss_acc);
+    cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
+    cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials);
+    cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
+    if (t->ev_t0) cudaEventDestroy(t->ev_t0);
+    if (t->ev_t1) cudaEventDestroy(t->ev_t1);
+    for (int i = 0; i < PH_COUNT; ++i) {
+        if (t->ph_start[i]) cudaEventDestroy(t->ph_start[i]);
+        if (t->ph_stop[i]) cudaEventDestroy(t->ph_stop[i]);
+    }
+    if (t->copy_stream) cudaStreamDestroy(t->copy_stream);
+    if (t->stream) cudaStreamDestroy(t->stream);
+    delete t;
+}
+
+int alloc_batch(tb_trainer* t, DevBatch* d) {
+    const size_t B = (size_t)t->cfg.batch_capacity, A = (size_t)t->cfg.max_active;
+    CU(t, dalloc(&d->stm, B * A)); CU(t, dalloc(&d->nstm, B * A)); CU(t, dalloc(&d->nnz, B)); CU(t, dalloc(&d->bucket, B));
+    CU(t, dalloc(&d->score, B)); CU(t, dalloc(&d->wdl, B));
+    return TB_OK;
+}
+
+int create_impl(tb_trainer* t) {
+    const tb_config& c = t->cfg;
+    CU(t, cudaSetDevice(c.device));
+    CU(t, cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking));
+    CU(t, cudaStreamCreateWithFlags(&t->copy_stream, cudaStreamNonBlocking));
+    const bool ls = c.arch == TB_ARCH_LAYERSTACK;
+    const int64_t N = c.ft_in, F = c.ft_out, l1 = c.l1_out, l2 = c.l2_out, nb = c.num_buckets;
+    t->Nt = c.ft_in + (c.ft_factorize ? c.piece_inputs : 0);
+    t->l1e = c.l1_out - 1;
+    t->l2in = 2 * t->l1e;
+    t->K = ls ? c.ft_out : 2 * c.ft_out;
+    auto add = [&](const char* name, int kind, float clamp, int64_t len) {
+        Group g; g.name = name; g.kind = kind; g.clamp = clamp; g.len = len; t->groups.push_back(g);
+    };
+    // group tables: trainer_layerstack.rs:740-762, trainer_simple.rs:2497-2578
+    add("ft_w", 0, CLAMP_NONE, (int64_t)t->Nt * F);
+    add("ft_b", 2, CLAMP_NONE, F);
+    if (ls) {
+        add("l1_w", 1, CLAMP_Q, nb * l1 * F);
+        add("l1_b", 2, CLAMP_Q, nb * l1);
+        add("l1_shared_weight", 1, CLAMP_Q, F * l1);
+        add("l1_shared_bias", 2, CLAMP_Q, l1);
+        add("l2_w", 1, CLAMP_Q, nb * l2 * t->l2in);
+        add("l2_b", 2, CLAMP_Q, nb * l2);
+        add("l3_w", 1, CLAMP_Q, nb * l2);
+        add("l3_b", 2, CLAMP_NONE, nb);
+    } else {
+        add("l1_w", 1, CLAMP_Q, 2 * F * l1);
+        add("l1_b", 2, CLAMP_Q, l1);
+        add("l2_w", 1, CLAMP_Q, l1 * l2);
+        add("l2_b", 2, CLAMP_Q, l2);
+        add("l3_w", 1, CLAMP_Q, l2);
+        add("l3_b", 2, CLAMP_NONE, 1);
+    }
+    // gradient arena: small groups first, then the real FT rows, then the virtual FT rows (which are derived
+    // from the real rows after the all-reduce and therefore stay out of it)
+    int64_t off = 0;
+    std::vector<int64_t> goff(t->groups.size());
+    for (size_t i = 1; i < t->groups.size(); ++i) { goff[i] = off; off += (t->groups[i].len + 3) / 4 * 4; }
+    goff[0] = off;
+    t->arena_reduce_len = off + N * F;
+    t->arena_len = off + t->groups[0].len;
+    CU(t, dalloc(&t->grad_arena, (size_t)t->arena_len));
+    for (size_t i = 0; i < t->groups.size(); ++i) {
+        Group& g = t->groups[i];
+        g.grad = t->grad_arena + goff[i];
+        CU(t, dalloc(&g.w, (size_t)g.len)); CU(t, dalloc(&g.m, (size_t)g.len)); CU(t, dalloc(&g.v, (size_t)g.len));
+        CU(t, dalloc(&g.slow, (size_t)(c.optimizer == TB_OPT_RANGER ? g.len : 1)));
+    }
+    if (c.ft_factorize) CU(t, dalloc(&t->comb, (size_t)(N * F)));
+
+    const size_t B = (size_t)c.batch_capacity, A = (size_t)c.max_active;
+    for (auto& d : t->ring) { int rc = alloc_batch(t, &d); if (rc) return rc; }
+    for (auto& d : t->slots) { int rc = alloc_batch(t, &d); if (rc) return rc; }
+    for (auto& s : t->stage) {
+        CU(t, cudaHostAlloc((void**)&s.stm, B * A * 4, cudaHostAllocDefault)); CU(t, cudaHostAlloc((void**)&s.nstm, B * A * 4, cudaHostAllocDefault));
+        CU(t, cudaHostAlloc((void**)&s.nnz, B * 4, cudaHostAllocDefault)); CU(t, cudaHostAlloc((void**)&s.bucket, B * 4, cudaHostAllocDefault));
+        CU(t, cudaHostAlloc((void**)&s.score, B * 4, cudaHostAllocDefault)); CU(t, cudaHostAlloc((void**)&s.wdl, B * 4, cudaHostAllocDefault));
+    }
+    for (int i = 0; i < 2; ++i) {
+        CU(t, cudaEventCreateWithFlags(&t->ev_upload[i], cudaEventDisableTiming));
+        CU(t, cudaEventCreateWithFlags(&t->ev_consumed[i], cudaEventDisableTiming));
+        CU(t, cudaEventCreateWithFlags(&t->ev_loss[i], cudaEventDisableTiming));
+        CU(t, cudaHostAlloc((void**)&t->loss_pinned[i], sizeof(double), cudaHostAllocDefault));
+        *t->loss_pinned[i] = 0.0;
+        CU(t, dalloc(&t->pre[i], B * F));
+        CU(t, dalloc(&t->dft[i], B * F));
+    }
+    CU(t, dalloc(&t->combined, B * (size_t)t->K));
+    CU(t, dalloc(&t->l1_out, B * l1)); CU(t, dalloc(&t->dl1, B * l1));
+    CU(t, dalloc(&t->net_output, B)); CU(t, dalloc(&t->dy, B));
+    CU(t, dalloc(&t->tail_a, B * (size_t)(ls ? t->l2in : l1)));
+    CU(t, dalloc(&t->tail_b, B * l2)); CU(t, dalloc(&t->tail_c, B * l2));
+    CU(t, dalloc(&t->loss_partials, B / 128 + 2)); CU(t, dalloc(&t->loss_acc, 1));
+    t->max_tiles = (int)(B / TB_TILE_M) + TB_MAX_BUCKETS + 2;
+    t->max_units = t->max_tiles / 16 + TB_MAX_BUCKETS + 2;
+    CU(t, dalloc(&t->order, B)); CU(t, dalloc(&t->n_tiles, 2)); CU(t, dalloc(&t->seg_start, TB_MAX_BUCKETS + 3));
+    CU(t, dalloc(&t->tiles, (size_t)t->max_tiles + t->max_units));
+    const size_t n_cells = ls ? (size_t)(l2 * t->l2in + 2 * l2 + 1 + l1) : (size_t)(l1 * l2 + 2 * l2 + 1 + l1);
+    CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 16 : (size_t)128) * n_cells));
+    CU(t, dalloc(&t->l1w_partials, (size_t)t->max_units * l1 * t->K));
+    CU(t, dalloc(&t->bias_partials, (size_t)DGRAD_CTAS * 2 * F));
+    CU(t, dalloc(&t->feat_counts, (size_t)4 * N + 1)); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
+    CU(t, dalloc(&t->feat_cursor, (size_t)2 * N)); CU(t, dalloc(&t->feat_lists, (size_t)4 * B * A));
+    CU(t, cudaEventCreate(&t->ev_t0)); CU(t, cudaEventCreate(&t->ev_t1));
+    for (int i = 0; i < PH_COUNT; ++i) {
+        CU(t, cudaEventCreate(&t->ph_start[i])); CU(t, cudaEventCreate(&t->ph_stop[i]));
+    }
+    if (c.world_size > 1) {
+        std::string e;
+        if (!load_nccl(&e)) return fail(t, TB_ERR_NCCL, "%s", e.c_str());
+        Uid id;
+        memcpy(id.internal, c.nccl_unique_id, 128);
+        const int rc = g_nccl.CommInitRank(&t->comm, c.world_size, id, c.rank);
+        if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(rc));
+    }
+    CU(t, cudaDeviceSynchronize());
+    return TB_OK;
+}
+
+int validate_config(const tb_config* c) {
+    if (!c) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "config is NULL");
+    if (c->struct_size != (int32_t)sizeof(tb_config))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "tb_config.struct_size %d != %d (header / library mismatch)", c->struct_size, (int)sizeof(tb_config));
+    if (c->arch != TB_ARCH_LAYERSTACK && c->arch != TB_ARCH_SIMPLE) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "unknown arch %d", c->arch);
+    if (c->batch_capacity < 16 || c->batch_capacity % 16 != 0 || c->batch_capacity > (1 << 20))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "batch_capacity must be a multiple of 16 in [16, 2^20] (got %d)", c->batch_capacity);
+    if (c->ft_out < 128 || c->ft_out % 128 != 0 || c->ft_out > 4096)
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "ft_out must be a multiple of 128 in [128, 4096] (got %d)", c->ft_out);
+    if (c->arch == TB_ARCH_LAYERSTACK && c->ft_out < 256)
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "LayerStack needs ft_out >= 256 (got %d)", c->ft_out);
+    if (c->ft_in < 1 || c->max_active < 1 || c->max_active > 256) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad ft_in / max_active");
+    if (c->ft_factorize && (c->piece_inputs < 1 || c->ft_in % c->piece_inputs != 0))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "ft_factorize needs ft_in (%d) divisible by piece_inputs (%d)", c->ft_in, c->piece_inputs);
+    if (c->l1_out < 2 || c->l1_out > TB_MAX_L1) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "l1_out must be in [2, %d]", TB_MAX_L1);
+    if (c->l2_out < 1 || c->l2_out > TB_MAX_L2) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "l2_out must be in [1, %d]", TB_MAX_L2);
+    // trainer_layerstack.rs:797-800
+    if (c->arch == TB_ARCH_LAYERSTACK && (c->num_buckets < 2 || c->num_buckets > TB_MAX_BUCKETS))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "LayerStack requires num_buckets in [2, %d]", TB_MAX_BUCKETS);
+    if (c->optimizer < TB_OPT_RANGER || c->optimizer > TB_OPT_ADAMW) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "unknown optimizer %d", c->optimizer);
+    // trainer_layerstack.rs:801-805
+    if ((c->precision & TB_PREC_FT_FP16_OUT) && !(c->precision & TB_PREC_FT_FP16))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "--ft-fp16-out requires --ft-fp16");
+    if (c->precision != 0) return fail(nullptr, TB_ERR_UNSUPPORTED, "reduced-precision modes (tf32 / fp16) are not implemented; precision must be 0");
+    if (c->world_size < 1 || c->rank < 0 || c->rank >= c->world_size) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad rank %d / world_size %d", c->rank, c->world_size);
+    return TB_OK;
+}
+
+}  // namespace
+
+// ==================================================================================================
+// C ABI
+// ==================================================================================================
+extern "C" {
+
+int tb_create(const tb_config* cfg, tb_trainer** out) {
+    if (!out) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "out is NULL");
+    *out = nullptr;
+    int rc = validate_config(cfg);
+    if (rc != TB_OK) return rc;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev < 1) { cudaGetLastError(); return fail(nullptr, TB_ERR_NO_DEVICE, "no CUDA device is available"); }
+    if (cfg->device < 0 || cfg->device >= n_dev) return fail(nullptr, TB_ERR_NO_DEVICE, "device %d out of range (%d devices)", cfg->device, n_dev);
+    tb_trainer* t = new tb_trainer();
+    t->cfg = *cfg;
+    for (int i = 0; i < PH_COUNT; ++i) { t->ph_start[i] = t->ph_stop[i] = nullptr; t->ph_used[i] = false; t->ph_ms[i] = 0.0; t->ph_launches[i] = 0; }
+    rc = create_impl(t);
+    if (rc != TB_OK) { g_create_error = t->err; free_all(t); return rc; }
+    *out = t;
+    return TB_OK;
+}
+
+void tb_destroy(tb_trainer* t) {
+    if (!t) return;
+    cudaSetDevice(t->cfg.device);
+    free_all(t);
+}
+
+const char* tb_last_error(const tb_trainer* t) { return t ? t->err.c_str() : g_create_error.c_str(); }
+
+int tb_num_groups(const tb_trainer* t) { return t ? (int)t->groups.size() : 0; }
+const char* tb_group_name(const tb_trainer* t, int g) { return (t && g >= 0 && g < (int)t->groups.size()) ? t->groups[g].name.c_str() : nullptr; }
+int64_t tb_group_len(const tb_trainer* t, const char* name) {
+    Group* g = find_group(const_cast<tb_trainer*>(t), name);
+    return g ? g->len : -1;
+}
+
+int tb_upload_group(tb_trainer* t, const char* name, const float* w, const float* m, const float* v, const float* slow, int64_t len) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    Group* g = find_group(t, name);
+    if (!g) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown group '%s'", name ? name : "(null)");
+    if (len != g->len) return fail(t, TB_ERR_INVALID_ARGUMENT, "group '%s' has %lld elements, got %lld", name, (long long)g->len, (long long)len);
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->stream));
+    const size_t bytes = (size_t)len * 4;
+    if (w) CU(t, cudaMemcpy(g->w, w, bytes, cudaMemcpyHostToDevice));
+    if (m) CU(t, cudaMemcpy(g->m, m, bytes, cudaMemcpyHostToDevice));
+    if (v) CU(t, cudaMemcpy(g->v, v, bytes, cudaMemcpyHostToDevice));
+    if (slow && t->cfg.optimizer == TB_OPT_RANGER) CU(t, cudaMemcpy(g->slow, slow, bytes, cudaMemcpyHostToDevice));
+    if (w && g == &t->groups[0] && t->cfg.ft_factorize) {
+        // sync_ft_forward_weights: the forward table follows the master weights
+        t->launches += launch_ft_fold(t->stream, g->w, t->comb, t->cfg.ft_in, t->cfg.piece_inputs, t->cfg.ft_out);
+        CU(t, cudaStreamSynchronize(t->stream));
+    }
+    return TB_OK;
+}
+
+int tb_download_group(tb_trainer* t, const char* name, float* w, float* m, float* v, float* slow, int64_t len) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    Group* g = find_group(t, name);
+    if (!g) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown group '%s'", name ? name : "(null)");
+    if (len != g->len) return fail(t, TB_ERR_INVALID_ARGUMENT, "group '%s' has %lld elements, got %lld", name, (long long)g->len, (long long)len);
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->stream));
+    const size_t bytes = (size_t)len * 4;
+    if (w) CU(t, cudaMemcpy(w, g->w, bytes, cudaMemcpyDeviceToHost));
+    if (m) CU(t, cudaMemcpy(m, g->m, bytes, cudaMemcpyDeviceToHost));
+    if (v) CU(t, cudaMemcpy(v, g->v, bytes, cudaMemcpyDeviceToHost));
+    if (slow) {
+        if (t->cfg.optimizer == TB_OPT_RANGER) CU(t, cudaMemcpy(slow, g->slow, bytes, cudaMemcpyDeviceToHost));
+        else memset(slow, 0, bytes);
+    }
+    return TB_OK;
+}
+
+int tb_get_step_count(const tb_trainer* t, uint64_t* s) { if (!t || !s) return TB_ERR_INVALID_ARGUMENT; *s = t->step_count; return TB_OK; }
+int tb_set_step_count(tb_trainer* t, uint64_t s) { if (!t) return TB_ERR_INVALID_ARGUMENT; t->step_count = s; return TB_OK; }
+
+int tb_train_step(tb_trainer* t, const tb_batch* batch, float lr, float wdl_lambda, const tb_loss* loss, double* loss_prev) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    int rc = check_batch(t, batch);
+    if (rc == TB_OK) rc = check_loss(t, loss);
+    if (rc != TB_OK) return rc;
+    if (batch->n_pos == 0) { if (loss_prev) *loss_prev = 0.0; return TB_OK; }  // trainer_layerstack.rs:2018-2023
+    CU(t, cudaSetDevice(t->cfg.device));
+    int s = 0;
+    rc = ring_upload(t, batch, &s);
+    if (rc != TB_OK) return rc;
+    rc = step_on(t, t->ring[s], lr, wdl_lambda, loss, loss_prev);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaEventRecord(t->ev_consumed[s], t->stream));
+    t->consumed_pending[s] = true;
+    return TB_OK;
+}
+
+int tb_flush_pending_loss(tb_trainer* t, double* loss) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    double returned = 0.0;
+    if (t->loss_primed) {
+        const int last = (int)((t->loss_step + 1) % 2);
+        CU(t, cudaEventSynchronize(t->ev_loss[last]));
+        returned = *t->loss_pinned[last];
+    }
+    t->loss_primed = false;
+    t->loss_step = 0;
+    if (loss) *loss = returned;
+    return TB_OK;
+}
+
+int tb_validate_step(tb_trainer* t, const tb_batch* batch, float wdl_lambda, const tb_loss* loss, double* sum_sq_err, float* net_output) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    int rc = check_batch(t, batch);
+    if (rc == TB_OK) rc = check_loss(t, loss);
+    if (rc != TB_OK) return rc;
+    if (batch->n_pos == 0) { if (sum_sq_err) *sum_sq_err = 0.0; return TB_OK; }
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->stream));  // GpuTrainer::validate drains the stream first
+    DevBatch& d = t->slots[TB_NUM_SLOTS - 1];
+    tb_batch b = *batch;
+    if (b.per_pos_norm == 0.f) b.per_pos_norm = 1.0f / (float)b.n_pos;
+    rc = upload_batch(t, &b, &d, nullptr, t->stream);
+    if (rc != TB_OK) return rc;
+    rc = run_forward(t, d, loss, wdl_lambda, 0);
+    if (rc != TB_OK) return rc;
+    double l = 0.0;
+    CU(t, cudaMemcpyAsync(&l, t->loss_acc, sizeof(double), cudaMemcpyDeviceToHost, t->stream));
+    if (net_output) CU(t, cudaMemcpyAsync(net_output, t->net_output, (size_t)b.n_pos * 4, cudaMemcpyDeviceToHost, t->stream));
+    CU(t, cudaStreamSynchronize(t->stream));
+    profile_collect(t);
+    if (sum_sq_err) *sum_sq_err = l;
+    return TB_OK;
+}
+
+int tb_read_fp16_clamp_count(tb_trainer* t, uint64_t* clamps, uint64_t* elems) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    if (clamps) *clamps = 0;  // no fp16 path: nothing is ever clamped
+    if (elems) *elems = 0;
+    return TB_OK;
+}
+
+int tb_stage_batch(tb_trainer* t, int slot, const tb_batch* batch) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    if (slot < 0 || slot >= TB_NUM_SLOTS - 1) return fail(t, TB_ERR_INVALID_ARGUMENT, "slot %d out of range [0, %d)", slot, TB_NUM_SLOTS - 1);
+    int rc = check_batch(t, batch);
+    if (rc != TB_OK) return rc;
+    if (batch->n_pos == 0) return fail(t, TB_ERR_INVALID_ARGUMENT, "cannot stage an empty batch");
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->stream));
+    rc = upload_batch(t, batch, &t->slots[slot], nullptr, t->stream);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaStreamSynchronize(t->stream));
+    return TB_OK;
+}
+
+int tb_train_step_staged(tb_trainer* t, int slot, float lr, float wdl_lambda, const tb_loss* loss, double* loss_prev) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    if (slot < 0 || slot >= TB_NUM_SLOTS - 1 || t->slots[slot].n_pos == 0) return fail(t, TB_ERR_INVALID_ARGUMENT, "slot %d holds no batch", slot);
+    int rc = check_loss(t, loss);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaSetDevice(t->cfg.device));
+    return step_on(t, t->slots[slot], lr, wdl_lambda, loss, loss_prev);
+}
+
+int tb_forward_backward(tb_trainer* t, const tb_batch* batch, float wdl_lambda, const tb_loss* loss, double* loss_now) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    int rc = check_batch(t, batch);
+    if (rc == TB_OK) rc = check_loss(t, loss);
+    if (rc != TB_OK) return rc;
+    if (batch->n_pos == 0) { if (loss_now) *loss_now = 0.0; return TB_OK; }
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->stream));
+    DevBatch& d = t->slots[TB_NUM_SLOTS - 1];
+    rc = upload_batch(t, batch, &d, nullptr, t->stream);
+    if (rc == TB_OK) rc = run_forward(t, d, loss, wdl_lambda, 1);
+    if (rc == TB_OK) rc = run_backward(t, d);
+    if (rc == TB_OK) rc = run_allreduce(t);
+    if (rc != TB_OK) return rc;
+    if (t->cfg.ft_factorize)
+        t->launches += launch_ft_reduce_virtual(t->stream, t->groups[0].grad, t->cfg.ft_in, t->cfg.piece_inputs, t->cfg.ft_out);
+    double l = 0.0;
+    CU(t, cudaMemcpyAsync(&l, t->loss_acc, sizeof(double), cudaMemcpyDeviceToHost, t->stream));
+    CU(t, cudaStreamSynchronize(t->stream));
+    CU(t, cudaGetLastError());
+    profile_collect(t);
+    if (loss_now) *loss_now = l;
+    return TB_OK;
+}
+
+int tb_apply_optimizer(tb_trainer* t, float lr) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    CU(t, cudaSetDevice(t->cfg.device));
+    int rc = run_optimizer(t, lr);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaStreamSynchronize(t->stream));
+    CU(t, cudaGetLastError());
+    profile_collect(t);
+    return TB_OK;
+}
+
+int tb_download_grad(tb_trainer* t, const char* name, float* grad, int64_t len) {
+    if (!t || !grad) return TB_ERR_INVALID_ARGUMENT;
+    Group* g = find_group(t, name);
+    if (!g) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown group '%s'", name ? name : "(null)");
+    if (len != g->len) return fail(t, TB_ERR_INVALID_ARGUMENT, "group '%s' has %lld elements, got %lld", name, (long long)g->len, (long long)len);
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->stream));
+    CU(t, cudaMemcpy(grad, g->grad, (size_t)len * 4, cudaMemcpyDeviceToHost));
+    return TB_OK;
+}
+
+int tb_read_buffer(tb_trainer* t, const char* name, float* out, int64_t len) {
+    if (!t || !name || !out) return TB_ERR_INVALID_ARGUMENT;
+    const tb_config& c = t->cfg;
+    const int64_t B = t->last_n, F = c.ft_out;
+    struct { const char* n; const float* p; int64_t l; } tab[] = {
+        {"ft_stm", t->pre[0], B * F}, {"ft_nstm", t->pre[1], B * F}, {"combined", t->combined, B * t->K},
+        {"l1_total", t->l1_out, B * c.l1_out}, {"net_output", t->net_output, B}, {"dy", t->dy, B},
+        {"dl1_total", t->dl1, B * c.l1_out}, {"dft_stm", t->dft[0], B * F}, {"dft_nstm", t->dft[1], B * F},
+        {"comb", t->comb, t->comb ? (int64_t)c.ft_in * F : 0}};
+    for (auto& e : tab)
+        if (strcmp(e.n, name) == 0) {
+            if (len != e.l) return fail(t, TB_ERR_INVALID_ARGUMENT, "buffer '%s' has %lld elements, got %lld", name, (long long)e.l, (long long)len);
+            CU(t, cudaSetDevice(c.device));
+            CU(t, cudaStreamSynchronize(t->stream));
+            if (len > 0) CU(t, cudaMemcpy(out, e.p, (size_t)len * 4, cudaMemcpyDeviceToHost));
+            return TB_OK;
+        }
+    return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown buffer '%s'", name);
+}
+
+int tb_timer_start(tb_trainer* t) { if (!t) return TB_ERR_INVALID_ARGUMENT; CU(t, cudaEventRecord(t->ev_t0, t->stream)); return TB_OK; }
+int tb_timer_stop(tb_trainer* t, float* ms) {
+    if (!t || !ms) return TB_ERR_INVALID_ARGUMENT;
+    CU(t, cudaEventRecord(t->ev_t1, t->stream));
+    CU(t, cudaEventSynchronize(t->ev_t1));
+    CU(t, cudaEventElapsedTime(ms, t->ev_t0, t->ev_t1));
+    return TB_OK;
+}
+int tb_profile_enable(tb_trainer* t, int on) { if (!t) return TB_ERR_INVALID_ARGUMENT; t->profile = on != 0; return TB_OK; }
+int tb_profile_num_phases(const tb_trainer* t) { (void)t; return PH_COUNT; }
+int tb_profile_read(tb_trainer* t, int phase, const char** name, double* total_ms, int64_t* launches) {
+    if (!t || phase < 0 || phase >= PH_COUNT) return TB_ERR_INVALID_ARGUMENT;
+    if (name) *name = kPhaseNames[phase];
+    if (total_ms) *total_ms = t->ph_ms[phase];
+    if (launches) *launches = t->ph_launches[phase];
+    return TB_OK;
+}
+int tb_profile_reset(tb_trainer* t) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    for (int i = 0; i < PH_COUNT; ++i) { t->ph_ms[i] = 0.0; t->ph_launches[i] = 0; t->ph_used[i] = false; }
+    return TB_OK;
+}
+int64_t tb_launch_count(const tb_trainer* t) { return t ? t->launches : 0; }
+int tb_synchronize(tb_trainer* t) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    CU(t, cudaSetDevice(t->cfg.device));
+    CU(t, cudaStreamSynchronize(t->copy_stream));
+    CU(t, cudaStreamSynchronize(t->stream));
+    return TB_OK;
+}
+
+int tb_nccl_unique_id(uint8_t out[128]) {
+    if (!out) return TB_ERR_INVALID_ARGUMENT;
+    std::string e;
+    if (!load_nccl(&e)) return fail(nullptr, TB_ERR_NCCL, "%s", e.c_str());
+    Uid id;
+    const int rc = g_nccl.GetUniqueId(&id);
+    if (rc != 0) return fail(nullptr, TB_ERR_NCCL, "ncclGetUniqueId: %s", g_nccl.GetErrorString(rc));
+    memcpy(out, id.internal, 128);
+    return TB_OK;
+}
+
+int tb_host_alloc(void** out, size_t bytes) {
+    if (!out) return TB_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(nullptr, TB_ERR_OUT_OF_MEMORY, "cudaHostAlloc(%zu): %s", bytes, cudaGetErrorString(e)); }
+    return TB_OK;
+}
+int tb_host_free(void* p) {
+    if (p && cudaFreeHost(p) != cudaSuccess) { cudaGetLastError(); return TB_ERR_CUDA; }
+    return TB_OK;
+}
+
+int tb_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+const char* tb_version(void) { return "tatara_b200 0.1 (sm_100a)"; }
+
+// ---- FT kernels alone -------------------------------------------------------------------------------------
+#define CUX(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { rc = fail(nullptr, TB_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); goto done; } } while (0)
+
+int tb_ft_forward_bench(int device, const float* table, const int32_t* indices, const int32_t* nnz, int batch, int ft_out,
+                        int ft_in, int max_active, int iters, float* out, float* ms_per_iter) {
+    if (!table || !indices || !nnz || batch < 1 || ft_out % 128 != 0 || iters < 1) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad argument");
+    int rc = TB_OK;
+    float *d_t = nullptr, *d_o = nullptr;
+    int *d_i = nullptr, *d_n = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    const size_t B = batch, F = ft_out, N = ft_in, A = max_active;
+    CUX(cudaSetDevice(device));
+    CUX(cudaMalloc(&d_t, N * F * 4)); CUX(cudaMalloc(&d_o, B * F * 4)); CUX(cudaMalloc(&d_i, B * A * 4)); CUX(cudaMalloc(&d_n, B * 4));
+    CUX(cudaMemcpy(d_t, table, N * F * 4, cudaMemcpyHostToDevice));
+    CUX(cudaMemcpy(d_i, indices, B * A * 4, cudaMemcpyHostToDevice));
+    CUX(cudaMemcpy(d_n, nnz, B * 4, cudaMemcpyHostToDevice));
+    CUX(cudaEventCreate(&e0)); CUX(cudaEventCreate(&e1));
+    launch_ft_forward(0, 0, d_t, d_i, d_i, d_n, nullptr, d_o, d_o, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1);
+    CUX(cudaDeviceSynchronize());
+    CUX(cudaEventRecord(e0, 0));
+    for (int i = 0; i < iters; ++i) launch_ft_forward(0, 0, d_t, d_i, d_i, d_n, nullptr, d_o, d_o, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1);
+    CUX(cudaEventRecord(e1, 0));
+    CUX(cudaEventSynchronize(e1));
+    { float ms = 0.f; CUX(cudaEventElapsedTime(&ms, e0, e1)); if (ms_per_iter) *ms_per_iter = ms / iters; }
+    if (out) CUX(cudaMemcpy(out, d_o, B * F * 4, cudaMemcpyDeviceToHost));
+done:
+    cudaFree(d_t); cudaFree(d_o); cudaFree(d_i); cudaFree(d_n);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    return rc;
+}
+
+int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, const int32_t* nnz, int batch, int ft_out,
+                         int ft_in, int max_active, int iters, float* grad, float* ms_per_iter) {
+    if (!dft || !indices || !nnz || batch < 1 || ft_out % 128 != 0 || iters < 1) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad argument");
+    int rc = TB_OK;
+    float *d_d = nullptr, *d_g = nullptr;
+    int *d_i = nullptr, *d_n = nullptr, *d_cnt = nullptr, *d_off = nullptr, *d_cur = nullptr, *d_lists = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    const size_t B = batch, F = ft_out, N = ft_in, A = max_active;
+    CUX(cudaSetDevice(device));
+    CUX(cudaMalloc(&d_d, B * F * 4)); CUX(cudaMalloc(&d_g, N * F * 4)); CUX(cudaMalloc(&d_i, B * A * 4)); CUX(cudaMalloc(&d_n, B * 4));
+    CUX(cudaMalloc(&d_cnt, (4 * N + 1) * 4)); CUX(cudaMalloc(&d_off, 2 * (N + 1) * 4)); CUX(cudaMalloc(&d_cur, 2 * N * 4));
+    CUX(cudaMalloc(&d_lists, 4 * B * A * 4));
+    CUX(cudaMemcpy(d_d, dft, B * F * 4, cudaMemcpyHostToDevice));
+    CUX(cudaMemcpy(d_i, indices, B * A * 4, cudaMemcpyHostToDevice));
+    CUX(cudaMemcpy(d_n, nnz, B * 4, cudaMemcpyHostToDevice));
+    CUX(cudaEventCreate(&e0)); CUX(cudaEventCreate(&e1));
+    for (int i = -1; i < iters; ++i) {
+        if (i == 0) { CUX(cudaDeviceSynchronize()); CUX(cudaEventRecord(e0, 0)); }
+        launch_inverse_index(0, d_i, d_i, d_n, batch, max_active, ft_in, 1, d_cnt, d_off, d_cur, d_lists);
+        launch_ft_backward(0, d_d, d_d, d_off, d_lists, batch, max_active, ft_in, ft_out, 1, d_g);
+    }
+    CUX(cudaEventRecord(e1, 0));
+    CUX(cudaEventSynchronize(e1));
+    { float ms = 0.f; CUX(cudaEventElapsedTime(&ms, e0, e1)); if (ms_per_iter) *ms_per_iter = ms / iters; }
+    if (grad) CUX(cudaMemcpy(grad, d_g, N * F * 4, cudaMemcpyDeviceToHost));
+done:
+    cudaFree(d_d); cudaFree(d_g); cudaFree(d_i); cudaFree(d_n); cudaFree(d_cnt); cudaFree(d_off); cudaFree(d_cur); cudaFree(d_lists);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    return rc;
+}
+
+int tb_adam_clamp_bench(int device, float* w, float* m, float* v, const float* grad, int64_t n, float lr, float decay,
+                        float min_w, float max_w, int iters, float* ms_per_iter) {
+    if (!w || !m || !v || !grad || n < 4 || n % 4 != 0 || iters < 1) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad argument");
+    int rc = TB_OK;
+    float *d_w = nullptr, *d_m = nullptr, *d_v = nullptr, *d_g = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    OptScalars sc;
+    sc.lr = lr; sc.step_size = 1.f; sc.decay = decay; sc.beta1 = 0.9f; sc.beta2 = BETA2; sc.eps = EPS; sc.min_w = min_w; sc.max_w = max_w;
+    sc.alpha = RANGER_ALPHA; sc.denom = 1; sc.lerp = 0;
+    const size_t bytes = (size_t)n * 4;
+    CUX(cudaSetDevice(device));
+    CUX(cudaMalloc(&d_w, bytes)); CUX(cudaMalloc(&d_m, bytes)); CUX(cudaMalloc(&d_v, bytes)); CUX(cudaMalloc(&d_g, bytes));
+    CUX(cudaMemcpy(d_w, w, bytes, cudaMemcpyHostToDevice)); CUX(cudaMemcpy(d_m, m, bytes, cudaMemcpyHostToDevice));
+    CUX(cudaMemcpy(d_v, v, bytes, cudaMemcpyHostToDevice)); CUX(cudaMemcpy(d_g, grad, bytes, cudaMemcpyHostToDevice));
+    CUX(cudaEventCreate(&e0)); CUX(cudaEventCreate(&e1));
+    CUX(cudaEventRecord(e0, 0));
+    for (int i = 0; i < iters; ++i) launch_radam(0, d_w, d_m, d_v, d_g, nullptr, n, sc);
+    CUX(cudaEventRecord(e1, 0));
+    CUX(cudaEventSynchronize(e1));
+    { float ms = 0.f; CUX(cudaEventElapsedTime(&ms, e0, e1)); if (ms_per_iter) *ms_per_iter = ms / iters; }
+    CUX(cudaMemcpy(w, d_w, bytes, cudaMemcpyDeviceToHost)); CUX(cudaMemcpy(m, d_m, bytes, cudaMemcpyDeviceToHost));
+    CUX(cudaMemcpy(v, d_v, bytes, cudaMemcpyDeviceToHost));
+done:
+    cudaFree(d_w); cudaFree(d_m); cudaFree(d_v); cudaFree(d_g);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    return rc;
+}
+
+}  // extern "C"
