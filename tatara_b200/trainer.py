@@ -209,7 +209,10 @@ class _Trainer:
 
     # -- parameter groups
     def group_len(self, name: str) -> int:
-        return int(self._lib.tb_group_len(self._h, name.encode()))
+        n = int(self._lib.tb_group_len(self._h, name.encode()))
+        if n < 0:
+            raise TrainerError("unknown group '%s'" % name)
+        return n
 
     def upload_group(self, name, w=None, m=None, v=None, slow=None):
         n = self.group_len(name)
