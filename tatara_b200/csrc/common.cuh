@@ -56,21 +56,37 @@ static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b;
 
 // ft_kernels.cu
 // mode: 0 raw gather-sum, 1 LayerStack pairwise (+bias, CReLU, product, scale), 2 Simple CReLU, 3 Simple SCReLU
+// items: the (position, perspective) processing order from launch_item_sort, or NULL for natural order
 int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
                       const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
-                      int B, int F, int N, int A, float scale, int n_persp);
+                      const int* items, int B, int F, int N, int A, float scale, int n_persp);
+// scratch of the inverse index, in ints: histogram [2N], a counter, a queue of long lists [2N], scan block sums
+static inline size_t inverse_index_counts_len(int N) { return 4 * (size_t)N + 1 + 2 * ((size_t)N / 2048 + 2); }
+// counts: [inverse_index_counts_len(N)], offsets: [2][N+1], cursor: [2][N], lists: [4][B*A] (lists + sort scratch)
 int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
-                         int N, int n_persp, int* counts /*[2][N]*/, int* offsets /*[2][N+1]*/,
-                         int* cursor /*[2][N]*/, int* lists /*[2][B*A]*/);
+                         int N, int n_persp, int* counts, int* offsets, int* cursor, int* lists);
+// one block per feature row, whatever the length of its list
 int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
                        const int* lists, int B, int A, int N, int F, int n_persp, float* grad);
+// long lists are cut into parts summed by separate blocks; plan: [2 + 2 * max_work + 3 * N] ints,
+// partial: [max_work][F] floats with max_work = ft_backward_max_work(B, A, n_persp)
+int ft_backward_max_work(int B, int A, int n_persp);
+int launch_ft_backward_split(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
+                             const int* lists, int B, int A, int N, int F, int n_persp, int* plan, float* partial,
+                             float* grad);
+// items of both perspectives sorted by the table slice of their features; hist: [(slices + 1) * ceil(n_persp*B/1024)],
+// seg: [slices + 2]
+int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,
+                     int rows_per_slice, int n_persp, int* items, int* hist, int* seg);
+int sort_max_units(int max_tiles);
 int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F);
 int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F);
 
 // dense_kernels.cu
 // tiles has room for max_tiles tiles followed by the work units; n_tiles is {tile count, unit count}
+// hist: scratch of (nb + 1) * ceil(B / 1024) ints
 int launch_bucket_sort(cudaStream_t s, const int* bucket /*may be NULL*/, int B, int nb, int* order,
-                       TileDesc* tiles, int* n_tiles, int* seg_start /*[nb+2]*/, int max_tiles);
+                       TileDesc* tiles, int* n_tiles, int* seg_start /*[nb+2]*/, int max_tiles, int* hist);
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb /*[nb][l1][K] or NULL*/,
                       const float* bb, const float* ws /*[K][l1]*/, const float* bs, float* y /*[B][l1]*/,

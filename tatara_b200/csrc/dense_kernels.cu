@@ -10,126 +10,6 @@
 
 #define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
 #define L1_SQR_SCALE (127.0f / 128.0f)
-#define UNIT_TILES 16  // tiles per work unit of the L1 weight-gradient kernel
-
-// ------------------------------------------------------------------------------------------------
-// bucket grouping: stable counting sort of the positions by bucket id, one block.
-// Replaces count_buckets / exclusive_scan_aligned / scatter_bucket_perm / permute_rows_f32
-// (native_kernels.cu:1858-1973); out-of-range bucket ids form a last group of their own.
-// units[]: runs of at most UNIT_TILES tiles of one bucket, stored behind the tiles as TileDesc
-// {first tile, tile count, bucket}.
-// ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) k_bucket_sort(const int* __restrict__ bucket, int B, int nb,
-                                                       int* __restrict__ order, TileDesc* __restrict__ tiles,
-                                                       int* __restrict__ n_tiles, int* __restrict__ seg_start,
-                                                       TileDesc* __restrict__ units, int* __restrict__ n_units) {
-    __shared__ int s_warp[32];
-    __shared__ int s_cnt[TB_MAX_BUCKETS + 1];
-    __shared__ int s_base[TB_MAX_BUCKETS + 2];
-    __shared__ int s_tile_base[TB_MAX_BUCKETS + 2];
-    __shared__ int s_unit_base[TB_MAX_BUCKETS + 2];
-    const int K = nb + 1;
-    const int per = (B + blockDim.x - 1) / blockDim.x;
-    const int beg = min((int)threadIdx.x * per, B), end = min(beg + per, B);
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    int cnt[TB_MAX_BUCKETS + 1];
-    int excl[TB_MAX_BUCKETS + 1];
-#pragma unroll
-    for (int k = 0; k <= TB_MAX_BUCKETS; ++k) cnt[k] = 0;
-    for (int i = beg; i < end; ++i) {
-        int k = bucket ? bucket[i] : 0;
-        if ((unsigned)k >= (unsigned)nb) k = nb;
-#pragma unroll
-        for (int q = 0; q <= TB_MAX_BUCKETS; ++q) cnt[q] += (q == k);
-    }
-#pragma unroll
-    for (int k = 0; k <= TB_MAX_BUCKETS; ++k) {
-        if (k < K) {
-            int incl = cnt[k];
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                int t = __shfl_up_sync(0xffffffffu, incl, d);
-                if (lane >= d) incl += t;
-            }
-            if (lane == 31) s_warp[w] = incl;
-            __syncthreads();
-            if (w == 0) {
-                int t = s_warp[lane];
-                int ti = t;
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    int u = __shfl_up_sync(0xffffffffu, ti, d);
-                    if (lane >= d) ti += u;
-                }
-                s_warp[lane] = ti - t;
-                if (lane == 31) s_cnt[k] = ti;
-            }
-            __syncthreads();
-            excl[k] = s_warp[w] + incl - cnt[k];
-            __syncthreads();
-        }
-    }
-    if (threadIdx.x == 0) {
-        int run = 0, trun = 0, urun = 0;
-        for (int k = 0; k < K; ++k) {
-            s_base[k] = run;
-            s_tile_base[k] = trun;
-            s_unit_base[k] = urun;
-            seg_start[k] = run;
-            run += s_cnt[k];
-            const int nt = (s_cnt[k] + TB_TILE_M - 1) / TB_TILE_M;
-            trun += nt;
-            urun += (nt + UNIT_TILES - 1) / UNIT_TILES;
-        }
-        s_base[K] = run;
-        s_tile_base[K] = trun;
-        s_unit_base[K] = urun;
-        seg_start[K] = run;
-        *n_tiles = trun;
-        *n_units = urun;
-    }
-    __syncthreads();
-    int run[TB_MAX_BUCKETS + 1];
-#pragma unroll
-    for (int k = 0; k <= TB_MAX_BUCKETS; ++k) run[k] = (k < K) ? s_base[k] + excl[k] : 0;
-    for (int i = beg; i < end; ++i) {
-        int k = bucket ? bucket[i] : 0;
-        if ((unsigned)k >= (unsigned)nb) k = nb;
-        int dst = 0;
-#pragma unroll
-        for (int q = 0; q <= TB_MAX_BUCKETS; ++q)
-            if (q == k) dst = run[q]++;
-        order[dst] = i;
-    }
-    for (int k = 0; k < K; ++k) {
-        const int c = s_cnt[k];
-        const int nt = (c + TB_TILE_M - 1) / TB_TILE_M;
-        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
-            TileDesc d;
-            d.start = s_base[k] + t * TB_TILE_M;
-            d.count = min(TB_TILE_M, c - t * TB_TILE_M);
-            d.bucket = k;
-            d.pad = 0;
-            tiles[s_tile_base[k] + t] = d;
-        }
-        const int nu = (nt + UNIT_TILES - 1) / UNIT_TILES;
-        for (int u = threadIdx.x; u < nu; u += blockDim.x) {
-            TileDesc d;
-            d.start = s_tile_base[k] + u * UNIT_TILES;
-            d.count = min(UNIT_TILES, nt - u * UNIT_TILES);
-            d.bucket = k;
-            d.pad = 0;
-            units[s_unit_base[k] + u] = d;
-        }
-    }
-}
-
-int launch_bucket_sort(cudaStream_t s, const int* bucket, int B, int nb, int* order, TileDesc* tiles,
-                       int* n_tiles, int* seg_start, int max_tiles) {
-    // units live behind the tiles: tiles[max_tiles .. ), n_units behind n_tiles
-    k_bucket_sort<<<1, 1024, 0, s>>>(bucket, B, nb, order, tiles, n_tiles, seg_start, tiles + max_tiles, n_tiles + 1);
-    return 1;
-}
 
 // ------------------------------------------------------------------------------------------------
 // L1 forward.  y[pos, o] = (bb[g, o] + sum_k x[pos, k] wb[g, o, k]) + (bs[o] + sum_k x[pos, k] ws[k, o])
@@ -202,9 +82,154 @@ __global__ void __launch_bounds__(256) k_l1_forward(const float* __restrict__ x,
     }
 }
 
+// Register-tiled variant for l1 % 4 == 0 (every shipped configuration).  A block of 64 threads owns one tile
+// of 32 positions and all NOUT output columns (LayerStack: [0, l1) per-bucket, [l1, 2 l1) shared; Simple:
+// [0, l1)), NT = ceil(NOUT / 32) column tiles.  Thread (ty, tx) accumulates rows 4ty..4ty+3 x columns
+// 4tx..4tx+3 of every column tile; per k it needs one 128-bit load of x (stored k-major in shared memory) and
+// one per column tile of w.  The next K chunk is fetched into registers while the current one is multiplied.
+template <int NT, bool HAS_BUCKET>
+__global__ void __launch_bounds__(64) k_l1_forward_tiled(const float* __restrict__ x, int K, const int* __restrict__ order,
+                                                          const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
+                                                          const float* __restrict__ wb, const float* __restrict__ bb,
+                                                          const float* __restrict__ ws, const float* __restrict__ bs,
+                                                          float* __restrict__ y, int l1, int nb) {
+    if ((int)blockIdx.x >= *n_tiles) return;
+    const TileDesc td = tiles[blockIdx.x];
+    constexpr int WS_LD = NT * 32 + 4;
+    __shared__ __align__(16) float xs[32][36];      // [k][position]
+    __shared__ __align__(16) float wsm[32][WS_LD];  // [k][output column]
+    __shared__ int s_pos[TB_TILE_M];
+    const int tid = threadIdx.x;
+    const int ty = tid >> 3, tx = tid & 7;
+    const bool use_b = HAS_BUCKET && td.bucket < nb;
+    const int NOUT = HAS_BUCKET ? 2 * l1 : l1;
+    if (tid < TB_TILE_M) s_pos[tid] = tid < td.count ? order[td.start + tid] : -1;
+    for (int e = tid; e < 32 * WS_LD; e += 64) (&wsm[0][0])[e] = 0.f;  // columns >= NOUT stay zero
+    __syncthreads();
+
+    // global -> register staging of one K chunk
+    float4 xr[4];
+    float4 wr[NT * 4];
+    const int l1q = l1 >> 2;  // float4 per shared-weight row
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = tid + 64 * j;
+            const int row = e >> 3, k4 = (e & 7) << 2;
+            const int pos = s_pos[row];
+            xr[j] = pos >= 0 ? __ldg(reinterpret_cast<const float4*>(x + (size_t)pos * K + k0 + k4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < NT * 4; ++j) {
+            const int e = tid + 64 * j;  // float4 index inside the chunk's weights
+            wr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (HAS_BUCKET) {
+                // first l1 * 8 float4: per-bucket rows wb[g][o][k0 + k4 ..]; then 32 * l1q float4: shared rows ws[k][o4 ..]
+                if (e < l1 * 8) {
+                    if (use_b) {
+                        const int o = e >> 3, k4 = (e & 7) << 2;
+                        wr[j] = __ldg(reinterpret_cast<const float4*>(wb + ((size_t)td.bucket * l1 + o) * K + k0 + k4));
+                    }
+                } else if (e < l1 * 8 + 32 * l1q) {
+                    wr[j] = __ldg(reinterpret_cast<const float4*>(ws + (size_t)k0 * l1) + (e - l1 * 8));
+                }
+            } else if (e < 32 * l1q) {
+                wr[j] = __ldg(reinterpret_cast<const float4*>(ws + (size_t)k0 * l1) + e);
+            }
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = tid + 64 * j;
+            const int row = e >> 3, k4 = (e & 7) << 2;
+            xs[k4 + 0][row] = xr[j].x; xs[k4 + 1][row] = xr[j].y; xs[k4 + 2][row] = xr[j].z; xs[k4 + 3][row] = xr[j].w;
+        }
+#pragma unroll
+        for (int j = 0; j < NT * 4; ++j) {
+            const int e = tid + 64 * j;
+            if (HAS_BUCKET) {
+                if (e < l1 * 8) {
+                    const int o = e >> 3, k4 = (e & 7) << 2;
+                    wsm[k4 + 0][o] = wr[j].x; wsm[k4 + 1][o] = wr[j].y; wsm[k4 + 2][o] = wr[j].z; wsm[k4 + 3][o] = wr[j].w;
+                } else if (e < l1 * 8 + 32 * l1q) {
+                    const int r = e - l1 * 8;
+                    const int k = r / l1q, o4 = (r - k * l1q) << 2;
+                    *reinterpret_cast<float4*>(&wsm[k][l1 + o4]) = wr[j];
+                }
+            } else if (e < 32 * l1q) {
+                const int k = e / l1q, o4 = (e - k * l1q) << 2;
+                *reinterpret_cast<float4*>(&wsm[k][o4]) = wr[j];
+            }
+        }
+    };
+
+    float acc[NT][4][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[t][i][j] = 0.f;
+
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        __syncthreads();  // the previous chunk has been consumed
+        stage();
+        __syncthreads();
+        if (k0 + 32 < K) fetch(k0 + 32);
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[k][4 * ty]);
+            const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const float4 b = *reinterpret_cast<const float4*>(&wsm[k][t * 32 + 4 * tx]);
+                const float bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[t][i][j] += av[i] * bv[j];
+            }
+        }
+    }
+    // combine the two halves through shared memory: out[row][col]
+    __syncthreads();
+    float* outs = &wsm[0][0];  // [32][WS_LD]
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<float4*>(&outs[(4 * ty + i) * WS_LD + t * 32 + 4 * tx]) =
+                make_float4(acc[t][i][0], acc[t][i][1], acc[t][i][2], acc[t][i][3]);
+    __syncthreads();
+    for (int e = tid; e < TB_TILE_M * l1; e += 64) {
+        const int r = e / l1, o = e - r * l1;
+        const int pos = s_pos[r];
+        if (pos < 0) continue;
+        if (HAS_BUCKET) {
+            const float yb = use_b ? bb[td.bucket * l1 + o] + outs[r * WS_LD + o] : 0.f;
+            const float ysv = bs[o] + outs[r * WS_LD + l1 + o];
+            y[(size_t)pos * l1 + o] = yb + ysv;
+        } else {
+            y[(size_t)pos * l1 + o] = bs[o] + outs[r * WS_LD + o];
+        }
+    }
+}
+
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb, const float* bb, const float* ws,
                       const float* bs, float* y, int l1, int nb) {
+    const int nout = wb ? 2 * l1 : l1;
+    if (l1 % 4 == 0 && nout <= 64) {
+        if (wb) {
+            if (nout <= 32) k_l1_forward_tiled<1, true><<<max_tiles, 64, 0, s>>>(x, K, order, tiles, n_tiles, wb, bb, ws, bs, y, l1, nb);
+            else k_l1_forward_tiled<2, true><<<max_tiles, 64, 0, s>>>(x, K, order, tiles, n_tiles, wb, bb, ws, bs, y, l1, nb);
+        } else {
+            k_l1_forward_tiled<1, false><<<max_tiles, 64, 0, s>>>(x, K, order, tiles, n_tiles, wb, bb, ws, bs, y, l1, nb);
+        }
+        return 1;
+    }
     if (wb)
         k_l1_forward<true><<<max_tiles, 256, 0, s>>>(x, K, order, tiles, n_tiles, wb, bb, ws, bs, y, l1, nb);
     else
@@ -673,13 +698,86 @@ __global__ void __launch_bounds__(256) k_l1_wgrad_final(const float* __restrict_
     gw_shared[(size_t)k * l1 + o] = total;
 }
 
+// Variant for l1 % 8 == 0: a thread owns four adjacent columns and OPT outputs (OPT = 8 or 16; two thread groups
+// split the outputs when l1 = 32), so that one 128-bit load of x feeds 4 * OPT multiply-adds and the dl1 values
+// come as broadcast 128-bit shared-memory loads.
+template <int OPT>
+__global__ void __launch_bounds__(256) k_l1_wgrad_v4(const float* __restrict__ x, int K, const float* __restrict__ dl1,
+                                                      const int* __restrict__ order, const TileDesc* __restrict__ tiles,
+                                                      const TileDesc* __restrict__ units, const int* __restrict__ n_units, int l1,
+                                                      float* __restrict__ partials) {
+    const int u = blockIdx.y;
+    if (u >= *n_units) return;
+    const TileDesc ud = units[u];
+    __shared__ __align__(16) float sdl[TB_TILE_M][TB_MAX_L1];
+    __shared__ int s_pos[TB_TILE_M];
+    const int K4 = K >> 2;
+    const int tcol = threadIdx.x & 127, og = threadIdx.x >> 7;
+    const int col4 = blockIdx.x * 128 + tcol;
+    const bool active = col4 < K4;
+    const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x);
+    float4 acc[OPT];
+#pragma unroll
+    for (int j = 0; j < OPT; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = ud.start; t < ud.start + ud.count; ++t) {
+        const TileDesc td = tiles[t];
+        __syncthreads();
+        for (int i = threadIdx.x; i < TB_TILE_M; i += blockDim.x) s_pos[i] = i < td.count ? order[td.start + i] : -1;
+        __syncthreads();
+        for (int e = threadIdx.x; e < TB_TILE_M * l1; e += blockDim.x) {
+            const int r = e / l1, o = e - r * l1;
+            const int p = s_pos[r];
+            sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
+        }
+        __syncthreads();
+        if (!active) continue;
+        for (int r0 = 0; r0 < td.count; r0 += 4) {
+            float4 xv[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int p = r0 + q < td.count ? s_pos[r0 + q] : -1;
+                xv[q] = p >= 0 ? __ldg(x4 + (size_t)p * K4 + col4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (r0 + q >= td.count) break;
+#pragma unroll
+                for (int j4 = 0; j4 < OPT / 4; ++j4) {
+                    const float4 g = *reinterpret_cast<const float4*>(&sdl[r0 + q][og * OPT + 4 * j4]);
+                    const float gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[4 * j4 + j].x += gv[j] * xv[q].x;
+                        acc[4 * j4 + j].y += gv[j] * xv[q].y;
+                        acc[4 * j4 + j].z += gv[j] * xv[q].z;
+                        acc[4 * j4 + j].w += gv[j] * xv[q].w;
+                    }
+                }
+            }
+        }
+    }
+    if (!active) return;
+#pragma unroll
+    for (int j = 0; j < OPT; ++j) {
+        const int o = og * OPT + j;
+        reinterpret_cast<float4*>(partials + ((size_t)u * l1 + o) * K)[col4] = acc[j];
+    }
+}
+
 int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, const int* order,
                     const TileDesc* tiles, const int* n_tiles, int max_tiles, int l1, int nb, float* partials,
                     float* gw_bucket, float* gw_shared) {
     const TileDesc* units = tiles + max_tiles;
     const int* n_units = n_tiles + 1;
-    const int max_units = max_tiles / UNIT_TILES + TB_MAX_BUCKETS + 2;
-    k_l1_wgrad<<<dim3(K / 128, max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+    const int max_units = sort_max_units(max_tiles);
+    if (l1 == 8)
+        k_l1_wgrad_v4<8><<<dim3(ceil_div(K / 4, 128), max_units), 128, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+    else if (l1 == 16)
+        k_l1_wgrad_v4<16><<<dim3(ceil_div(K / 4, 128), max_units), 128, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+    else if (l1 == 32)
+        k_l1_wgrad_v4<16><<<dim3(ceil_div(K / 4, 128), max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+    else
+        k_l1_wgrad<<<dim3(K / 128, max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
     k_l1_wgrad_final<<<ceil_div(l1 * K, 256), 256, 0, s>>>(partials, units, n_units, K, l1, nb, gw_bucket, gw_shared);
     return 2;
 }
@@ -756,15 +854,17 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
                     if (MODE == 1) xb[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + half + wcol);
                 }
             }
+            float4 dd[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+            for (int o = 0; o < l1; ++o) {
+                const float4 w4 = *reinterpret_cast<const float4*>(s_weff + o * CW + 4 * threadIdx.x);
+                const float g0 = sdl[r0][o], g1 = sdl[r0 + 1 < TB_TILE_M ? r0 + 1 : r0][o];
+                dd[0].x += g0 * w4.x; dd[0].y += g0 * w4.y; dd[0].z += g0 * w4.z; dd[0].w += g0 * w4.w;
+                dd[1].x += g1 * w4.x; dd[1].y += g1 * w4.y; dd[1].z += g1 * w4.z; dd[1].w += g1 * w4.w;
+            }
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 if (pp[q] < 0) continue;
-                float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int o = 0; o < l1; ++o) {
-                    const float g = sdl[r0 + q][o];
-                    const float4 w4 = *reinterpret_cast<const float4*>(s_weff + o * CW + 4 * threadIdx.x);
-                    d.x += g * w4.x; d.y += g * w4.y; d.z += g * w4.z; d.w += g * w4.w;
-                }
+                const float4 d = dd[q];
                 if (MODE == 1) {
                     const float4 a = make_float4(xa[q].x + bias0.x, xa[q].y + bias0.y, xa[q].z + bias0.z, xa[q].w + bias0.w);
                     const float4 b = make_float4(xb[q].x + bias1.x, xb[q].y + bias1.y, xb[q].z + bias1.z, xb[q].w + bias1.w);

@@ -17,26 +17,36 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
                                                      const int* __restrict__ idx_nstm, const int* __restrict__ nnz,
                                                      const float* __restrict__ bias, float* __restrict__ pre_stm,
                                                      float* __restrict__ pre_nstm, float* __restrict__ combined,
-                                                     int B, int F, int N, int A, float scale, int ipc) {
-    extern __shared__ int s_idx[];  // [ipc][A]
+                                                     const int* __restrict__ items, int n_items, int B, int F, int N, int A,
+                                                     float scale, int ipc) {
+    extern __shared__ int s_idx[];  // [ipc][A] indices, then [ipc] item ids
+    int* s_item = s_idx + ipc * A;
     const int tpi = F >> 3;
     const int il = threadIdx.x / tpi;
     const int lane = threadIdx.x - il * tpi;
-    const int persp = blockIdx.y;
-    const int* __restrict__ idx = persp ? idx_nstm : idx_stm;
-    const int item0 = blockIdx.x * ipc;
+    const int slot0 = blockIdx.x * ipc;
 
+    for (int i = threadIdx.x; i < ipc; i += blockDim.x) {
+        const int sl = slot0 + i;
+        s_item[i] = sl < n_items ? (items ? items[sl] : sl) : -1;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < ipc * A; i += blockDim.x) {
         const int li = i / A, a = i - li * A;
-        const int it = item0 + li;
+        const int it = s_item[li];
         int v = -1;
-        if (it < B && a < nnz[it]) v = idx[(size_t)it * A + a];
+        if (it >= 0) {
+            const int p = it >= B, b = it - p * B;
+            if (a < nnz[b]) v = (p ? idx_nstm : idx_stm)[(size_t)b * A + a];
+        }
         if ((unsigned)v >= (unsigned)N) v = -1;  // padding and out-of-range indices are skipped
         s_idx[i] = v;
     }
     __syncthreads();
-    const int item = item0 + il;
-    if (item >= B) return;
+    const int it = s_item[il];
+    if (it < 0) return;
+    const int persp = it >= B;
+    const int item = it - persp * B;  // the position
     int n = nnz[item];
     n = n < 0 ? 0 : (n > A ? A : n);
     const int* my = s_idx + il * A;
@@ -106,19 +116,22 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
 
 int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
                       const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
-                      int B, int F, int N, int A, float scale, int n_persp) {
+                      const int* items, int B, int F, int N, int A, float scale, int n_persp) {
     if (B <= 0) return 0;
     const int tpi = F / 8;
     int ipc = 256 / tpi;
     if (ipc < 1) ipc = 1;
-    dim3 grid(ceil_div(B, ipc), n_persp), block(ipc * tpi);
-    size_t smem = (size_t)ipc * A * sizeof(int);
+    const int n_items = n_persp * B;
+    dim3 grid(ceil_div(n_items, ipc)), block(ipc * tpi);
+    size_t smem = (size_t)ipc * (A + 1) * sizeof(int);
+#define FT_FWD_ARGS table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, items, n_items, B, F, N, A, scale, ipc
     switch (mode) {
-        case 0: k_ft_forward<0><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
-        case 1: k_ft_forward<1><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
-        case 2: k_ft_forward<2><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
-        default: k_ft_forward<3><<<grid, block, smem, s>>>(table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, B, F, N, A, scale, ipc); break;
+        case 0: k_ft_forward<0><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        case 1: k_ft_forward<1><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        case 2: k_ft_forward<2><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        default: k_ft_forward<3><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
     }
+#undef FT_FWD_ARGS
     return 1;
 }
 
@@ -139,50 +152,63 @@ __global__ void k_feat_count(const int* __restrict__ idx_stm, const int* __restr
     }
 }
 
-// one block per perspective: offsets[p][0..N] = exclusive prefix sum of counts[p][0..N)
-__global__ void __launch_bounds__(1024) k_feat_scan(const int* __restrict__ counts, int N, int* __restrict__ offsets,
-                                                     int* __restrict__ cursor) {
+// offsets[p][0..N] = exclusive prefix sum of counts[p][0..N), in two launches: block-local scans of 2048
+// cells with their sums, then every block adds the sums of the blocks before it.
+#define SCAN_CELLS 2048
+__global__ void __launch_bounds__(1024) k_feat_scan_local(const int* __restrict__ counts, int N, int* __restrict__ offsets,
+                                                           int* __restrict__ block_sums) {
     __shared__ int warp_tot[32];
-    __shared__ int carry;
-    const int p = blockIdx.x;
+    const int p = blockIdx.y;
     const int* c = counts + (size_t)p * N;
     int* o = offsets + (size_t)p * (N + 1);
-    int* cur = cursor + (size_t)p * N;
-    const int per = (N + blockDim.x - 1) / blockDim.x;
-    const int beg = threadIdx.x * per;
-    const int end = min(beg + per, N);
-    int sum = 0;
-    for (int i = beg; i < end; ++i) sum += c[i];
-    // block-wide exclusive scan of `sum`
+    const int i0 = blockIdx.x * SCAN_CELLS + 2 * threadIdx.x;
+    const int a = i0 < N ? c[i0] : 0, b = i0 + 1 < N ? c[i0 + 1] : 0;
+    const int sum = a + b;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     int incl = sum;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        int t = __shfl_up_sync(0xffffffffu, incl, d);
+        const int t = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= d) incl += t;
     }
     if (lane == 31) warp_tot[w] = incl;
-    if (threadIdx.x == 0) carry = 0;
     __syncthreads();
     if (w == 0) {
-        int t = lane < (blockDim.x >> 5) ? warp_tot[lane] : 0;
+        const int t = warp_tot[lane];
         int ti = t;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            int u = __shfl_up_sync(0xffffffffu, ti, d);
+            const int u = __shfl_up_sync(0xffffffffu, ti, d);
             if (lane >= d) ti += u;
         }
-        warp_tot[lane] = ti - t;  // exclusive warp offsets
-        if (lane == 31) carry = ti;
+        warp_tot[lane] = ti - t;
+        if (lane == 31) block_sums[p * gridDim.x + blockIdx.x] = ti;
     }
     __syncthreads();
-    int run = warp_tot[w] + incl - sum;
-    for (int i = beg; i < end; ++i) {
-        o[i] = run;
-        cur[i] = run;
-        run += c[i];
+    const int excl = warp_tot[w] + incl - sum;
+    if (i0 < N) o[i0] = excl;
+    if (i0 + 1 < N) o[i0 + 1] = excl + a;
+}
+
+__global__ void __launch_bounds__(1024) k_feat_scan_add(int N, int* __restrict__ offsets, int* __restrict__ cursor,
+                                                         const int* __restrict__ block_sums) {
+    __shared__ int s_off;
+    const int p = blockIdx.y;
+    int* o = offsets + (size_t)p * (N + 1);
+    int* cur = cursor + (size_t)p * N;
+    if (threadIdx.x < 32) {
+        int t = 0;
+        for (int j = threadIdx.x; j < (int)blockIdx.x; j += 32) t += block_sums[p * gridDim.x + j];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) t += __shfl_down_sync(0xffffffffu, t, d);
+        if (threadIdx.x == 0) s_off = t;
     }
-    if (threadIdx.x == 0) o[N] = carry;
+    __syncthreads();
+    const int off = s_off;
+    const int i0 = blockIdx.x * SCAN_CELLS + 2 * threadIdx.x;
+    if (i0 < N) { const int v = o[i0] + off; o[i0] = v; cur[i0] = v; }
+    if (i0 + 1 < N) { const int v = o[i0 + 1] + off; o[i0 + 1] = v; cur[i0 + 1] = v; }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) o[N] = off + block_sums[p * gridDim.x + blockIdx.x];
 }
 
 __global__ void k_feat_fill(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
@@ -322,7 +348,12 @@ int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     k_feat_count<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, counts);
-    k_feat_scan<<<n_persp, 1024, 0, s>>>(counts, N, offsets, cursor);
+    {   // block sums live behind the long-list queue (which holds at most 2N ids)
+        int* block_sums = long_queue + (size_t)2 * N;
+        const dim3 sg(ceil_div(N, SCAN_CELLS), n_persp);
+        k_feat_scan_local<<<sg, 1024, 0, s>>>(counts, N, offsets, block_sums);
+        k_feat_scan_add<<<sg, 1024, 0, s>>>(N, offsets, cursor, block_sums);
+    }
     k_feat_fill<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, cursor, lists);
     int* scratch = lists + (size_t)2 * B * A;  // the list buffer carries a second copy's worth of room
     const long long warps = (long long)n_persp * N;
@@ -335,7 +366,7 @@ int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm
         attr_set = true;
     }
     k_lists_sort_long<<<148 * 4, 256, (size_t)words * 4, s>>>(offsets, N, B, A, lists, scratch, long_queue, long_count, words);
-    return 5;
+    return 6;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -378,6 +409,134 @@ int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_ns
                        const int* lists, int B, int A, int N, int F, int n_persp, float* grad) {
     k_ft_backward<<<N, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
     return 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward with list splitting.  A feature that is active in very many positions (the king square of a
+// king bucket, a pawn in hand) makes one block walk a list of thousands of rows; with real, skewed data such
+// lists reach tens of thousands of entries and would set the kernel's run time on their own.  Features whose
+// lists (stm + nstm) exceed BWD_PART entries are cut into parts of BWD_PART entries; every part is summed
+// by its own block into a scratch row, and a last kernel adds the parts of a feature in order.  Which
+// block gets which part depends on timing, the sums do not.
+// ------------------------------------------------------------------------------------------------
+#define BWD_PART 4096
+
+__global__ void k_bwd_plan(const int* __restrict__ offsets, int N, int n_persp, int* __restrict__ counters,
+                           int2* __restrict__ work, int* __restrict__ longf) {
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= N) return;
+    int len = 0;
+    for (int p = 0; p < n_persp; ++p) len += offsets[(size_t)p * (N + 1) + f + 1] - offsets[(size_t)p * (N + 1) + f];
+    if (len <= BWD_PART) return;
+    const int parts = (len + BWD_PART - 1) / BWD_PART;
+    const int base = atomicAdd(&counters[0], parts);
+    const int q = atomicAdd(&counters[1], 1);
+    longf[3 * q + 0] = f;
+    longf[3 * q + 1] = base;
+    longf[3 * q + 2] = parts;
+    for (int i = 0; i < parts; ++i) work[base + i] = make_int2(f, i);
+}
+
+static __device__ __forceinline__ float4 sum_rows(const float4* __restrict__ d, const int* __restrict__ L, int beg, int end,
+                                                  int row4, int c, float4 acc) {
+    for (int j = beg; j < end; j += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (j + u < end) {
+                const int b = __ldg(L + j + u);
+                v[u] = __ldg(d + (size_t)b * row4 + c);
+            } else {
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+        }
+    }
+    return acc;
+}
+
+__global__ void __launch_bounds__(1024) k_ft_backward_short(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+                                                             const int* __restrict__ offsets, const int* __restrict__ lists,
+                                                             int B, int A, int N, int F, int n_persp, float* __restrict__ grad) {
+    const int f = blockIdx.x;
+    const int c = threadIdx.x;
+    const int row4 = F >> 2;
+    int beg[2], end[2], len = 0;
+    for (int p = 0; p < n_persp; ++p) {
+        beg[p] = offsets[(size_t)p * (N + 1) + f];
+        end[p] = offsets[(size_t)p * (N + 1) + f + 1];
+        len += end[p] - beg[p];
+    }
+    if (len > BWD_PART) return;  // summed in parts by k_ft_backward_long
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < n_persp; ++p)
+        acc = sum_rows(reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm), lists + (size_t)p * B * A, beg[p], end[p], row4, c, acc);
+    reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
+}
+
+__global__ void __launch_bounds__(1024) k_ft_backward_long(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+                                                            const int* __restrict__ offsets, const int* __restrict__ lists,
+                                                            int B, int A, int N, int F, int n_persp,
+                                                            const int* __restrict__ counters, const int2* __restrict__ work,
+                                                            float* __restrict__ partial) {
+    const int c = threadIdx.x;
+    const int row4 = F >> 2;
+    const int n_work = counters[0];
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+        const int2 wk = work[w];
+        const int f = wk.x;
+        int lo = wk.y * BWD_PART, hi = lo + BWD_PART;  // range in the concatenated (stm, nstm) list
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < n_persp; ++p) {
+            const int beg = offsets[(size_t)p * (N + 1) + f], len = offsets[(size_t)p * (N + 1) + f + 1] - beg;
+            const int a = max(lo, 0), b = min(hi, len);
+            if (a < b)
+                acc = sum_rows(reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm), lists + (size_t)p * B * A, beg + a, beg + b,
+                               row4, c, acc);
+            lo -= len;
+            hi -= len;
+        }
+        reinterpret_cast<float4*>(partial)[(size_t)w * row4 + c] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(1024) k_ft_backward_long_final(const int* __restrict__ counters, const int* __restrict__ longf,
+                                                                  const float* __restrict__ partial, int F,
+                                                                  float* __restrict__ grad) {
+    const int c = threadIdx.x;
+    const int row4 = F >> 2;
+    const int n_long = counters[1];
+    const float4* p4 = reinterpret_cast<const float4*>(partial);
+    for (int q = blockIdx.x; q < n_long; q += gridDim.x) {
+        const int f = longf[3 * q], base = longf[3 * q + 1], parts = longf[3 * q + 2];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < parts; ++i) {
+            const float4 v = p4[(size_t)(base + i) * row4 + c];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
+    }
+}
+
+int ft_backward_max_work(int B, int A, int n_persp) { return 2 * (int)(((long long)n_persp * B * A) / BWD_PART) + 2; }
+
+// plan: [2] counters, then [2 * max_work] work items, then [3 * N] long-feature records; partial: [max_work][F]
+int launch_ft_backward_split(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
+                             const int* lists, int B, int A, int N, int F, int n_persp, int* plan, float* partial,
+                             float* grad) {
+    const int max_work = ft_backward_max_work(B, A, n_persp);
+    int* counters = plan;
+    int2* work = reinterpret_cast<int2*>(plan + 2);
+    int* longf = plan + 2 + 2 * max_work;
+    cudaMemsetAsync(counters, 0, 2 * sizeof(int), s);
+    k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf);
+    k_ft_backward_short<<<N, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
+    k_ft_backward_long<<<148 * 4, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial);
+    k_ft_backward_long_final<<<148 * 2, F / 4, 0, s>>>(counters, longf, partial, F, grad);
+    return 4;
 }
 
 // ft_reduce_virtual_grad (sparse/ft_factorize.rs:109-121): grad[N + v] = sum over king buckets of grad[kb*pi + v]

@@ -1,0 +1,181 @@
+// Small-key stable counting sorts over many blocks (keys < 128):
+//  - positions by LayerStack bucket  -> `order`, bucket segments, dense tiles and work units
+//    (replaces count_buckets / exclusive_scan_aligned / scatter_bucket_perm, native_kernels.cu:1858-1925)
+//  - (position, perspective) items by the king bucket of their feature rows -> `items`, so that blocks that
+//    run at the same time gather from the same slice of the FT table and the slice stays in L2.
+// Three launches each: per-block histogram, one-block scan of the [key][block] matrix, stable scatter
+// (rank inside a block = warp match + prefix over the block's warps).  Results do not depend on timing.
+#include "common.cuh"
+
+#define SORT_BLOCK 1024
+#define SORT_MAX_KEYS 128
+#define UNIT_TILES 8  // tiles per work unit of the L1 weight-gradient kernel
+
+struct BucketKey {
+    const int* bucket;  // may be NULL: one group
+    int nb;
+    __device__ int operator()(int i) const {
+        const int k = bucket ? bucket[i] : 0;
+        return (unsigned)k < (unsigned)nb ? k : nb;  // out-of-range ids form the last group
+    }
+};
+
+// item i < B is the stm perspective of position i, item B + b the nstm perspective of position b.  The key is
+// the table slice (index / rows_per_slice) of the item's first feature; items without one go last.
+struct ItemKey {
+    const int* idx_stm;
+    const int* idx_nstm;
+    const int* nnz;
+    int B, A, N, rows_per_slice, n_slices;
+    __device__ int operator()(int i) const {
+        const int p = i >= B, b = i - p * B;
+        if (nnz[b] <= 0) return n_slices;
+        const int f = (p ? idx_nstm : idx_stm)[(size_t)b * A];
+        return (unsigned)f < (unsigned)N ? f / rows_per_slice : n_slices;
+    }
+};
+
+template <class KeyFn>
+__global__ void __launch_bounds__(SORT_BLOCK) k_sort_hist(KeyFn fn, int n, int K, int G, int* __restrict__ hist) {
+    __shared__ int s_h[SORT_MAX_KEYS];
+    if (threadIdx.x < SORT_MAX_KEYS) s_h[threadIdx.x] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * SORT_BLOCK + threadIdx.x;
+    if (i < n) atomicAdd(&s_h[fn(i)], 1);
+    __syncthreads();
+    if ((int)threadIdx.x < K) hist[threadIdx.x * G + blockIdx.x] = s_h[threadIdx.x];
+}
+
+// exclusive scan of hist[K][G] in key-major order (in place); seg_start[k] = first output slot of key k
+__global__ void __launch_bounds__(1024) k_sort_scan(int* __restrict__ hist, int K, int G, int n, int* __restrict__ seg_start) {
+    __shared__ int s_warp[32];
+    const int total = K * G;
+    const int per = (total + 1023) / 1024;
+    const int beg = min((int)threadIdx.x * per, total), end = min(beg + per, total);
+    int sum = 0;
+    for (int i = beg; i < end; ++i) sum += hist[i];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += t;
+    }
+    if (lane == 31) s_warp[w] = incl;
+    __syncthreads();
+    if (w == 0) {
+        const int t = s_warp[lane];
+        int ti = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, ti, d);
+            if (lane >= d) ti += u;
+        }
+        s_warp[lane] = ti - t;
+    }
+    __syncthreads();
+    int run = s_warp[w] + incl - sum;
+    for (int i = beg; i < end; ++i) {
+        const int c = hist[i];
+        hist[i] = run;
+        if (i % G == 0) seg_start[i / G] = run;
+        run += c;
+    }
+    if (threadIdx.x == 0) seg_start[K] = n;
+}
+
+template <class KeyFn>
+__global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, int K, int G, const int* __restrict__ base,
+                                                             int* __restrict__ out) {
+    __shared__ int s_cnt[32][SORT_MAX_KEYS];
+    for (int e = threadIdx.x; e < 32 * SORT_MAX_KEYS; e += SORT_BLOCK) (&s_cnt[0][0])[e] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * SORT_BLOCK + threadIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int key = i < n ? fn(i) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (rank == 0 && key >= 0) s_cnt[w][key] = __popc(peers);
+    __syncthreads();
+    if ((int)threadIdx.x < K) {
+        int run = 0;
+        for (int ww = 0; ww < 32; ++ww) {
+            const int c = s_cnt[ww][threadIdx.x];
+            s_cnt[ww][threadIdx.x] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    if (key >= 0) out[base[key * G + blockIdx.x] + s_cnt[w][key] + rank] = i;
+}
+
+// tiles: runs of <= TB_TILE_M positions of one bucket; units: runs of <= UNIT_TILES tiles of one bucket
+__global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_start, int K, TileDesc* __restrict__ tiles,
+                                                     int* __restrict__ n_tiles, TileDesc* __restrict__ units,
+                                                     int* __restrict__ n_units) {
+    __shared__ int s_tile_base[SORT_MAX_KEYS + 1], s_unit_base[SORT_MAX_KEYS + 1];
+    if (threadIdx.x == 0) {
+        int trun = 0, urun = 0;
+        for (int k = 0; k < K; ++k) {
+            s_tile_base[k] = trun;
+            s_unit_base[k] = urun;
+            const int nt = (seg_start[k + 1] - seg_start[k] + TB_TILE_M - 1) / TB_TILE_M;
+            trun += nt;
+            urun += (nt + UNIT_TILES - 1) / UNIT_TILES;
+        }
+        *n_tiles = trun;
+        *n_units = urun;
+    }
+    __syncthreads();
+    for (int k = 0; k < K; ++k) {
+        const int s0 = seg_start[k], c = seg_start[k + 1] - s0;
+        const int nt = (c + TB_TILE_M - 1) / TB_TILE_M;
+        for (int t = threadIdx.x; t < nt; t += blockDim.x) {
+            TileDesc d;
+            d.start = s0 + t * TB_TILE_M;
+            d.count = min(TB_TILE_M, c - t * TB_TILE_M);
+            d.bucket = k;
+            d.pad = 0;
+            tiles[s_tile_base[k] + t] = d;
+        }
+        const int nu = (nt + UNIT_TILES - 1) / UNIT_TILES;
+        for (int u = threadIdx.x; u < nu; u += blockDim.x) {
+            TileDesc d;
+            d.start = s_tile_base[k] + u * UNIT_TILES;
+            d.count = min(UNIT_TILES, nt - u * UNIT_TILES);
+            d.bucket = k;
+            d.pad = 0;
+            units[s_unit_base[k] + u] = d;
+        }
+    }
+}
+
+int sort_max_units(int max_tiles) { return max_tiles / UNIT_TILES + TB_MAX_BUCKETS + 2; }
+
+// hist: scratch of (nb + 1) * ceil(B / 1024) ints
+int launch_bucket_sort(cudaStream_t s, const int* bucket, int B, int nb, int* order, TileDesc* tiles, int* n_tiles,
+                       int* seg_start, int max_tiles, int* hist) {
+    const int K = nb + 1, G = ceil_div(B, SORT_BLOCK);
+    BucketKey fn{bucket, nb};
+    k_sort_hist<<<G, SORT_BLOCK, 0, s>>>(fn, B, K, G, hist);
+    k_sort_scan<<<1, 1024, 0, s>>>(hist, K, G, B, seg_start);
+    k_sort_scatter<<<G, SORT_BLOCK, 0, s>>>(fn, B, K, G, hist, order);
+    k_make_tiles<<<1, 256, 0, s>>>(seg_start, K, tiles, n_tiles, tiles + max_tiles, n_tiles + 1);
+    return 4;
+}
+
+// items[2B] sorted by table slice; hist: scratch of (n_slices + 1) * ceil(2B / 1024) ints; seg: [n_slices + 2]
+int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,
+                     int rows_per_slice, int n_persp, int* items, int* hist, int* seg) {
+    int n_slices = ceil_div(N, rows_per_slice);
+    if (n_slices + 1 > SORT_MAX_KEYS) {  // too many slices for the small-key sort: coarser slices keep most of the locality
+        rows_per_slice = ceil_div(N, SORT_MAX_KEYS - 1);
+        n_slices = ceil_div(N, rows_per_slice);
+    }
+    const int n = n_persp * B, K = n_slices + 1, G = ceil_div(n, SORT_BLOCK);
+    ItemKey fn{idx_stm, idx_nstm, nnz, B, A, N, rows_per_slice, n_slices};
+    k_sort_hist<<<G, SORT_BLOCK, 0, s>>>(fn, n, K, G, hist);
+    k_sort_scan<<<1, 1024, 0, s>>>(hist, K, G, n, seg);
+    k_sort_scatter<<<G, SORT_BLOCK, 0, s>>>(fn, n, K, G, hist, items);
+    return 3;
+}

@@ -119,6 +119,8 @@ struct tb_trainer {
     TileDesc* tiles = nullptr;
     float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr;
     int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
+    int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr;
+    float* bwd_partial = nullptr;
     int last_n = 0;
     // loss ring (AsyncLossRing, trainer_common.rs:909-1000)
     double* loss_pinned[2] = {nullptr, nullptr};
@@ -300,12 +302,16 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     const float* table = c.ft_factorize ? t->comb : t->groups[0].w;
     t->last_n = B;
     { PhaseScope p(t, PH_SORT);
-      p.done(launch_bucket_sort(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
-                                t->seg_start, t->max_tiles)); }
+      int n = launch_bucket_sort(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
+                                 t->seg_start, t->max_tiles, t->sort_hist);
+      // items of both perspectives ordered by the king-bucket slice of the FT table they read
+      n += launch_item_sort(t->stream, d.stm, d.nstm, d.nnz, B, A, N, c.piece_inputs > 0 ? c.piece_inputs : N, 2, t->items,
+                            t->sort_hist, t->item_seg);
+      p.done(n); }
     { PhaseScope p(t, PH_FT_FWD);
       const int mode = ls ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
       p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1], t->combined,
-                               B, F, N, A, FT_POST_SCALE, 2)); }
+                               t->items, B, F, N, A, FT_POST_SCALE, 2)); }
     const LossParams lp = make_loss(loss, lambda, d.norm);
     if (ls) {
         { PhaseScope p(t, PH_L1_FWD);
@@ -363,7 +369,8 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
       p.done(launch_inverse_index(t->stream, d.stm, d.nstm, d.nnz, B, A, N, 2, t->feat_counts, t->feat_offsets, t->feat_cursor,
                                   t->feat_lists)); }
     { PhaseScope p(t, PH_FT_BWD);
-      p.done(launch_ft_backward(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->groups[0].grad)); }
+      p.done(launch_ft_backward_split(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->bwd_plan,
+                                      t->bwd_partial, t->groups[0].grad)); }
     return TB_OK;
 }
 
@@ -501,6 +508,7 @@ void free_all(tb_trainer* t) {
     cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
     cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials);
     cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
+    cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
     if (t->ev_t0) cudaEventDestroy(t->ev_t0);
     if (t->ev_t1) cudaEventDestroy(t->ev_t1);
     for (int i = 0; i < PH_COUNT; ++i) {
@@ -594,14 +602,20 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->tail_b, B * l2)); CU(t, dalloc(&t->tail_c, B * l2));
     CU(t, dalloc(&t->loss_partials, B / 128 + 2)); CU(t, dalloc(&t->loss_acc, 1));
     t->max_tiles = (int)(B / TB_TILE_M) + TB_MAX_BUCKETS + 2;
-    t->max_units = t->max_tiles / 16 + TB_MAX_BUCKETS + 2;
+    t->max_units = sort_max_units(t->max_tiles);
     CU(t, dalloc(&t->order, B)); CU(t, dalloc(&t->n_tiles, 2)); CU(t, dalloc(&t->seg_start, TB_MAX_BUCKETS + 3));
     CU(t, dalloc(&t->tiles, (size_t)t->max_tiles + t->max_units));
     const size_t n_cells = ls ? (size_t)(l2 * t->l2in + 2 * l2 + 1 + l1) : (size_t)(l1 * l2 + 2 * l2 + 1 + l1);
     CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 16 : (size_t)128) * n_cells));
     CU(t, dalloc(&t->l1w_partials, (size_t)t->max_units * l1 * t->K));
     CU(t, dalloc(&t->bias_partials, (size_t)DGRAD_CTAS * 2 * F));
-    CU(t, dalloc(&t->feat_counts, (size_t)4 * N + 1)); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
+    CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
+    CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
+    {
+        const size_t max_work = (size_t)ft_backward_max_work((int)B, (int)A, 2);
+        CU(t, dalloc(&t->bwd_plan, 2 + 2 * max_work + 3 * (size_t)N));
+        CU(t, dalloc(&t->bwd_partial, max_work * (size_t)F));
+    }
     CU(t, dalloc(&t->feat_cursor, (size_t)2 * N)); CU(t, dalloc(&t->feat_lists, (size_t)4 * B * A));
     CU(t, cudaEventCreate(&t->ev_t0)); CU(t, cudaEventCreate(&t->ev_t1));
     for (int i = 0; i < PH_COUNT; ++i) {
@@ -957,10 +971,10 @@ int tb_ft_forward_bench(int device, const float* table, const int32_t* indices, 
     CUX(cudaMemcpy(d_i, indices, B * A * 4, cudaMemcpyHostToDevice));
     CUX(cudaMemcpy(d_n, nnz, B * 4, cudaMemcpyHostToDevice));
     CUX(cudaEventCreate(&e0)); CUX(cudaEventCreate(&e1));
-    launch_ft_forward(0, 0, d_t, d_i, d_i, d_n, nullptr, d_o, d_o, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1);
+    launch_ft_forward(0, 0, d_t, d_i, d_i, d_n, nullptr, d_o, d_o, nullptr, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1);
     CUX(cudaDeviceSynchronize());
     CUX(cudaEventRecord(e0, 0));
-    for (int i = 0; i < iters; ++i) launch_ft_forward(0, 0, d_t, d_i, d_i, d_n, nullptr, d_o, d_o, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1);
+    for (int i = 0; i < iters; ++i) launch_ft_forward(0, 0, d_t, d_i, d_i, d_n, nullptr, d_o, d_o, nullptr, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1);
     CUX(cudaEventRecord(e1, 0));
     CUX(cudaEventSynchronize(e1));
     { float ms = 0.f; CUX(cudaEventElapsedTime(&ms, e0, e1)); if (ms_per_iter) *ms_per_iter = ms / iters; }
@@ -977,13 +991,16 @@ int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, c
     if (!dft || !indices || !nnz || batch < 1 || ft_out % 128 != 0 || iters < 1) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad argument");
     int rc = TB_OK;
     float *d_d = nullptr, *d_g = nullptr;
-    int *d_i = nullptr, *d_n = nullptr, *d_cnt = nullptr, *d_off = nullptr, *d_cur = nullptr, *d_lists = nullptr;
+    int *d_i = nullptr, *d_n = nullptr, *d_cnt = nullptr, *d_off = nullptr, *d_cur = nullptr, *d_lists = nullptr, *d_plan = nullptr;
+    float* d_part = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     const size_t B = batch, F = ft_out, N = ft_in, A = max_active;
+    const size_t max_work = (size_t)ft_backward_max_work(batch, max_active, 1);
     CUX(cudaSetDevice(device));
     CUX(cudaMalloc(&d_d, B * F * 4)); CUX(cudaMalloc(&d_g, N * F * 4)); CUX(cudaMalloc(&d_i, B * A * 4)); CUX(cudaMalloc(&d_n, B * 4));
-    CUX(cudaMalloc(&d_cnt, (4 * N + 1) * 4)); CUX(cudaMalloc(&d_off, 2 * (N + 1) * 4)); CUX(cudaMalloc(&d_cur, 2 * N * 4));
+    CUX(cudaMalloc(&d_cnt, inverse_index_counts_len(ft_in) * 4)); CUX(cudaMalloc(&d_off, 2 * (N + 1) * 4)); CUX(cudaMalloc(&d_cur, 2 * N * 4));
     CUX(cudaMalloc(&d_lists, 4 * B * A * 4));
+    CUX(cudaMalloc(&d_plan, (2 + 2 * max_work + 3 * N) * 4)); CUX(cudaMalloc(&d_part, max_work * F * 4));
     CUX(cudaMemcpy(d_d, dft, B * F * 4, cudaMemcpyHostToDevice));
     CUX(cudaMemcpy(d_i, indices, B * A * 4, cudaMemcpyHostToDevice));
     CUX(cudaMemcpy(d_n, nnz, B * 4, cudaMemcpyHostToDevice));
@@ -991,7 +1008,7 @@ int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, c
     for (int i = -1; i < iters; ++i) {
         if (i == 0) { CUX(cudaDeviceSynchronize()); CUX(cudaEventRecord(e0, 0)); }
         launch_inverse_index(0, d_i, d_i, d_n, batch, max_active, ft_in, 1, d_cnt, d_off, d_cur, d_lists);
-        launch_ft_backward(0, d_d, d_d, d_off, d_lists, batch, max_active, ft_in, ft_out, 1, d_g);
+        launch_ft_backward_split(0, d_d, d_d, d_off, d_lists, batch, max_active, ft_in, ft_out, 1, d_plan, d_part, d_g);
     }
     CUX(cudaEventRecord(e1, 0));
     CUX(cudaEventSynchronize(e1));
@@ -999,6 +1016,7 @@ int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, c
     if (grad) CUX(cudaMemcpy(grad, d_g, N * F * 4, cudaMemcpyDeviceToHost));
 done:
     cudaFree(d_d); cudaFree(d_g); cudaFree(d_i); cudaFree(d_n); cudaFree(d_cnt); cudaFree(d_off); cudaFree(d_cur); cudaFree(d_lists);
+    cudaFree(d_plan); cudaFree(d_part);
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     return rc;

@@ -139,7 +139,7 @@ def test_ft_backward_matches_oracle(F, B, A, N):
 
 def test_ft_backward_hot_feature_long_list():
     # one feature in every position (the king feature of a king bucket): exercises the long-list path
-    F, B, A, N = 256, 4096, 4, 64
+    F, B, A, N = 256, 16384, 4, 64
     rng = np.random.default_rng(5)
     dft = (rng.standard_normal((B, F)) * 1e-3).astype(np.float32)
     idx = np.stack([np.full(B, 7), rng.integers(8, N, B), rng.integers(8, N, B), np.full(B, -1)], 1).astype(np.int32)
@@ -148,7 +148,11 @@ def test_ft_backward_hot_feature_long_list():
     O.lib().ora_sparse_ft_backward(dft.reshape(-1), np.where(np.arange(A)[None] < 3, idx, -1).astype(np.int32).reshape(-1),
                                    want.reshape(-1), B, F, N, A)
     got = _ft_backward(dft, idx, nnz, N, F, A)
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # lists longer than 4096 entries are summed in parts: same terms, different association
+    assert_close_scaled(got, want, 1e-5, "hot feature")
+    assert np.array_equal(got[8:].view(np.uint32), want[8:].view(np.uint32))     # short lists stay bit-exact
+    again = _ft_backward(dft, idx, nnz, N, F, A)
+    assert np.array_equal(got.view(np.uint32), again.view(np.uint32))            # and the result is reproducible
 
 
 def test_adam_clamp_matches_oracle():
