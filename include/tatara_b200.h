@@ -183,6 +183,23 @@ int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, c
 int tb_adam_clamp_bench(int device, float* w, float* m, float* v, const float* grad, int64_t n, float lr,
                         float decay, float min_w, float max_w, int iters, float* ms_per_iter);
 
+/* ---- FT weight gradient without any allocation -------------------------------------------
+ * No counterpart in the reference (its trainers allocate their workspace in the constructor).
+ * For hosts that must not allocate device memory once they run — a framework whose allocator owns the
+ * whole GPU, a process with a fixed memory plan — this variant of the FT backward keeps the working
+ * memory of the inverse index in a static device array inside the library (about 14.7 MB per GPU, held
+ * until exit) and calls no cudaMalloc / cudaFree.  ALL pointers are DEVICE memory owned by the caller;
+ * the work is enqueued on `stream` (a cudaStream_t, NULL = default stream) and not synchronised.
+ * Limits: ft_in <= TB_STATIC_SCRATCH_MAX_FT_IN and batch * max_active <= TB_STATIC_SCRATCH_MAX_PAIRS;
+ * beyond them the call fails and writes the reason to err (may be NULL).  Calls share the one array:
+ * never let two of them overlap on a GPU.  The first call on a device resolves the array's address;
+ * issue it before any stream capture.  Same result as tb_ft_backward_bench. */
+#define TB_STATIC_SCRATCH_MAX_FT_IN 131072
+#define TB_STATIC_SCRATCH_MAX_PAIRS 655360
+int tb_ft_backward_static_scratch(const float* d_dft, const int32_t* d_indices, const int32_t* d_nnz, int batch,
+                                  int ft_out, int ft_in, int max_active, float* d_grad, void* stream, char* err,
+                                  size_t err_len);
+
 /* ---- inputs: PackedSfenValue records -> step inputs, on the device ---------------------
  * Decodes 40-byte records (crates/shogi-format/src/packed_sfen.rs:387-448) and extracts the active
  * feature indices of both perspectives (crates/shogi-features/src/feature_set.rs:655-808), the

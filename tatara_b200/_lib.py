@@ -87,6 +87,7 @@ SIGNATURES = {
     "tb_init_sample": (C.c_int, [vp, i64, i64, i64, C.c_int, C.c_int, f, C.c_int, C.c_uint64]),
     "tb_host_alloc": (C.c_int, [C.POINTER(vp), C.c_size_t]),
     "tb_host_free": (C.c_int, [vp]),
+    "tb_ft_backward_static_scratch": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, C.c_char_p, C.c_size_t]),
     "tb_nccl_unique_id": (C.c_int, [vp]),
     "tb_device_count": (C.c_int, []),
     "tb_version": (C.c_char_p, []),

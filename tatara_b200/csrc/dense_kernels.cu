@@ -843,15 +843,28 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
             sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
         }
         __syncthreads();
+        // the pre-activations of the next two positions are requested before the current two are processed
+        float4 xa_n[2], xb_n[2];
+        int pp_n[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            pp_n[q] = q < td.count ? s_pos[q] : -1;
+            xa_n[q] = xb_n[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (pp_n[q] >= 0) {
+                xa_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol));
+                if (MODE == 1) xb_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol));
+            }
+        }
         for (int r0 = 0; r0 < td.count; r0 += 2) {
             float4 xa[2], xb[2];
             int pp[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-                pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
-                if (pp[q] >= 0) {
-                    xa[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + wcol);
-                    if (MODE == 1) xb[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + half + wcol);
+                xa[q] = xa_n[q]; xb[q] = xb_n[q]; pp[q] = pp_n[q];
+                pp_n[q] = r0 + 2 + q < td.count ? s_pos[r0 + 2 + q] : -1;
+                if (pp_n[q] >= 0) {
+                    xa_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol));
+                    if (MODE == 1) xb_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol));
                 }
             }
             float4 dd[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
@@ -877,7 +890,7 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
                     gb.y = (b.y > 0.f && b.y < 1.f) ? d.y * crelu01(a.y) * scale : 0.f;
                     gb.z = (b.z > 0.f && b.z < 1.f) ? d.z * crelu01(a.z) * scale : 0.f;
                     gb.w = (b.w > 0.f && b.w < 1.f) ? d.w * crelu01(a.w) * scale : 0.f;
-                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = ga;
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = ga;   // re-read 40 times by the FT backward: keep in L2
                     *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + half + wcol) = gb;
                     bacc0.x += ga.x; bacc0.y += ga.y; bacc0.z += ga.z; bacc0.w += ga.w;
                     bacc1.x += gb.x; bacc1.y += gb.y; bacc1.z += gb.z; bacc1.w += gb.w;

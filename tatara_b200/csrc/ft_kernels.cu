@@ -77,14 +77,15 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
     }
 
     float4* pre = reinterpret_cast<float4*>(persp ? pre_nstm : pre_stm) + (size_t)item * row4;
+    // outputs are written once and read by later kernels only: streaming stores leave L2 to the table slice
     if (MODE == 0) {
-        pre[c0] = acc0;
-        pre[c1] = acc1;
+        __stcs(pre + c0, acc0);
+        __stcs(pre + c1, acc1);
     } else if (MODE == 1) {
         // ft_post_perspective_fwd (layerstack/ft_post_perspective.rs:57-83): the raw sums are kept for the
         // backward pass, combined[b, persp*F/2 + r] = crelu(x_r + b_r) * crelu(x_{r+F/2} + b_{r+F/2}) * scale
-        pre[c0] = acc0;
-        pre[c1] = acc1;
+        __stcs(pre + c0, acc0);
+        __stcs(pre + c1, acc1);
         const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias) + c0);
         const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + c1);
         float4 o;
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
         o.y = crelu01(acc0.y + b0.y) * crelu01(acc1.y + b1.y) * scale;
         o.z = crelu01(acc0.z + b0.z) * crelu01(acc1.z + b1.z) * scale;
         o.w = crelu01(acc0.w + b0.w) * crelu01(acc1.w + b1.w) * scale;
-        reinterpret_cast<float4*>(combined)[(size_t)item * row4 + persp * tpi + c0] = o;
+        __stcs(reinterpret_cast<float4*>(combined) + (size_t)item * row4 + persp * tpi + c0, o);
     } else {
         // simple_ft_post_fused_{crelu,screlu} (native_kernels.cu:1406-1450): the biased value replaces the
         // raw sum, combined[b, persp*F + c] = act(x)
@@ -100,8 +101,8 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
         const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + c1);
         float4 x0 = make_float4(acc0.x + b0.x, acc0.y + b0.y, acc0.z + b0.z, acc0.w + b0.w);
         float4 x1 = make_float4(acc1.x + b1.x, acc1.y + b1.y, acc1.z + b1.z, acc1.w + b1.w);
-        pre[c0] = x0;
-        pre[c1] = x1;
+        __stcs(pre + c0, x0);
+        __stcs(pre + c1, x1);
         float4 a0 = make_float4(crelu01(x0.x), crelu01(x0.y), crelu01(x0.z), crelu01(x0.w));
         float4 a1 = make_float4(crelu01(x1.x), crelu01(x1.y), crelu01(x1.z), crelu01(x1.w));
         if (MODE == 3) {
@@ -109,8 +110,8 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
             a1.x *= a1.x; a1.y *= a1.y; a1.z *= a1.z; a1.w *= a1.w;
         }
         float4* comb = reinterpret_cast<float4*>(combined) + (size_t)item * (2 * row4) + persp * row4;
-        comb[c0] = a0;
-        comb[c1] = a1;
+        __stcs(comb + c0, a0);
+        __stcs(comb + c1, a1);
     }
 }
 
@@ -474,7 +475,7 @@ __global__ void __launch_bounds__(1024) k_ft_backward_short(const float* __restr
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < n_persp; ++p)
         acc = sum_rows(reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm), lists + (size_t)p * B * A, beg[p], end[p], row4, c, acc);
-    reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
+    __stcs(reinterpret_cast<float4*>(grad) + (size_t)f * row4 + c, acc);
 }
 
 __global__ void __launch_bounds__(1024) k_ft_backward_long(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,

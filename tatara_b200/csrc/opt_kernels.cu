@@ -113,17 +113,19 @@ __global__ void __launch_bounds__(1024) k_radam_factorized(float4* __restrict__ 
     const float decay_mul = 1.0f - sc.decay * rate;
     const int KB = N / pi;
     float4 gsum = make_float4(0.f, 0.f, 0.f, 0.f);
+    // m, v and the gradient stream through once: evict-first loads / stores keep them from pushing the freshly
+    // written weights out of L2 before pass 2 reads them back
 #pragma unroll 4
     for (int kb = 0; kb < KB; ++kb) {
         const size_t i = (size_t)(kb * pi + vr) * row4 + c;
-        const float4 gi = g[i];
-        float4 mi = m[i], vi = v[i];
+        const float4 gi = __ldcs(g + i);
+        float4 mi = __ldcs(m + i), vi = __ldcs(v + i);
         float4 p = radam_four(w[i], mi, vi, gi, sc, rate, decay_mul);
-        m[i] = mi;
-        v[i] = vi;
+        __stcs(m + i, mi);
+        __stcs(v + i, vi);
         if (sc.lerp) {
-            p = lerp_four(p, slow[i], sc.alpha);
-            slow[i] = p;
+            p = lerp_four(p, __ldcs(slow + i), sc.alpha);
+            __stcs(slow + i, p);
         }
         w[i] = p;
         gsum.x += gi.x; gsum.y += gi.y; gsum.z += gi.z; gsum.w += gi.w;
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(1024) k_radam_factorized(float4* __restrict__ 
     for (int kb = 0; kb < KB; ++kb) {
         const size_t i = (size_t)(kb * pi + vr) * row4 + c;
         const float4 p = w[i];
-        comb[i] = make_float4(p.x + pv.x, p.y + pv.y, p.z + pv.z, p.w + pv.w);
+        __stcs(comb + i, make_float4(p.x + pv.x, p.y + pv.y, p.z + pv.z, p.w + pv.w));
     }
 }
 
