@@ -8,6 +8,8 @@
 // rows through `order` and write results back at the position's own row.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 #define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
 #define L1_SQR_SCALE (127.0f / 128.0f)
 
@@ -795,7 +797,7 @@ int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, con
 // grid (n_ctas, 2 perspectives, column chunks); a block walks the tiles t = blockIdx.x, += gridDim.x and
 // keeps the effective weights of the current bucket in shared memory.
 // ------------------------------------------------------------------------------------------------
-template <int MODE>
+template <int MODE, bool PF>
 __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict__ dl1, const int* __restrict__ order,
                                                           const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
                                                           const float* __restrict__ wb, const float* __restrict__ ws,
@@ -843,16 +845,19 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
             sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
         }
         __syncthreads();
-        // the pre-activations of the next two positions are requested before the current two are processed
+        // PF: the pre-activations of the next two positions are requested before the current two are processed
         float4 xa_n[2], xb_n[2];
         int pp_n[2];
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-            pp_n[q] = q < td.count ? s_pos[q] : -1;
+            pp_n[q] = -1;
             xa_n[q] = xb_n[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (pp_n[q] >= 0) {
-                xa_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol));
-                if (MODE == 1) xb_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol));
+            if (PF) {
+                pp_n[q] = q < td.count ? s_pos[q] : -1;
+                if (pp_n[q] >= 0) {
+                    xa_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol);
+                    if (MODE == 1) xb_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol);
+                }
             }
         }
         for (int r0 = 0; r0 < td.count; r0 += 2) {
@@ -860,11 +865,19 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
             int pp[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-                xa[q] = xa_n[q]; xb[q] = xb_n[q]; pp[q] = pp_n[q];
-                pp_n[q] = r0 + 2 + q < td.count ? s_pos[r0 + 2 + q] : -1;
-                if (pp_n[q] >= 0) {
-                    xa_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol));
-                    if (MODE == 1) xb_n[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol));
+                if (PF) {
+                    xa[q] = xa_n[q]; xb[q] = xb_n[q]; pp[q] = pp_n[q];
+                    pp_n[q] = r0 + 2 + q < td.count ? s_pos[r0 + 2 + q] : -1;
+                    if (pp_n[q] >= 0) {
+                        xa_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol);
+                        if (MODE == 1) xb_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol);
+                    }
+                } else {
+                    pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
+                    if (pp[q] >= 0) {
+                        xa[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + wcol);
+                        if (MODE == 1) xb[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + half + wcol);
+                    }
                 }
             }
             float4 dd[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
@@ -945,16 +958,17 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
     const int CW = work_cols / n_chunks;
     const size_t smem = (size_t)CW * l1 * sizeof(float);
     dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
-    if (mode == 1) {
-        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        k_l1_dgrad_ftgrad<1><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);
-    } else if (mode == 2) {
-        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        k_l1_dgrad_ftgrad<2><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);
-    } else {
-        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-        k_l1_dgrad_ftgrad<3><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);
-    }
+    static const bool pf = getenv("TATARA_DEBUG_DGRAD_PF") != nullptr;
+#define DGRAD_LAUNCH(M, P)                                                                                               \
+    do {                                                                                                                 \
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<M, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);           \
+        k_l1_dgrad_ftgrad<M, P><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, \
+                                                         scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);        \
+    } while (0)
+    if (mode == 1) { if (pf) DGRAD_LAUNCH(1, true); else DGRAD_LAUNCH(1, false); }
+    else if (mode == 2) { if (pf) DGRAD_LAUNCH(2, true); else DGRAD_LAUNCH(2, false); }
+    else { if (pf) DGRAD_LAUNCH(3, true); else DGRAD_LAUNCH(3, false); }
+#undef DGRAD_LAUNCH
     k_bias_partials_reduce<<<ceil_div(F, 256), 256, 0, s>>>(bias_partials, n_ctas, F, ft_b_grad);
     return 2;
 }

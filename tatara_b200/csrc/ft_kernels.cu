@@ -375,11 +375,11 @@ int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm
 // written exactly once per step (stm list first, then nstm list, each in ascending position order —
 // the accumulation order of sparse_ft_backward_cpu called for stm then nstm).
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) k_ft_backward(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+__global__ void __launch_bounds__(512) k_ft_backward(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
                                                        const int* __restrict__ offsets, const int* __restrict__ lists,
                                                        int B, int A, int N, int F, int n_persp, float* __restrict__ grad) {
     const int f = blockIdx.x;
-    const int c = threadIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < n_persp; ++p) {
@@ -387,19 +387,17 @@ __global__ void __launch_bounds__(1024) k_ft_backward(const float* __restrict__ 
         const int* __restrict__ L = lists + (size_t)p * B * A;
         const float4* __restrict__ d = reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm);
         for (int j = beg; j < end; j += 8) {
+            // unconditional loads (a slot past the end re-reads the last row and is dropped below), so that all
+            // eight row loads are in flight together
+            int bi[8];
             float4 v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (j + u < end) {
-                    const int b = __ldg(L + j + u);
-                    v[u] = __ldg(d + (size_t)b * row4 + c);
-                } else {
-                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-            }
+            for (int u = 0; u < 8; ++u) bi[u] = __ldg(L + min(j + u, end - 1));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldg(d + (size_t)bi[u] * row4 + c);
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+                if (j + u < end) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
             }
         }
     }
@@ -408,7 +406,8 @@ __global__ void __launch_bounds__(1024) k_ft_backward(const float* __restrict__ 
 
 int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
                        const int* lists, int B, int A, int N, int F, int n_persp, float* grad) {
-    k_ft_backward<<<N, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
+    const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
+    k_ft_backward<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
     return 1;
 }
 
@@ -441,49 +440,58 @@ __global__ void k_bwd_plan(const int* __restrict__ offsets, int N, int n_persp, 
 static __device__ __forceinline__ float4 sum_rows(const float4* __restrict__ d, const int* __restrict__ L, int beg, int end,
                                                   int row4, int c, float4 acc) {
     for (int j = beg; j < end; j += 8) {
+        int bi[8];
         float4 v[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (j + u < end) {
-                const int b = __ldg(L + j + u);
-                v[u] = __ldg(d + (size_t)b * row4 + c);
-            } else {
-                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-        }
+        for (int u = 0; u < 8; ++u) bi[u] = __ldg(L + min(j + u, end - 1));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldg(d + (size_t)bi[u] * row4 + c);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+            if (j + u < end) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
         }
     }
     return acc;
 }
 
-__global__ void __launch_bounds__(1024) k_ft_backward_short(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+__global__ void __launch_bounds__(512) k_ft_backward_short(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
                                                              const int* __restrict__ offsets, const int* __restrict__ lists,
                                                              int B, int A, int N, int F, int n_persp, float* __restrict__ grad) {
     const int f = blockIdx.x;
-    const int c = threadIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
-    int beg[2], end[2], len = 0;
-    for (int p = 0; p < n_persp; ++p) {
-        beg[p] = offsets[(size_t)p * (N + 1) + f];
-        end[p] = offsets[(size_t)p * (N + 1) + f + 1];
-        len += end[p] - beg[p];
-    }
+    int len = offsets[f + 1] - offsets[f];
+    if (n_persp > 1) len += offsets[(size_t)(N + 1) + f + 1] - offsets[(size_t)(N + 1) + f];
     if (len > BWD_PART) return;  // summed in parts by k_ft_backward_long
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < n_persp; ++p)
-        acc = sum_rows(reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm), lists + (size_t)p * B * A, beg[p], end[p], row4, c, acc);
-    __stcs(reinterpret_cast<float4*>(grad) + (size_t)f * row4 + c, acc);
+    for (int p = 0; p < n_persp; ++p) {
+        const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
+        const int* __restrict__ L = lists + (size_t)p * B * A;
+        const float4* __restrict__ d = reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm);
+        for (int j = beg; j < end; j += 8) {
+            // unconditional loads (a slot past the end re-reads the last row and is dropped below), so that all
+            // eight row loads are in flight together
+            int bi[8];
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) bi[u] = __ldg(L + min(j + u, end - 1));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldg(d + (size_t)bi[u] * row4 + c);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (j + u < end) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+            }
+        }
+    }
+    reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
 }
 
-__global__ void __launch_bounds__(1024) k_ft_backward_long(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+__global__ void __launch_bounds__(512) k_ft_backward_long(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
                                                             const int* __restrict__ offsets, const int* __restrict__ lists,
                                                             int B, int A, int N, int F, int n_persp,
                                                             const int* __restrict__ counters, const int2* __restrict__ work,
                                                             float* __restrict__ partial) {
-    const int c = threadIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
     const int n_work = counters[0];
     for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
@@ -504,10 +512,10 @@ __global__ void __launch_bounds__(1024) k_ft_backward_long(const float* __restri
     }
 }
 
-__global__ void __launch_bounds__(1024) k_ft_backward_long_final(const int* __restrict__ counters, const int* __restrict__ longf,
+__global__ void __launch_bounds__(512) k_ft_backward_long_final(const int* __restrict__ counters, const int* __restrict__ longf,
                                                                   const float* __restrict__ partial, int F,
                                                                   float* __restrict__ grad) {
-    const int c = threadIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
     const int n_long = counters[1];
     const float4* p4 = reinterpret_cast<const float4*>(partial);
@@ -534,9 +542,10 @@ int launch_ft_backward_split(cudaStream_t s, const float* dft_stm, const float* 
     int* longf = plan + 2 + 2 * max_work;
     cudaMemsetAsync(counters, 0, 2 * sizeof(int), s);
     k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf);
-    k_ft_backward_short<<<N, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
-    k_ft_backward_long<<<148 * 4, F / 4, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial);
-    k_ft_backward_long_final<<<148 * 2, F / 4, 0, s>>>(counters, longf, partial, F, grad);
+    const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
+    k_ft_backward_short<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
+    k_ft_backward_long<<<dim3(148 * 4, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial);
+    k_ft_backward_long_final<<<dim3(148 * 2, ny), bx, 0, s>>>(counters, longf, partial, F, grad);
     return 4;
 }
 

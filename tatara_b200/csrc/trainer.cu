@@ -369,6 +369,10 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
       p.done(launch_inverse_index(t->stream, d.stm, d.nstm, d.nnz, B, A, N, 2, t->feat_counts, t->feat_offsets, t->feat_cursor,
                                   t->feat_lists)); }
     { PhaseScope p(t, PH_FT_BWD);
+      static const bool old_bwd = getenv("TATARA_DEBUG_OLD_BWD") != nullptr;
+      if (old_bwd)
+          p.done(launch_ft_backward(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->groups[0].grad));
+      else
       p.done(launch_ft_backward_split(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->bwd_plan,
                                       t->bwd_partial, t->groups[0].grad)); }
     return TB_OK;
