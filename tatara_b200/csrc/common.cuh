@@ -60,6 +60,15 @@ static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b;
 int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
                       const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
                       const int* items, int B, int F, int N, int A, float scale, int n_persp);
+// slice-resident forward: every item's rows come from a 32-column strip of its king-bucket slice held in shared
+// memory.  Needs items / item_seg from launch_item_sort with the same rows_per_slice; work: scratch of
+// ft_forward_slice_work_ints(n_items, slices + 1) ints.
+bool ft_forward_slice_supported(int F, int N, int A, int rows_per_slice);
+size_t ft_forward_slice_work_ints(int n_items, int n_keys);
+int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
+                            const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
+                            const int* items, const int* item_seg, int* work, int B, int F, int N, int A,
+                            int rows_per_slice, float scale, int n_persp);
 // scratch of the inverse index, in ints: histogram [2N], a counter, a queue of long lists [2N], scan block sums
 static inline size_t inverse_index_counts_len(int N) { return 4 * (size_t)N + 1 + 2 * ((size_t)N / 2048 + 2); }
 // counts: [inverse_index_counts_len(N)], offsets: [2][N+1], cursor: [2][N], lists: [4][B*A] (lists + sort scratch)

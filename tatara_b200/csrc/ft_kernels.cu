@@ -6,6 +6,8 @@
 // every access below is a 128-bit vector.
 #include "common.cuh"
 
+#define SORT_KEYS_MAX 128  // key limit of the small-key sorts (sort_kernels.cu)
+
 // ------------------------------------------------------------------------------------------------
 // forward: one (position, perspective) item per group of F/8 threads.  Thread `lane` owns the float4
 // at column 4*lane and its pair partner at column F/2 + 4*lane, so that the pairwise product of the
@@ -134,6 +136,237 @@ int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* i
     }
 #undef FT_FWD_ARGS
     return 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// forward, slice-resident variant.  The generic kernel above gathers every row from L2; with the items sorted
+// by king-bucket slice all of an item's rows lie in one slice of rows_per_slice rows, and a 32-column strip
+// of that slice (rows_per_slice * 128 bytes, 208 KB for 1629 rows) fits in shared memory.  A block owns
+// (run of <= 1024 items of one slice, column strip), loads the strip once and serves all of its items'
+// row reads from shared memory; eight lanes work on one item, a lane on four adjacent columns (128-bit
+// shared loads), rows are added in slot order as in the generic kernel, so the sums are bit-identical.
+// A row outside the block's slice (arbitrary index lists) is read from the table in global memory instead.
+// LayerStack strips hold columns [16s, 16s+16) and their pair partners [F/2 + 16s, F/2 + 16s + 16); the other
+// modes 32 adjacent columns.
+// ------------------------------------------------------------------------------------------------
+#define SLICE_IPC 1024  // items per block
+struct FwdWork {
+    int slice, begin, end, pad;
+};
+
+__global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork* __restrict__ work, int* __restrict__ n_work) {
+    // n_keys = slices + 1 (the last key collects items without a usable first index)
+    __shared__ int s_base[SORT_KEYS_MAX + 1];
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int k = 0; k < n_keys; ++k) {
+            s_base[k] = run;
+            run += (item_seg[k + 1] - item_seg[k] + SLICE_IPC - 1) / SLICE_IPC;
+        }
+        s_base[n_keys] = run;
+        *n_work = run;
+    }
+    __syncthreads();
+    for (int k = 0; k < n_keys; ++k) {
+        const int b0 = item_seg[k], e0 = item_seg[k + 1];
+        const int n = s_base[k + 1] - s_base[k];
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            FwdWork w;
+            w.slice = k;
+            w.begin = b0 + i * SLICE_IPC;
+            w.end = min(e0, w.begin + SLICE_IPC);
+            w.pad = 0;
+            work[s_base[k] + i] = w;
+        }
+    }
+}
+
+template <int MODE, int NQ>
+__global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __restrict__ table, const int* __restrict__ idx_stm,
+                                                               const int* __restrict__ idx_nstm, const int* __restrict__ nnz,
+                                                               const float* __restrict__ bias, float* __restrict__ pre_stm,
+                                                               float* __restrict__ pre_nstm, float* __restrict__ combined,
+                                                               const int* __restrict__ items, const FwdWork* __restrict__ work,
+                                                               const int* __restrict__ n_work, int B, int F, int N, int A, int rps,
+                                                               int n_slices, float scale) {
+    extern __shared__ __align__(16) float s_slice[];  // [rows][32]
+    if ((int)blockIdx.x >= *n_work) return;
+    const FwdWork wk = work[blockIdx.x];
+    const int strip = blockIdx.y;
+    const bool has_slice = wk.slice < n_slices;
+    const int row0 = wk.slice * rps;
+    const int rows = has_slice ? min(rps, N - row0) : 0;
+    const int half = F >> 1;
+    const int cA = MODE == 1 ? 16 * strip : 32 * strip;  // first column of the strip's first 16 (or all 32) columns
+    const int cB = MODE == 1 ? half + 16 * strip : cA + 16;
+    for (int e = threadIdx.x; e < rows * 8; e += blockDim.x) {
+        const int r = e >> 3, q = e & 7;
+        const int col = q < 4 ? cA + 4 * q : cB + 4 * (q - 4);
+        *reinterpret_cast<float4*>(s_slice + r * 32 + 4 * q) =
+            __ldg(reinterpret_cast<const float4*>(table + (size_t)(row0 + r) * F + col));
+    }
+    const int zero_row = rps * 32;  // float offset of one row of zeros behind the strip
+    if (threadIdx.x < 32) s_slice[zero_row + threadIdx.x] = 0.f;
+    __syncthreads();
+
+    // eight lanes per item (a lane owns four adjacent columns: one 128-bit shared load per row), four items per warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 3, j = lane & 7;
+    const int mycol = j < 4 ? cA + 4 * j : cB + 4 * (j - 4);
+    const float4 mybias = bias ? *reinterpret_cast<const float4*>(bias + mycol) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 pbias = mybias;  // the pair partner's bias (LayerStack)
+    pbias.x = __shfl_xor_sync(0xffffffffu, mybias.x, 4); pbias.y = __shfl_xor_sync(0xffffffffu, mybias.y, 4);
+    pbias.z = __shfl_xor_sync(0xffffffffu, mybias.z, 4); pbias.w = __shfl_xor_sync(0xffffffffu, mybias.w, 4);
+    const float4* __restrict__ t4 = reinterpret_cast<const float4*>(table);
+    // NQ index registers per lane: slots j, j + 8, ..., j + 8 (NQ - 1)
+    const float* s_lane = s_slice + 4 * j;
+
+    // software pipeline: item id two rounds ahead, its nnz and indices one round ahead
+    auto load_item = [&](int slot) { return slot < wk.end ? __ldg(items + slot) : -1; };
+    auto load_feats = [&](int it, int& n, int (&raw)[NQ]) {
+        n = 0;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) raw[q] = -1;
+        if (it >= 0) {
+            const int p = it >= B, b = it - p * B;
+            n = __ldg(nnz + b);
+            const int* ip = (p ? idx_nstm : idx_stm) + (size_t)b * A;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q)
+                if (j + 8 * q < A) raw[q] = __ldg(ip + j + 8 * q);
+        }
+    };
+    const int per_round = 4 * (blockDim.x >> 5);
+    const int slot0 = wk.begin + 4 * warp + g;
+    int it_c = load_item(slot0), it_n = load_item(slot0 + per_round);
+    int n_c, raw_c[NQ];
+    load_feats(it_c, n_c, raw_c);
+    for (int base = wk.begin; base < wk.end; base += per_round) {
+        const int it_n2 = load_item(base + 2 * per_round + 4 * warp + g);
+        int n_n, raw_n[NQ];
+        load_feats(it_n, n_n, raw_n);
+
+        // ---- current item: indices -> shared-memory float offsets (>= 0), global fallback (<= -2) or skip (-1)
+        const int n = n_c < 0 ? 0 : (n_c > A ? A : n_c);
+        int code[NQ];
+        bool outside = false;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            const int f = (j + 8 * q < n) ? raw_c[q] : -1;
+            int c = zero_row;  // skipped slot: the all-zero row
+            if ((unsigned)f < (unsigned)N) {
+                const int r = f - row0;
+                c = (unsigned)r < (unsigned)rows ? r * 32 : -(f + 2);
+            }
+            outside |= c < 0;
+            code[q] = c;
+        }
+        int nmax = n;
+        nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, 8));
+        nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, 16));
+        const bool slow = __any_sync(0xffffffffu, outside);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            if (8 * q >= nmax) break;
+            if (!slow) {
+                // every row of the round comes from the strip: branch-free; a skipped slot reads the all-zero row
+                // kept behind the strip (x + 0.0 == x).  Two batches of four rows keep the register count low
+                // enough for 32 warps per SM.
+#pragma unroll
+                for (int u0 = 0; u0 < 8; u0 += 4) {
+                    float4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = __shfl_sync(0xffffffffu, code[q], (lane & 24) | (u0 + u));
+                        v[u] = *reinterpret_cast<const float4*>(s_lane + c);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int c = __shfl_sync(0xffffffffu, code[q], (lane & 24) | u);
+                    float4 v;
+                    if (c >= 0) v = *reinterpret_cast<const float4*>(s_lane + c);
+                    else v = __ldg(t4 + (((size_t)(-c - 2) * F + mycol) >> 2));
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                }
+            }
+        }
+
+        // ---- epilogue
+        const bool valid = it_c >= 0;
+        const int persp = it_c >= B, b = valid ? it_c - persp * B : 0;
+        float* pre = (persp ? pre_nstm : pre_stm) + (size_t)b * F;
+        if (MODE == 0) {
+            if (valid) __stcs(reinterpret_cast<float4*>(pre + mycol), acc);
+        } else if (MODE == 1) {
+            float4 pa;
+            pa.x = __shfl_xor_sync(0xffffffffu, acc.x, 4); pa.y = __shfl_xor_sync(0xffffffffu, acc.y, 4);
+            pa.z = __shfl_xor_sync(0xffffffffu, acc.z, 4); pa.w = __shfl_xor_sync(0xffffffffu, acc.w, 4);
+            if (valid) {
+                __stcs(reinterpret_cast<float4*>(pre + mycol), acc);
+                if (j < 4) {
+                    float4 o;
+                    o.x = crelu01(acc.x + mybias.x) * crelu01(pa.x + pbias.x) * scale;
+                    o.y = crelu01(acc.y + mybias.y) * crelu01(pa.y + pbias.y) * scale;
+                    o.z = crelu01(acc.z + mybias.z) * crelu01(pa.z + pbias.z) * scale;
+                    o.w = crelu01(acc.w + mybias.w) * crelu01(pa.w + pbias.w) * scale;
+                    __stcs(reinterpret_cast<float4*>(combined + (size_t)b * F + persp * half + cA + 4 * j), o);
+                }
+            }
+        } else if (valid) {
+            const float4 x = make_float4(acc.x + mybias.x, acc.y + mybias.y, acc.z + mybias.z, acc.w + mybias.w);
+            __stcs(reinterpret_cast<float4*>(pre + mycol), x);
+            float4 a = make_float4(crelu01(x.x), crelu01(x.y), crelu01(x.z), crelu01(x.w));
+            if (MODE == 3) { a.x *= a.x; a.y *= a.y; a.z *= a.z; a.w *= a.w; }
+            __stcs(reinterpret_cast<float4*>(combined + (size_t)b * 2 * F + persp * F + mycol), a);
+        }
+        it_c = it_n; it_n = it_n2; n_c = n_n;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) raw_c[q] = raw_n[q];
+    }
+}
+
+// work: [ceil(n_items / 1024) + keys + 1] FwdWork records followed by one int (their count)
+size_t ft_forward_slice_work_ints(int n_items, int n_keys) { return 4 * ((size_t)n_items / SLICE_IPC + n_keys + 2) + 4; }
+
+bool ft_forward_slice_supported(int F, int N, int A, int rps) {
+    int n_slices = ceil_div(N, rps);
+    return F % 32 == 0 && A <= 64 && ((size_t)rps + 1) * 128 <= 226 * 1024 && n_slices + 1 <= SORT_KEYS_MAX;
+}
+
+int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
+                            const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
+                            const int* items, const int* item_seg, int* work, int B, int F, int N, int A, int rps,
+                            float scale, int n_persp) {
+    if (B <= 0) return 0;
+    const int n_items = n_persp * B;
+    const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
+    const int max_work = n_items / SLICE_IPC + n_keys + 2;
+    FwdWork* wk = reinterpret_cast<FwdWork*>(work);
+    int* n_work = work + 4 * (size_t)max_work;
+    k_fwd_plan<<<1, 128, 0, s>>>(item_seg, n_keys, wk, n_work);
+    const size_t smem = ((size_t)rps + 1) * 32 * sizeof(float);  // the strip and one row of zeros
+    dim3 grid(max_work, F / 32);
+#define FT_SLICE_ARGS table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, items, wk, n_work, B, F, N, A, rps, n_slices, scale
+#define FT_SLICE_LAUNCH(M, Q)                                                                                      \
+    do {                                                                                                           \
+        cudaFuncSetAttribute(k_ft_forward_slice<M, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+        k_ft_forward_slice<M, Q><<<grid, 1024, smem, s>>>(FT_SLICE_ARGS);                                          \
+    } while (0)
+    const bool q5 = A <= 40;
+    switch (mode) {
+        case 0: if (q5) FT_SLICE_LAUNCH(0, 5); else FT_SLICE_LAUNCH(0, 8); break;
+        case 1: if (q5) FT_SLICE_LAUNCH(1, 5); else FT_SLICE_LAUNCH(1, 8); break;
+        case 2: if (q5) FT_SLICE_LAUNCH(2, 5); else FT_SLICE_LAUNCH(2, 8); break;
+        default: if (q5) FT_SLICE_LAUNCH(3, 5); else FT_SLICE_LAUNCH(3, 8); break;
+    }
+#undef FT_SLICE_LAUNCH
+#undef FT_SLICE_ARGS
+    return 2;
 }
 
 // ------------------------------------------------------------------------------------------------

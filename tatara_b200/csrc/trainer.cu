@@ -119,7 +119,7 @@ struct tb_trainer {
     TileDesc* tiles = nullptr;
     float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr;
     int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
-    int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr;
+    int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr;
     float* bwd_partial = nullptr;
     int last_n = 0;
     // loss ring (AsyncLossRing, trainer_common.rs:909-1000)
@@ -310,8 +310,14 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
       p.done(n); }
     { PhaseScope p(t, PH_FT_FWD);
       const int mode = ls ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
-      p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1], t->combined,
-                               t->items, B, F, N, A, FT_POST_SCALE, 2)); }
+      static const bool no_slice = getenv("TATARA_DEBUG_NO_SLICE_FWD") != nullptr;
+      const int rps = c.piece_inputs > 0 ? c.piece_inputs : N;
+      if (!no_slice && ft_forward_slice_supported(F, N, A, rps))
+          p.done(launch_ft_forward_slice(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1],
+                                         t->combined, t->items, t->item_seg, t->fwd_work, B, F, N, A, rps, FT_POST_SCALE, 2));
+      else
+          p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1], t->combined,
+                                   t->items, B, F, N, A, FT_POST_SCALE, 2)); }
     const LossParams lp = make_loss(loss, lambda, d.norm);
     if (ls) {
         { PhaseScope p(t, PH_L1_FWD);
@@ -512,7 +518,7 @@ void free_all(tb_trainer* t) {
     cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
     cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials);
     cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
-    cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
+    cudaFree(t->fwd_work); cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
     if (t->ev_t0) cudaEventDestroy(t->ev_t0);
     if (t->ev_t1) cudaEventDestroy(t->ev_t1);
     for (int i = 0; i < PH_COUNT; ++i) {
@@ -615,6 +621,7 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->bias_partials, (size_t)DGRAD_CTAS * 2 * F));
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
     CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
+    CU(t, dalloc(&t->fwd_work, ft_forward_slice_work_ints((int)(2 * B), 129)));
     {
         const size_t max_work = (size_t)ft_backward_max_work((int)B, (int)A, 2);
         CU(t, dalloc(&t->bwd_plan, 2 + 2 * max_work + 3 * (size_t)N));
