@@ -382,6 +382,89 @@ __global__ void __launch_bounds__(128) k_tail_layerstack(const float* __restrict
     block_loss_partial(e2, loss_partials);
 }
 
+// Warp-per-position variant for l2 <= 32 and 2 (l1 - 1) <= 32: lane o owns output o of L2, lane i input i; the
+// vectors travel between lanes through shuffles, every store of a per-position vector is one coalesced row.
+// Sums over the L2 inputs / outputs run in index order, like the oracle; only the 32-term L3 dot product is
+// a butterfly reduction.
+__global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __restrict__ l1_total, const int* __restrict__ bucket,
+                                                               const float* __restrict__ score, const float* __restrict__ wdl,
+                                                               const float* __restrict__ l2_w, const float* __restrict__ l2_b,
+                                                               const float* __restrict__ l3_w, const float* __restrict__ l3_b,
+                                                               LossParams lp, int B, int l1, int l2, int nb,
+                                                               float* __restrict__ net_output, float* __restrict__ dy_out,
+                                                               float* __restrict__ dl1_total, float* __restrict__ l2_input_o,
+                                                               float* __restrict__ dl2_out_o, float* __restrict__ l2_acted_o,
+                                                               double* __restrict__ loss_partials, int backward) {
+    extern __shared__ float s_w[];
+    const int l1e = l1 - 1, l2in = 2 * l1e;
+    float* sw2 = s_w;                   // [nb][l2][l2in]
+    float* sb2 = sw2 + nb * l2 * l2in;  // [nb][l2]
+    float* sw3 = sb2 + nb * l2;         // [nb][l2]
+    float* sb3 = sw3 + nb * l2;         // [nb]
+    for (int i = threadIdx.x; i < nb * l2 * l2in; i += blockDim.x) sw2[i] = l2_w[i];
+    for (int i = threadIdx.x; i < nb * l2; i += blockDim.x) { sb2[i] = l2_b[i]; sw3[i] = l3_w[i]; }
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) sb3[i] = l3_b[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    const unsigned full = 0xffffffffu;
+    double e2 = 0.0;
+    for (int b = blockIdx.x * wpb + (threadIdx.x >> 5); b < B; b += gridDim.x * wpb) {
+        const int g = bucket[b];
+        const bool valid = (unsigned)g < (unsigned)nb;
+        const float t = lane < l1 ? l1_total[(size_t)b * l1 + lane] : 0.f;
+        const float skip = __shfl_sync(full, t, l1e);
+        // lane i < l1e: sqr_i; lane l1e + i: main_i (concat_l1sqr_main), then CReLU
+        const float m = __shfl_sync(full, t, lane < l1e ? lane : (lane - l1e < l1e ? lane - l1e : 0));
+        const float pre = lane < l1e ? m * m * L1_SQR_SCALE : m;
+        const float in = lane < l2in ? crelu01(pre) : 0.f;
+        float d2 = 0.f, a2 = 0.f, l3 = 0.f;
+        if (valid) {
+            const float* wr = sw2 + ((size_t)g * l2 + (lane < l2 ? lane : 0)) * l2in;
+            float sum = lane < l2 ? sb2[g * l2 + lane] : 0.f;
+            for (int i = 0; i < l2in; ++i) sum += __shfl_sync(full, in, i) * wr[i];
+            d2 = lane < l2 ? sum : 0.f;
+            a2 = lane < l2 ? crelu01(d2) : 0.f;
+            float part = lane < l2 ? a2 * sw3[g * l2 + lane] : 0.f;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(full, part, d);
+            l3 = sb3[g] + part;
+        }
+        const float out = l3 + skip;
+        float dyv;
+        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
+        if (lane == 0) {
+            e2 += (double)err * (double)err;
+            net_output[b] = out;
+            dy_out[b] = dyv;
+        }
+        if (backward) {
+            float dl2o = 0.f;
+            if (valid && lane < l2) {
+                const float da = dyv * sw3[g * l2 + lane];
+                dl2o = (d2 > 0.f && d2 < 1.0f) ? da : 0.f;
+            }
+            float sum = 0.f;
+            if (valid) {
+                const float* wc = sw2 + (size_t)g * l2 * l2in + (lane < l2in ? lane : 0);
+                for (int o = 0; o < l2; ++o) sum += __shfl_sync(full, dl2o, o) * wc[o * l2in];
+            }
+            const float dpre = (lane < l2in && pre > 0.f && pre < 1.0f) ? sum : 0.f;  // crelu_grad on l2_pre
+            // lane i < l1e: d(main_i) = dpre[l1e + i] + 2 main_i scale dpre[i]
+            const float dmain_concat = __shfl_sync(full, dpre, lane + l1e < 32 ? lane + l1e : 0);
+            const float from_sqr = 2.0f * t * L1_SQR_SCALE * dpre;
+            if (lane < l1e) dl1_total[(size_t)b * l1 + lane] = dmain_concat + from_sqr;
+            else if (lane == l1e) dl1_total[(size_t)b * l1 + l1e] = dyv;
+            if (lane < l2in) l2_input_o[(size_t)b * l2in + lane] = in;
+            if (lane < l2) {
+                dl2_out_o[(size_t)b * l2 + lane] = dl2o;
+                l2_acted_o[(size_t)b * l2 + lane] = a2;
+            }
+        }
+    }
+    block_loss_partial(e2, loss_partials);
+}
+
 int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
                            const float* wdl, const float* l2_w, const float* l2_b, const float* l3_w,
                            const float* l3_b, LossParams lp, int B, int l1, int l2, int nb, float* net_output,
@@ -390,6 +473,16 @@ int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* buc
     const int l2in = 2 * (l1 - 1);
     const size_t smem = sizeof(float) * ((size_t)nb * l2 * l2in + 2 * (size_t)nb * l2 + nb);
     cudaFuncSetAttribute(k_tail_layerstack, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (l2 <= 32 && l2in <= 32 && smem <= 96 * 1024) {
+        cudaFuncSetAttribute(k_tail_layerstack_warp, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        int blocks = ceil_div(B, 8);
+        if (blocks > 148 * 4) blocks = 148 * 4;
+        k_tail_layerstack_warp<<<blocks, 256, smem, s>>>(l1_total, bucket, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, B, l1, l2, nb,
+                                                        net_output, dy, dl1_total, l2_input, dl2_out, l2_acted, loss_partials,
+                                                        backward);
+        k_reduce_double<<<1, 256, 0, s>>>(loss_partials, blocks, loss_acc);
+        return 2;
+    }
     const int blocks = ceil_div(B, 128);
     k_tail_layerstack<<<blocks, 128, smem, s>>>(l1_total, bucket, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, B, l1, l2, nb,
                                                net_output, dy, dl1_total, l2_input, dl2_out, l2_acted, loss_partials, backward);
@@ -462,12 +555,82 @@ __global__ void __launch_bounds__(128) k_tail_simple(const float* __restrict__ l
     block_loss_partial(e2, loss_partials);
 }
 
+// Warp-per-position variant for l1 <= 32 and l2 <= 32 (lane i: L1 output i; lane o: L2 output o).
+__global__ void __launch_bounds__(256) k_tail_simple_warp(const float* __restrict__ l1_pre, const float* __restrict__ score,
+                                                           const float* __restrict__ wdl, const float* __restrict__ l2_w,
+                                                           const float* __restrict__ l2_b, const float* __restrict__ l3_w,
+                                                           const float* __restrict__ l3_b, LossParams lp, int act, int B, int l1,
+                                                           int l2, float* __restrict__ net_output, float* __restrict__ dy_out,
+                                                           float* __restrict__ dl1_pre, float* __restrict__ l1_acted_o,
+                                                           float* __restrict__ dl2_pre_o, float* __restrict__ l2_acted_o,
+                                                           double* __restrict__ loss_partials, int backward) {
+    __shared__ float sw2[32][33];   // [i][o]
+    __shared__ float sw2t[32][33];  // [o][i]
+    __shared__ float sb2[32], sw3[32];
+    for (int e = threadIdx.x; e < 32 * 32; e += blockDim.x) {
+        const int i = e >> 5, o = e & 31;
+        const float v = (i < l1 && o < l2) ? l2_w[i * l2 + o] : 0.f;
+        sw2[i][o] = v;
+        sw2t[o][i] = v;
+    }
+    if (threadIdx.x < 32) {
+        sb2[threadIdx.x] = (int)threadIdx.x < l2 ? l2_b[threadIdx.x] : 0.f;
+        sw3[threadIdx.x] = (int)threadIdx.x < l2 ? l3_w[threadIdx.x] : 0.f;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int wpb = blockDim.x >> 5;
+    const unsigned full = 0xffffffffu;
+    const float b3 = l3_b[0];
+    double e2 = 0.0;
+    for (int b = blockIdx.x * wpb + (threadIdx.x >> 5); b < B; b += gridDim.x * wpb) {
+        const float x1 = lane < l1 ? l1_pre[(size_t)b * l1 + lane] : 0.f;
+        const float a1 = lane < l1 ? act_fwd(act, x1) : 0.f;
+        float x2 = sb2[lane];
+        for (int i = 0; i < l1; ++i) x2 += __shfl_sync(full, a1, i) * sw2[i][lane];
+        const float a2 = lane < l2 ? act_fwd(act, x2) : 0.f;
+        float part = a2 * sw3[lane];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(full, part, d);
+        const float out = b3 + part;
+        float dyv;
+        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
+        if (lane == 0) {
+            e2 += (double)err * (double)err;
+            net_output[b] = out;
+            dy_out[b] = dyv;
+        }
+        if (backward) {
+            const float d2 = lane < l2 ? act_grad(act, x2, dyv * sw3[lane]) : 0.f;
+            float sum = 0.f;
+            for (int o = 0; o < l2; ++o) sum += __shfl_sync(full, d2, o) * sw2t[o][lane];
+            if (lane < l1) {
+                dl1_pre[(size_t)b * l1 + lane] = act_grad(act, x1, sum);
+                l1_acted_o[(size_t)b * l1 + lane] = a1;
+            }
+            if (lane < l2) {
+                dl2_pre_o[(size_t)b * l2 + lane] = d2;
+                l2_acted_o[(size_t)b * l2 + lane] = a2;
+            }
+        }
+    }
+    block_loss_partial(e2, loss_partials);
+}
+
 int launch_tail_simple(cudaStream_t s, const float* l1_pre, const float* score, const float* wdl,
                        const float* l2_w, const float* l2_b, const float* l3_w, const float* l3_b, LossParams lp,
                        int act, int B, int l1, int l2, float* net_output, float* dy, float* dl1_pre,
                        float* l1_acted, float* dl2_pre, float* l2_acted, double* loss_partials,
                        double* loss_acc, int backward) {
     const size_t smem = sizeof(float) * ((size_t)l1 * l2 + 2 * (size_t)l2);
+    if (l1 <= 32 && l2 <= 32) {
+        int blocks = ceil_div(B, 8);
+        if (blocks > 148 * 4) blocks = 148 * 4;
+        k_tail_simple_warp<<<blocks, 256, 0, s>>>(l1_pre, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, act, B, l1, l2, net_output, dy,
+                                                 dl1_pre, l1_acted, dl2_pre, l2_acted, loss_partials, backward);
+        k_reduce_double<<<1, 256, 0, s>>>(loss_partials, blocks, loss_acc);
+        return 2;
+    }
     const int blocks = ceil_div(B, 128);
     k_tail_simple<<<blocks, 128, smem, s>>>(l1_pre, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, act, B, l1, l2, net_output, dy,
                                            dl1_pre, l1_acted, dl2_pre, l2_acted, loss_partials, backward);
@@ -679,24 +842,43 @@ __global__ void __launch_bounds__(256) k_l1_wgrad(const float* __restrict__ x, i
     }
 }
 
+// Second stage: block column g adds the work units of bucket g in order (the units of a bucket are contiguous);
+// the last column (g == nb: positions with an out-of-range bucket id, or the whole batch for Simple) goes to a
+// scratch row.  Third stage: gw_shared[k][o] = sum over the columns.
 __global__ void __launch_bounds__(256) k_l1_wgrad_final(const float* __restrict__ partials, const TileDesc* __restrict__ units,
                                                          const int* __restrict__ n_units, int K, int l1, int nb,
-                                                         float* __restrict__ gw_bucket, float* __restrict__ gw_shared) {
+                                                         float* __restrict__ gw_bucket, float* __restrict__ rest) {
+    __shared__ int s_range[2];
+    const int g = blockIdx.y;
+    if (threadIdx.x == 0) {
+        const int nu = *n_units;
+        int first = nu, last = nu;
+        for (int u = 0; u < nu; ++u) {
+            const int bk = units[u].bucket;
+            if (bk == g && first == nu) first = u;
+            if (bk > g) { last = u; break; }
+        }
+        if (first == nu) last = nu;
+        s_range[0] = first;
+        s_range[1] = last;
+    }
+    __syncthreads();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= l1 * K) return;
+    float sum = 0.f;
+    for (int u = s_range[0]; u < s_range[1]; ++u) sum += partials[(size_t)u * l1 * K + i];
+    if (g < nb) gw_bucket[(size_t)g * l1 * K + i] = sum;
+    else rest[i] = sum;
+}
+
+__global__ void __launch_bounds__(256) k_l1_wgrad_shared(const float* __restrict__ gw_bucket, const float* __restrict__ rest,
+                                                          int K, int l1, int nb, float* __restrict__ gw_shared) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= l1 * K) return;
     const int o = i / K, k = i - o * K;
-    const int nu = *n_units;
     float total = 0.f;
-    int u = 0;
-    for (int g = 0; g <= nb; ++g) {
-        float sum = 0.f;
-        while (u < nu && units[u].bucket == g) {
-            sum += partials[((size_t)u * l1 + o) * K + k];
-            ++u;
-        }
-        if (gw_bucket && g < nb) gw_bucket[((size_t)g * l1 + o) * K + k] = sum;
-        total += sum;
-    }
+    for (int g = 0; g < nb; ++g) total += gw_bucket[(size_t)g * l1 * K + i];
+    total += rest[i];
     gw_shared[(size_t)k * l1 + o] = total;
 }
 
@@ -780,8 +962,10 @@ int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, con
         k_l1_wgrad_v4<16><<<dim3(ceil_div(K / 4, 128), max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
     else
         k_l1_wgrad<<<dim3(K / 128, max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
-    k_l1_wgrad_final<<<ceil_div(l1 * K, 256), 256, 0, s>>>(partials, units, n_units, K, l1, nb, gw_bucket, gw_shared);
-    return 2;
+    float* rest = partials + (size_t)max_units * l1 * K;  // one more [l1][K] row behind the unit partials
+    k_l1_wgrad_final<<<dim3(ceil_div(l1 * K, 256), nb + 1), 256, 0, s>>>(partials, units, n_units, K, l1, nb, gw_bucket, rest);
+    k_l1_wgrad_shared<<<ceil_div(l1 * K, 256), 256, 0, s>>>(gw_bucket, rest, K, l1, nb, gw_shared);
+    return 3;
 }
 
 // ------------------------------------------------------------------------------------------------

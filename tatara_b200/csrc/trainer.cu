@@ -617,7 +617,7 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->tiles, (size_t)t->max_tiles + t->max_units));
     const size_t n_cells = ls ? (size_t)(l2 * t->l2in + 2 * l2 + 1 + l1) : (size_t)(l1 * l2 + 2 * l2 + 1 + l1);
     CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 16 : (size_t)128) * n_cells));
-    CU(t, dalloc(&t->l1w_partials, (size_t)t->max_units * l1 * t->K));
+    CU(t, dalloc(&t->l1w_partials, ((size_t)t->max_units + 1) * l1 * t->K));
     CU(t, dalloc(&t->bias_partials, (size_t)DGRAD_CTAS * 2 * F));
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
     CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
