@@ -610,7 +610,7 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->net_output, B)); CU(t, dalloc(&t->dy, B));
     CU(t, dalloc(&t->tail_a, B * (size_t)(ls ? t->l2in : l1)));
     CU(t, dalloc(&t->tail_b, B * l2)); CU(t, dalloc(&t->tail_c, B * l2));
-    CU(t, dalloc(&t->loss_partials, B / 128 + 2)); CU(t, dalloc(&t->loss_acc, 1));
+    CU(t, dalloc(&t->loss_partials, B / 128 + 1024)); CU(t, dalloc(&t->loss_acc, 1));  // one partial per tail block (<= 148 * 4 or B / 128)
     t->max_tiles = (int)(B / TB_TILE_M) + TB_MAX_BUCKETS + 2;
     t->max_units = sort_max_units(t->max_tiles);
     CU(t, dalloc(&t->order, B)); CU(t, dalloc(&t->n_tiles, 2)); CU(t, dalloc(&t->seg_start, TB_MAX_BUCKETS + 3));
