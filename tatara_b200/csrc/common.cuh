@@ -62,9 +62,9 @@ int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* i
                       const int* items, int B, int F, int N, int A, float scale, int n_persp);
 // slice-resident forward: every item's rows come from a 32-column strip of its king-bucket slice held in shared
 // memory.  Needs items / item_seg from launch_item_sort with the same rows_per_slice; work: scratch of
-// ft_forward_slice_work_ints(n_items, slices + 1) ints.
+// ft_forward_slice_work_ints(n_items, slices + 1, A) ints.
 bool ft_forward_slice_supported(int F, int N, int A, int rows_per_slice);
-size_t ft_forward_slice_work_ints(int n_items, int n_keys);
+size_t ft_forward_slice_work_ints(int n_items, int n_keys, int A);
 int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
                             const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
                             const int* items, const int* item_seg, int* work, int B, int F, int N, int A,

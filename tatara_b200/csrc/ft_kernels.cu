@@ -181,120 +181,178 @@ __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork
     }
 }
 
-template <int MODE, int NQ>
-__global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __restrict__ table, const int* __restrict__ idx_stm,
-                                                               const int* __restrict__ idx_nstm, const int* __restrict__ nnz,
-                                                               const float* __restrict__ bias, float* __restrict__ pre_stm,
-                                                               float* __restrict__ pre_nstm, float* __restrict__ combined,
-                                                               const int* __restrict__ items, const FwdWork* __restrict__ work,
-                                                               const int* __restrict__ n_work, int B, int F, int N, int A, int rps,
-                                                               int n_slices, float scale) {
-    extern __shared__ __align__(16) float s_slice[];  // [rows][32]
+// Row codes of the slice-resident forward, one thread per slot of the sorted item list: for every feature slot the
+// row number inside the item's slice (16 bits), SLICE_ZERO_ROW's stand-in rps for a slot without a feature (the strip
+// keeps a row of zeros there), SLICE_OUTSIDE for a table row outside the slice (the kernel then reads the index list).
+// info[slot] = item | SLICE_SLOW_BIT when the item has an outside row.  Codes of consecutive slots are contiguous
+// (A_pad 16-bit codes each, A_pad a multiple of 8), so a warp copies its round of four items in 16-byte pieces.
+#define SLICE_OUTSIDE 0xFFFFu
+#define SLICE_SLOW_BIT 0x40000000
+__global__ void __launch_bounds__(256) k_fwd_codes(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
+                                                   const int* __restrict__ nnz, const int* __restrict__ items,
+                                                   const int* __restrict__ item_seg, int n_keys, int n_items, int B, int N,
+                                                   int A, int A_pad, int rps, uint4* __restrict__ codes,
+                                                   int* __restrict__ info) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n_items) return;
+    int lo = 0, hi = n_keys - 1;  // the key whose segment holds slot s
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(item_seg + mid) <= s) lo = mid; else hi = mid - 1;
+    }
+    const int row0 = lo * rps;
+    const int rows = max(0, min(rps, N - row0));
+    const int it = __ldg(items + s);
+    const int p = it >= B, b = it - p * B;
+    int n = __ldg(nnz + b);
+    n = n < 0 ? 0 : (n > A ? A : n);
+    const int* ip = (p ? idx_nstm : idx_stm) + (size_t)b * A;
+    bool outside = false;
+    for (int q0 = 0; q0 < A_pad; q0 += 8) {
+        unsigned c[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int q = q0 + u;
+            unsigned code = (unsigned)rps;
+            if (q < n) {
+                const int f = __ldg(ip + q);
+                if ((unsigned)f < (unsigned)N) {
+                    const int r = f - row0;
+                    if ((unsigned)r < (unsigned)rows) code = (unsigned)r;
+                    else { code = SLICE_OUTSIDE; outside = true; }
+                }
+            }
+            c[u] = code;
+        }
+        codes[((size_t)s * A_pad + q0) >> 3] = make_uint4(c[0] | (c[1] << 16), c[2] | (c[3] << 16), c[4] | (c[5] << 16), c[6] | (c[7] << 16));
+    }
+    info[s] = it | (outside ? SLICE_SLOW_BIT : 0);
+}
+
+// two fp32 additions in one instruction (sm_100 packed arithmetic); each half is an IEEE round-to-nearest add
+static __device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+static __device__ __forceinline__ float lo_f(unsigned long long v) { return __uint_as_float((unsigned)v); }
+static __device__ __forceinline__ float hi_f(unsigned long long v) { return __uint_as_float((unsigned)(v >> 32)); }
+// asynchronous 16-byte copy global -> shared; src_bytes = 0 writes zeros and reads nothing
+static __device__ __forceinline__ void cp_async16(void* dst_shared, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src),
+                 "r"(src_bytes)
+                 : "memory");
+}
+static __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_PENDING>
+static __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_PENDING) : "memory"); }
+
+template <int MODE>
+__global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __restrict__ table, const float* __restrict__ bias,
+                                                               float* __restrict__ pre_stm, float* __restrict__ pre_nstm,
+                                                               float* __restrict__ combined, const int* __restrict__ idx_stm,
+                                                               const int* __restrict__ idx_nstm, const int* __restrict__ info,
+                                                               const uint4* __restrict__ codes, const FwdWork* __restrict__ work,
+                                                               const int* __restrict__ n_work, int n_items, int B, int F, int N,
+                                                               int A, int A_pad, int rps, float scale) {
+    // strip [rps + 1][32] floats, then two buffers of [32 warps][4 items][A_pad] 16-bit row codes
+    extern __shared__ __align__(16) unsigned char s_raw[];
     if ((int)blockIdx.x >= *n_work) return;
     const FwdWork wk = work[blockIdx.x];
     const int strip = blockIdx.y;
-    const bool has_slice = wk.slice < n_slices;
     const int row0 = wk.slice * rps;
-    const int rows = has_slice ? min(rps, N - row0) : 0;
+    const int rows = max(0, min(rps, N - row0));
     const int half = F >> 1;
     const int cA = MODE == 1 ? 16 * strip : 32 * strip;  // first column of the strip's first 16 (or all 32) columns
     const int cB = MODE == 1 ? half + 16 * strip : cA + 16;
-    for (int e = threadIdx.x; e < rows * 8; e += blockDim.x) {
-        const int r = e >> 3, q = e & 7;
-        const int col = q < 4 ? cA + 4 * q : cB + 4 * (q - 4);
-        *reinterpret_cast<float4*>(s_slice + r * 32 + 4 * q) =
-            __ldg(reinterpret_cast<const float4*>(table + (size_t)(row0 + r) * F + col));
-    }
-    const int zero_row = rps * 32;  // float offset of one row of zeros behind the strip
-    if (threadIdx.x < 32) s_slice[zero_row + threadIdx.x] = 0.f;
-    __syncthreads();
-
-    // eight lanes per item (a lane owns four adjacent columns: one 128-bit shared load per row), four items per warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 3, j = lane & 7;
     const int mycol = j < 4 ? cA + 4 * j : cB + 4 * (j - 4);
+
+    // strip fill: thread e & 7 == j copies the 16 bytes it will later read, for rows e >> 3
+    for (int e = threadIdx.x; e < rows * 8; e += blockDim.x)
+        cp_async16(s_raw + (size_t)e * 16, table + (size_t)(row0 + (e >> 3)) * F + mycol, 16);
+    if (threadIdx.x < 32) reinterpret_cast<float*>(s_raw)[rps * 32 + threadIdx.x] = 0.f;  // the row of zeros
+    for (int e = rows * 8 + threadIdx.x; e < rps * 8; e += blockDim.x)  // rows past the end of the table
+        *reinterpret_cast<float4*>(s_raw + (size_t)e * 16) = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    // a round = four items per warp; their codes arrive by asynchronous copy one round ahead
+    const int code_bytes = 4 * A_pad * 2;  // per warp and buffer
+    unsigned char* s_codes = s_raw + ((size_t)rps + 1) * 128 + (size_t)warp * code_bytes;
+    const int buf_stride = 32 * code_bytes;
+    const unsigned char* codes_b = reinterpret_cast<const unsigned char*>(codes);
+    const int chunk_item = (lane * 16) / (A_pad * 2);  // which of the four items this lane's 16-byte piece belongs to
+    auto fetch_codes = [&](int slot, int buf) {
+        if (lane * 16 < code_bytes) {
+            // pieces of slots past the end of the run are filled with zeros (row 0): whatever lies there is never a
+            // valid offset into this block's strip
+            const bool ok = slot + chunk_item < wk.end;
+            const long long off = (long long)slot * A_pad * 2 + lane * 16;
+            cp_async16(s_codes + buf * buf_stride + lane * 16, codes_b + (ok ? off : 0), ok ? 16 : 0);
+        }
+    };
+    const int per_round = 4 * (blockDim.x >> 5);
+    fetch_codes(wk.begin + 4 * warp, 0);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
     const float4 mybias = bias ? *reinterpret_cast<const float4*>(bias + mycol) : make_float4(0.f, 0.f, 0.f, 0.f);
     float4 pbias = mybias;  // the pair partner's bias (LayerStack)
     pbias.x = __shfl_xor_sync(0xffffffffu, mybias.x, 4); pbias.y = __shfl_xor_sync(0xffffffffu, mybias.y, 4);
     pbias.z = __shfl_xor_sync(0xffffffffu, mybias.z, 4); pbias.w = __shfl_xor_sync(0xffffffffu, mybias.w, 4);
-    const float4* __restrict__ t4 = reinterpret_cast<const float4*>(table);
-    // NQ index registers per lane: slots j, j + 8, ..., j + 8 (NQ - 1)
-    const float* s_lane = s_slice + 4 * j;
+    const ulonglong2* __restrict__ t2 = reinterpret_cast<const ulonglong2*>(table);
+    const unsigned char* s_lane = s_raw + 16 * j;
 
-    // software pipeline: item id two rounds ahead, its nnz and indices one round ahead
-    auto load_item = [&](int slot) { return slot < wk.end ? __ldg(items + slot) : -1; };
-    auto load_feats = [&](int it, int& n, int (&raw)[NQ]) {
-        n = 0;
-#pragma unroll
-        for (int q = 0; q < NQ; ++q) raw[q] = -1;
-        if (it >= 0) {
-            const int p = it >= B, b = it - p * B;
-            n = __ldg(nnz + b);
-            const int* ip = (p ? idx_nstm : idx_stm) + (size_t)b * A;
-#pragma unroll
-            for (int q = 0; q < NQ; ++q)
-                if (j + 8 * q < A) raw[q] = __ldg(ip + j + 8 * q);
-        }
-    };
-    const int per_round = 4 * (blockDim.x >> 5);
-    const int slot0 = wk.begin + 4 * warp + g;
-    int it_c = load_item(slot0), it_n = load_item(slot0 + per_round);
-    int n_c, raw_c[NQ];
-    load_feats(it_c, n_c, raw_c);
-    for (int base = wk.begin; base < wk.end; base += per_round) {
-        const int it_n2 = load_item(base + 2 * per_round + 4 * warp + g);
-        int n_n, raw_n[NQ];
-        load_feats(it_n, n_n, raw_n);
+    int buf = 0;
+    for (int base = wk.begin; base < wk.end; base += per_round, buf ^= 1) {
+        const int slot = base + 4 * warp + g;
+        const int inf = slot < wk.end ? __ldg(info + slot) : -1;
+        fetch_codes(base + per_round + 4 * warp, buf ^ 1);  // the other buffer was last read a round ago (warp barrier below)
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const bool slow = __any_sync(0xffffffffu, inf >= 0 && (inf & SLICE_SLOW_BIT));
+        const int it_c = inf < 0 ? -1 : (inf & ~SLICE_SLOW_BIT);
+        const unsigned char* my_codes = s_codes + buf * buf_stride + g * A_pad * 2;
 
-        // ---- current item: indices -> shared-memory float offsets (>= 0), global fallback (<= -2) or skip (-1)
-        const int n = n_c < 0 ? 0 : (n_c > A ? A : n_c);
-        int code[NQ];
-        bool outside = false;
-#pragma unroll
-        for (int q = 0; q < NQ; ++q) {
-            const int f = (j + 8 * q < n) ? raw_c[q] : -1;
-            int c = zero_row;  // skipped slot: the all-zero row
-            if ((unsigned)f < (unsigned)N) {
-                const int r = f - row0;
-                c = (unsigned)r < (unsigned)rows ? r * 32 : -(f + 2);
+        unsigned long long a0 = 0ull, a1 = 0ull;  // columns (0, 1) and (2, 3) of the lane
+        if (!slow) {
+            // every row of the round comes from the strip: branch-free; a slot without a feature reads the row of zeros
+            // (x + 0.0 == x), rows are added in slot order
+#pragma unroll 1
+            for (int q = 0; q < A_pad; q += 8) {
+                const uint4 c = *reinterpret_cast<const uint4*>(my_codes + 2 * q);
+                const ulonglong2 v0 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.x & 0xffffu) * 128u);
+                const ulonglong2 v1 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.x >> 16) * 128u);
+                const ulonglong2 v2 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.y & 0xffffu) * 128u);
+                const ulonglong2 v3 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.y >> 16) * 128u);
+                const ulonglong2 v4 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.z & 0xffffu) * 128u);
+                const ulonglong2 v5 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.z >> 16) * 128u);
+                const ulonglong2 v6 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.w & 0xffffu) * 128u);
+                const ulonglong2 v7 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.w >> 16) * 128u);
+                a0 = fadd2(a0, v0.x); a1 = fadd2(a1, v0.y);
+                a0 = fadd2(a0, v1.x); a1 = fadd2(a1, v1.y);
+                a0 = fadd2(a0, v2.x); a1 = fadd2(a1, v2.y);
+                a0 = fadd2(a0, v3.x); a1 = fadd2(a1, v3.y);
+                a0 = fadd2(a0, v4.x); a1 = fadd2(a1, v4.y);
+                a0 = fadd2(a0, v5.x); a1 = fadd2(a1, v5.y);
+                a0 = fadd2(a0, v6.x); a1 = fadd2(a1, v6.y);
+                a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
             }
-            outside |= c < 0;
-            code[q] = c;
-        }
-        int nmax = n;
-        nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, 8));
-        nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, 16));
-        const bool slow = __any_sync(0xffffffffu, outside);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int q = 0; q < NQ; ++q) {
-            if (8 * q >= nmax) break;
-            if (!slow) {
-                // every row of the round comes from the strip: branch-free; a skipped slot reads the all-zero row
-                // kept behind the strip (x + 0.0 == x).  Two batches of four rows keep the register count low
-                // enough for 32 warps per SM.
-#pragma unroll
-                for (int u0 = 0; u0 < 8; u0 += 4) {
-                    float4 v[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int c = __shfl_sync(0xffffffffu, code[q], (lane & 24) | (u0 + u));
-                        v[u] = *reinterpret_cast<const float4*>(s_lane + c);
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
-                }
-            } else {
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int c = __shfl_sync(0xffffffffu, code[q], (lane & 24) | u);
-                    float4 v;
-                    if (c >= 0) v = *reinterpret_cast<const float4*>(s_lane + c);
-                    else v = __ldg(t4 + (((size_t)(-c - 2) * F + mycol) >> 2));
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                }
+        } else {
+            const int p = it_c >= B, bb = it_c < 0 ? 0 : it_c - p * B;
+            const int* ip = (p ? idx_nstm : idx_stm) + (size_t)bb * A;
+            for (int q = 0; q < A_pad; ++q) {
+                const unsigned c = reinterpret_cast<const unsigned short*>(my_codes)[q];
+                ulonglong2 v;
+                if (c != SLICE_OUTSIDE || it_c < 0) v = *reinterpret_cast<const ulonglong2*>(s_lane + min(c, (unsigned)rps) * 128u);
+                else v = __ldg(t2 + (((size_t)__ldg(ip + q) * F + mycol) >> 2));
+                a0 = fadd2(a0, v.x); a1 = fadd2(a1, v.y);
             }
         }
+        __syncwarp();  // all lanes are done with this round's codes before the next round overwrites the other buffer's twin
+        const float4 acc = make_float4(lo_f(a0), hi_f(a0), lo_f(a1), hi_f(a1));
 
         // ---- epilogue
         const bool valid = it_c >= 0;
@@ -324,18 +382,23 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
             if (MODE == 3) { a.x *= a.x; a.y *= a.y; a.z *= a.z; a.w *= a.w; }
             __stcs(reinterpret_cast<float4*>(combined + (size_t)b * 2 * F + persp * F + mycol), a);
         }
-        it_c = it_n; it_n = it_n2; n_c = n_n;
-#pragma unroll
-        for (int q = 0; q < NQ; ++q) raw_c[q] = raw_n[q];
     }
+    cp_async_wait<0>();  // nothing of this block is in flight when it leaves
 }
 
-// work: [ceil(n_items / 1024) + keys + 1] FwdWork records followed by one int (their count)
-size_t ft_forward_slice_work_ints(int n_items, int n_keys) { return 4 * ((size_t)n_items / SLICE_IPC + n_keys + 2) + 4; }
+static inline int slice_a_pad(int A) { return (A + 7) / 8 * 8; }
+static inline size_t slice_max_work(int n_items, int n_keys) { return (size_t)n_items / SLICE_IPC + n_keys + 2; }
+
+// work: FwdWork records, one int (their count), the slot info [n_items], then the 16-bit row codes [n_items][A rounded up to 8]
+size_t ft_forward_slice_work_ints(int n_items, int n_keys, int A) {
+    return 4 * slice_max_work(n_items, n_keys) + 4 + ((size_t)n_items + 3) / 4 * 4 + ((size_t)n_items * slice_a_pad(A) + 1) / 2 + 4;
+}
+
+static inline size_t slice_smem_bytes(int rps, int A) { return ((size_t)rps + 1) * 128 + (size_t)2 * 32 * 4 * slice_a_pad(A) * 2; }
 
 bool ft_forward_slice_supported(int F, int N, int A, int rps) {
     int n_slices = ceil_div(N, rps);
-    return F % 32 == 0 && A <= 64 && ((size_t)rps + 1) * 128 <= 226 * 1024 && n_slices + 1 <= SORT_KEYS_MAX;
+    return F % 32 == 0 && A <= 64 && rps < 0xFFFF && slice_smem_bytes(rps, A) <= 227 * 1024 && n_slices + 1 <= SORT_KEYS_MAX;
 }
 
 int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
@@ -345,28 +408,32 @@ int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const 
     if (B <= 0) return 0;
     const int n_items = n_persp * B;
     const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
-    const int max_work = n_items / SLICE_IPC + n_keys + 2;
+    const int max_work = (int)slice_max_work(n_items, n_keys);
+    const int A_pad = slice_a_pad(A);
     FwdWork* wk = reinterpret_cast<FwdWork*>(work);
     int* n_work = work + 4 * (size_t)max_work;
+    int* info = n_work + 4;                                                            // 16-byte aligned
+    uint4* codes = reinterpret_cast<uint4*>(info + ((size_t)n_items + 3) / 4 * 4);     // 16-byte aligned
     k_fwd_plan<<<1, 128, 0, s>>>(item_seg, n_keys, wk, n_work);
-    const size_t smem = ((size_t)rps + 1) * 32 * sizeof(float);  // the strip and one row of zeros
+    k_fwd_codes<<<ceil_div(n_items, 256), 256, 0, s>>>(idx_stm, idx_nstm, nnz, items, item_seg, n_keys, n_items, B, N, A, A_pad,
+                                                       rps, codes, info);
+    const size_t smem = slice_smem_bytes(rps, A);
     dim3 grid(max_work, F / 32);
-#define FT_SLICE_ARGS table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, items, wk, n_work, B, F, N, A, rps, n_slices, scale
-#define FT_SLICE_LAUNCH(M, Q)                                                                                      \
-    do {                                                                                                           \
-        cudaFuncSetAttribute(k_ft_forward_slice<M, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-        k_ft_forward_slice<M, Q><<<grid, 1024, smem, s>>>(FT_SLICE_ARGS);                                          \
+#define FT_SLICE_LAUNCH(M)                                                                                        \
+    do {                                                                                                          \
+        cudaFuncSetAttribute(k_ft_forward_slice<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+        k_ft_forward_slice<M><<<grid, 1024, smem, s>>>(table, bias, pre_stm, pre_nstm, combined, idx_stm, idx_nstm, \
+                                                       info, codes, wk, n_work, n_items, B, F, N, A, A_pad, rps,  \
+                                                       scale);                                                    \
     } while (0)
-    const bool q5 = A <= 40;
     switch (mode) {
-        case 0: if (q5) FT_SLICE_LAUNCH(0, 5); else FT_SLICE_LAUNCH(0, 8); break;
-        case 1: if (q5) FT_SLICE_LAUNCH(1, 5); else FT_SLICE_LAUNCH(1, 8); break;
-        case 2: if (q5) FT_SLICE_LAUNCH(2, 5); else FT_SLICE_LAUNCH(2, 8); break;
-        default: if (q5) FT_SLICE_LAUNCH(3, 5); else FT_SLICE_LAUNCH(3, 8); break;
+        case 0: FT_SLICE_LAUNCH(0); break;
+        case 1: FT_SLICE_LAUNCH(1); break;
+        case 2: FT_SLICE_LAUNCH(2); break;
+        default: FT_SLICE_LAUNCH(3); break;
     }
 #undef FT_SLICE_LAUNCH
-#undef FT_SLICE_ARGS
-    return 2;
+    return 3;
 }
 
 // ------------------------------------------------------------------------------------------------

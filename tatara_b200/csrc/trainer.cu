@@ -621,7 +621,7 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->bias_partials, (size_t)DGRAD_CTAS * 2 * F));
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
     CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
-    CU(t, dalloc(&t->fwd_work, ft_forward_slice_work_ints((int)(2 * B), 129)));
+    CU(t, dalloc(&t->fwd_work, ft_forward_slice_work_ints((int)(2 * B), 129, A)));
     {
         const size_t max_work = (size_t)ft_backward_max_work((int)B, (int)A, 2);
         CU(t, dalloc(&t->bwd_plan, 2 + 2 * max_work + 3 * (size_t)N));
