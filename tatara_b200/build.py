@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libtatara_b200.so")
-SOURCES = ["ft_kernels.cu", "sort_kernels.cu", "dense_kernels.cu", "opt_kernels.cu", "psv.cu", "host_util.cu", "trainer.cu", "noalloc.cu"]
+SOURCES = ["ft_kernels.cu", "ft_slice_bwd.cu", "sort_kernels.cu", "dense_kernels.cu", "opt_kernels.cu", "psv.cu", "host_util.cu", "trainer.cu", "noalloc.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(os.path.dirname(HERE), "include", "tatara_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC",
               "-diag-suppress", "68"]

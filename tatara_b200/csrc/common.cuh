@@ -72,7 +72,8 @@ int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const 
 // scratch of the inverse index, in ints: histogram [2N], a counter, a queue of long lists [2N], scan block sums
 static inline size_t inverse_index_counts_len(int N) { return 4 * (size_t)N + 1 + 2 * ((size_t)N / 2048 + 2); }
 // counts: [inverse_index_counts_len(N)], offsets: [2][N+1], cursor: [2][N], lists: [4][B*A] (lists + sort scratch)
-int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
+// run_if (here and below): NULL, or a device flag; the launched kernels return at once while it is 0
+int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
                          int N, int n_persp, int* counts, int* offsets, int* cursor, int* lists);
 // one block per feature row, whatever the length of its list
 int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
@@ -80,9 +81,20 @@ int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_ns
 // long lists are cut into parts summed by separate blocks; plan: [2 + 2 * max_work + 3 * N] ints,
 // partial: [max_work][F] floats with max_work = ft_backward_max_work(B, A, n_persp)
 int ft_backward_max_work(int B, int A, int n_persp);
-int launch_ft_backward_split(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
+int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft_stm, const float* dft_nstm, const int* offsets,
                              const int* lists, int B, int A, int N, int F, int n_persp, int* plan, float* partial,
                              float* grad);
+// slice-resident weight gradient (ft_slice_bwd.cu).  Needs the slice-resident forward of the same step (its row codes
+// in fwd_work) and items / item_seg of the same rows_per_slice; bwd_work: ft_backward_slice_ints(...) ints.  The kernels
+// do nothing when the batch has a row outside its item's slice: *ft_slice_outside_flag(...) is then 1 and the generic
+// kernels, launched with it as run_if, do the work instead.
+bool ft_backward_slice_supported(int F, int N, int A, int rows_per_slice);
+size_t ft_backward_slice_ints(int n_items, int A, int rows_per_slice);
+const int* ft_slice_outside_flag(int* fwd_work, int n_items, int N, int rows_per_slice);
+int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int* bwd_work, int B, int A, int N,
+                         int rows_per_slice, int n_persp);
+int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
+                             int A, int N, int F, int rows_per_slice, int n_persp, float* grad);
 // items of both perspectives sorted by the table slice of their features; hist: [(slices + 1) * ceil(n_persp*B/1024)],
 // seg: [slices + 2]
 int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,

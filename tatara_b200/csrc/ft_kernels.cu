@@ -5,6 +5,7 @@
 // per-position tensor is row-major [B, F].  F is a multiple of 128, so rows are 512-byte aligned and
 // every access below is a 128-bit vector.
 #include "common.cuh"
+#include "ft_slice.cuh"
 
 #define SORT_KEYS_MAX 128  // key limit of the small-key sorts (sort_kernels.cu)
 
@@ -149,11 +150,6 @@ int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* i
 // LayerStack strips hold columns [16s, 16s+16) and their pair partners [F/2 + 16s, F/2 + 16s + 16); the other
 // modes 32 adjacent columns.
 // ------------------------------------------------------------------------------------------------
-#define SLICE_IPC 1024  // items per block
-struct FwdWork {
-    int slice, begin, end, pad;
-};
-
 __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork* __restrict__ work, int* __restrict__ n_work) {
     // n_keys = slices + 1 (the last key collects items without a usable first index)
     __shared__ int s_base[SORT_KEYS_MAX + 1];
@@ -164,7 +160,8 @@ __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork
             run += (item_seg[k + 1] - item_seg[k] + SLICE_IPC - 1) / SLICE_IPC;
         }
         s_base[n_keys] = run;
-        *n_work = run;
+        n_work[0] = run;
+        n_work[1] = 0;  // "some item has a row outside its slice", raised by k_fwd_codes
     }
     __syncthreads();
     for (int k = 0; k < n_keys; ++k) {
@@ -186,13 +183,11 @@ __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork
 // keeps a row of zeros there), SLICE_OUTSIDE for a table row outside the slice (the kernel then reads the index list).
 // info[slot] = item | SLICE_SLOW_BIT when the item has an outside row.  Codes of consecutive slots are contiguous
 // (A_pad 16-bit codes each, A_pad a multiple of 8), so a warp copies its round of four items in 16-byte pieces.
-#define SLICE_OUTSIDE 0xFFFFu
-#define SLICE_SLOW_BIT 0x40000000
 __global__ void __launch_bounds__(256) k_fwd_codes(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
                                                    const int* __restrict__ nnz, const int* __restrict__ items,
                                                    const int* __restrict__ item_seg, int n_keys, int n_items, int B, int N,
                                                    int A, int A_pad, int rps, uint4* __restrict__ codes,
-                                                   int* __restrict__ info) {
+                                                   int* __restrict__ info, int* __restrict__ outside_flag) {
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= n_items) return;
     int lo = 0, hi = n_keys - 1;  // the key whose segment holds slot s
@@ -227,25 +222,8 @@ __global__ void __launch_bounds__(256) k_fwd_codes(const int* __restrict__ idx_s
         codes[((size_t)s * A_pad + q0) >> 3] = make_uint4(c[0] | (c[1] << 16), c[2] | (c[3] << 16), c[4] | (c[5] << 16), c[6] | (c[7] << 16));
     }
     info[s] = it | (outside ? SLICE_SLOW_BIT : 0);
+    if (outside) *outside_flag = 1;
 }
-
-// two fp32 additions in one instruction (sm_100 packed arithmetic); each half is an IEEE round-to-nearest add
-static __device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-static __device__ __forceinline__ float lo_f(unsigned long long v) { return __uint_as_float((unsigned)v); }
-static __device__ __forceinline__ float hi_f(unsigned long long v) { return __uint_as_float((unsigned)(v >> 32)); }
-// asynchronous 16-byte copy global -> shared; src_bytes = 0 writes zeros and reads nothing
-static __device__ __forceinline__ void cp_async16(void* dst_shared, const void* src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src),
-                 "r"(src_bytes)
-                 : "memory");
-}
-static __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N_PENDING>
-static __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_PENDING) : "memory"); }
 
 template <int MODE>
 __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __restrict__ table, const float* __restrict__ bias,
@@ -386,8 +364,6 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
     cp_async_wait<0>();  // nothing of this block is in flight when it leaves
 }
 
-static inline int slice_a_pad(int A) { return (A + 7) / 8 * 8; }
-static inline size_t slice_max_work(int n_items, int n_keys) { return (size_t)n_items / SLICE_IPC + n_keys + 2; }
 
 // work: FwdWork records, one int (their count), the slot info [n_items], then the 16-bit row codes [n_items][A rounded up to 8]
 size_t ft_forward_slice_work_ints(int n_items, int n_keys, int A) {
@@ -410,13 +386,14 @@ int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const 
     const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
     const int max_work = (int)slice_max_work(n_items, n_keys);
     const int A_pad = slice_a_pad(A);
-    FwdWork* wk = reinterpret_cast<FwdWork*>(work);
-    int* n_work = work + 4 * (size_t)max_work;
-    int* info = n_work + 4;                                                            // 16-byte aligned
-    uint4* codes = reinterpret_cast<uint4*>(info + ((size_t)n_items + 3) / 4 * 4);     // 16-byte aligned
+    const SliceBuffers sb = slice_buffers(work, n_items, n_keys);
+    FwdWork* wk = sb.work;
+    int* n_work = sb.n_work;
+    int* info = sb.info;
+    uint4* codes = sb.codes;
     k_fwd_plan<<<1, 128, 0, s>>>(item_seg, n_keys, wk, n_work);
     k_fwd_codes<<<ceil_div(n_items, 256), 256, 0, s>>>(idx_stm, idx_nstm, nnz, items, item_seg, n_keys, n_items, B, N, A, A_pad,
-                                                       rps, codes, info);
+                                                       rps, codes, info, sb.outside_flag);
     const size_t smem = slice_smem_bytes(rps, A);
     dim3 grid(max_work, F / 32);
 #define FT_SLICE_LAUNCH(M)                                                                                        \
@@ -441,7 +418,8 @@ int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const 
 // native_kernels.cu:1630-1765: histogram, exclusive scan, ranked scatter).
 // ------------------------------------------------------------------------------------------------
 __global__ void k_feat_count(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
-                             const int* __restrict__ nnz, int B, int A, int N, int n_persp, int* __restrict__ counts) {
+                             const int* __restrict__ nnz, int B, int A, int N, int n_persp, int* __restrict__ counts, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const long long total = (long long)n_persp * B * A;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int p = (int)(i / ((long long)B * A));
@@ -457,7 +435,8 @@ __global__ void k_feat_count(const int* __restrict__ idx_stm, const int* __restr
 // cells with their sums, then every block adds the sums of the blocks before it.
 #define SCAN_CELLS 2048
 __global__ void __launch_bounds__(1024) k_feat_scan_local(const int* __restrict__ counts, int N, int* __restrict__ offsets,
-                                                           int* __restrict__ block_sums) {
+                                                           int* __restrict__ block_sums, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     __shared__ int warp_tot[32];
     const int p = blockIdx.y;
     const int* c = counts + (size_t)p * N;
@@ -492,7 +471,8 @@ __global__ void __launch_bounds__(1024) k_feat_scan_local(const int* __restrict_
 }
 
 __global__ void __launch_bounds__(1024) k_feat_scan_add(int N, int* __restrict__ offsets, int* __restrict__ cursor,
-                                                         const int* __restrict__ block_sums) {
+                                                         const int* __restrict__ block_sums, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     __shared__ int s_off;
     const int p = blockIdx.y;
     int* o = offsets + (size_t)p * (N + 1);
@@ -514,7 +494,8 @@ __global__ void __launch_bounds__(1024) k_feat_scan_add(int N, int* __restrict__
 
 __global__ void k_feat_fill(const int* __restrict__ idx_stm, const int* __restrict__ idx_nstm,
                             const int* __restrict__ nnz, int B, int A, int N, int n_persp, int* __restrict__ cursor,
-                            int* __restrict__ lists) {
+                            int* __restrict__ lists, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const long long total = (long long)n_persp * B * A;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int p = (int)(i / ((long long)B * A));
@@ -537,7 +518,8 @@ __global__ void k_feat_fill(const int* __restrict__ idx_stm, const int* __restri
 // index row repeats a feature) falls back to ranking by counting.
 __global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict__ offsets, int N, int n_persp, int B, int A,
                                                            int* __restrict__ lists, int* __restrict__ long_queue,
-                                                           int* __restrict__ long_count) {
+                                                           int* __restrict__ long_count, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= n_persp * N) return;
@@ -566,7 +548,8 @@ __global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict_
 __global__ void __launch_bounds__(256) k_lists_sort_long(const int* __restrict__ offsets, int N, int B, int A,
                                                           int* __restrict__ lists, int* __restrict__ scratch,
                                                           const int* __restrict__ long_queue,
-                                                          const int* __restrict__ long_count, int bitmap_words) {
+                                                          const int* __restrict__ long_count, int bitmap_words, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     extern __shared__ unsigned s_bits[];  // [bitmap_words]; 0 words: always use the counting fallback
     __shared__ int s_warp[8];
     __shared__ int s_total;
@@ -638,7 +621,7 @@ __global__ void __launch_bounds__(256) k_lists_sort_long(const int* __restrict__
     }
 }
 
-int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
+int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
                          int N, int n_persp, int* counts, int* offsets, int* cursor, int* lists) {
     if (B <= 0) return 0;
     // counts holds [2][N] histogram cells followed by one counter and a queue of [2*N] long-list ids
@@ -648,17 +631,17 @@ int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm
     const long long total = (long long)n_persp * B * A;
     int blocks = (int)((total + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
-    k_feat_count<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, counts);
+    k_feat_count<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, counts, run_if);
     {   // block sums live behind the long-list queue (which holds at most 2N ids)
         int* block_sums = long_queue + (size_t)2 * N;
         const dim3 sg(ceil_div(N, SCAN_CELLS), n_persp);
-        k_feat_scan_local<<<sg, 1024, 0, s>>>(counts, N, offsets, block_sums);
-        k_feat_scan_add<<<sg, 1024, 0, s>>>(N, offsets, cursor, block_sums);
+        k_feat_scan_local<<<sg, 1024, 0, s>>>(counts, N, offsets, block_sums, run_if);
+        k_feat_scan_add<<<sg, 1024, 0, s>>>(N, offsets, cursor, block_sums, run_if);
     }
-    k_feat_fill<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, cursor, lists);
+    k_feat_fill<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, cursor, lists, run_if);
     int* scratch = lists + (size_t)2 * B * A;  // the list buffer carries a second copy's worth of room
     const long long warps = (long long)n_persp * N;
-    k_lists_sort_short<<<(int)((warps * 32 + 255) / 256), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count);
+    k_lists_sort_short<<<(int)((warps * 32 + 255) / 256), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count, run_if);
     int words = (B + 31) / 32;
     if ((size_t)words * 4 > 160 * 1024) words = 0;
     static bool attr_set = false;
@@ -666,7 +649,7 @@ int launch_inverse_index(cudaStream_t s, const int* idx_stm, const int* idx_nstm
         cudaFuncSetAttribute(k_lists_sort_long, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         attr_set = true;
     }
-    k_lists_sort_long<<<148 * 4, 256, (size_t)words * 4, s>>>(offsets, N, B, A, lists, scratch, long_queue, long_count, words);
+    k_lists_sort_long<<<148 * 4, 256, (size_t)words * 4, s>>>(offsets, N, B, A, lists, scratch, long_queue, long_count, words, run_if);
     return 6;
 }
 
@@ -722,7 +705,8 @@ int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_ns
 #define BWD_PART 4096
 
 __global__ void k_bwd_plan(const int* __restrict__ offsets, int N, int n_persp, int* __restrict__ counters,
-                           int2* __restrict__ work, int* __restrict__ longf) {
+                           int2* __restrict__ work, int* __restrict__ longf, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const int f = blockIdx.x * blockDim.x + threadIdx.x;
     if (f >= N) return;
     int len = 0;
@@ -756,7 +740,8 @@ static __device__ __forceinline__ float4 sum_rows(const float4* __restrict__ d, 
 
 __global__ void __launch_bounds__(512) k_ft_backward_short(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
                                                              const int* __restrict__ offsets, const int* __restrict__ lists,
-                                                             int B, int A, int N, int F, int n_persp, float* __restrict__ grad) {
+                                                             int B, int A, int N, int F, int n_persp, float* __restrict__ grad, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const int f = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
@@ -790,7 +775,8 @@ __global__ void __launch_bounds__(512) k_ft_backward_long(const float* __restric
                                                             const int* __restrict__ offsets, const int* __restrict__ lists,
                                                             int B, int A, int N, int F, int n_persp,
                                                             const int* __restrict__ counters, const int2* __restrict__ work,
-                                                            float* __restrict__ partial) {
+                                                            float* __restrict__ partial, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
     const int n_work = counters[0];
@@ -814,7 +800,8 @@ __global__ void __launch_bounds__(512) k_ft_backward_long(const float* __restric
 
 __global__ void __launch_bounds__(512) k_ft_backward_long_final(const int* __restrict__ counters, const int* __restrict__ longf,
                                                                   const float* __restrict__ partial, int F,
-                                                                  float* __restrict__ grad) {
+                                                                  float* __restrict__ grad, const int* __restrict__ run_if) {
+    if (run_if && *run_if == 0) return;  // gated: another path does this step's work
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
     const int n_long = counters[1];
@@ -833,7 +820,7 @@ __global__ void __launch_bounds__(512) k_ft_backward_long_final(const int* __res
 int ft_backward_max_work(int B, int A, int n_persp) { return 2 * (int)(((long long)n_persp * B * A) / BWD_PART) + 2; }
 
 // plan: [2] counters, then [2 * max_work] work items, then [3 * N] long-feature records; partial: [max_work][F]
-int launch_ft_backward_split(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
+int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft_stm, const float* dft_nstm, const int* offsets,
                              const int* lists, int B, int A, int N, int F, int n_persp, int* plan, float* partial,
                              float* grad) {
     const int max_work = ft_backward_max_work(B, A, n_persp);
@@ -841,11 +828,11 @@ int launch_ft_backward_split(cudaStream_t s, const float* dft_stm, const float* 
     int2* work = reinterpret_cast<int2*>(plan + 2);
     int* longf = plan + 2 + 2 * max_work;
     cudaMemsetAsync(counters, 0, 2 * sizeof(int), s);
-    k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf);
+    k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf, run_if);
     const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
-    k_ft_backward_short<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
-    k_ft_backward_long<<<dim3(148 * 4, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial);
-    k_ft_backward_long_final<<<dim3(148 * 2, ny), bx, 0, s>>>(counters, longf, partial, F, grad);
+    k_ft_backward_short<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
+    k_ft_backward_long<<<dim3(148 * 4, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial, run_if);
+    k_ft_backward_long_final<<<dim3(148 * 2, ny), bx, 0, s>>>(counters, longf, partial, F, grad, run_if);
     return 4;
 }
 

@@ -1,0 +1,395 @@
+// FT weight gradient, slice-resident variant (the transposed twin of k_ft_forward_slice).
+//
+// When every feature of an item lies in the item's own king-bucket slice of the table (true for the king-relative
+// feature sets by construction; k_fwd_codes checks it for the batch at hand), a feature row of slice k is touched
+// only by the items sorted into slice k.  The slice's items are cut into chunks of <= CH consecutive slots; for
+// each chunk one block builds the inverse index locally (k_inv_chunk: for every row of the slice the ascending
+// list of chunk-local slots that hold it, by a stable counting sort in shared memory, no atomics, no per-list
+// sort), and the gradient kernel keeps a 32-column strip of the chunk's dft rows in shared memory together with
+// all of the chunk's lists, so that every row read of the sum comes from shared memory.
+// A block owns (slice, column strip), walks the slice's chunks in order and carries the running sums through the
+// gradient rows themselves, so a row's terms are added one by one in ascending item order: the result is
+// bit-identical to the per-row sequential sum of the generic kernels (stm items first, ascending position).
+//
+// Both kernels return at once when the batch has a row outside its item's slice (outside_flag != 0); the generic
+// kernels, gated the other way round, then do the work.
+#include "ft_slice.cuh"
+
+#define INV_SORT_N 2048  // rows per slice limit (bitonic sort size)
+
+struct BwdLayout {
+    int CH;             // slots per chunk (multiple of 32)
+    int rps_pad;        // row records per chunk
+    int region;         // 16-bit list cells per chunk (multiple of 8)
+    int max_chunks;
+    size_t off_first, off_len, off_rowinfo, off_lists, total_ints;
+};
+
+static inline size_t bwd_smem_bytes(int CH, int rps, int A_pad) {
+    const int rps_pad = (rps + 3) / 4 * 4;
+    return ((size_t)CH + 1) * 128 + (size_t)rps_pad * 8 + ((size_t)CH * A_pad + 8 * (size_t)rps) * 2;
+}
+
+static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
+    BwdLayout L;
+    const int A_pad = slice_a_pad(A);
+    int CH = 0;
+    for (int c = 32; c <= 4096; c += 32) {
+        if (bwd_smem_bytes(c, rps, A_pad) > 227 * 1024) break;
+        if ((size_t)c * A_pad + 8 * (size_t)rps > 65535) break;
+        CH = c;
+    }
+    L.CH = CH;
+    L.rps_pad = (rps + 3) / 4 * 4;
+    L.region = CH * A_pad + 8 * rps;
+    L.max_chunks = CH > 0 ? n_items / CH + SORT_KEYS_LIMIT + 2 : 0;
+    size_t o = 4 * (size_t)L.max_chunks + 4;            // chunk records + their count
+    L.off_first = o; o += SORT_KEYS_LIMIT + 4;          // first chunk of every slice (+ end)
+    L.off_len = o; o += ((size_t)L.max_chunks + 3) / 4 * 4;
+    L.off_rowinfo = o; o += 2 * (size_t)L.max_chunks * L.rps_pad;
+    L.off_lists = o; o += ((size_t)L.max_chunks * L.region + 1) / 2 + 4;
+    L.total_ints = o;
+    return L;
+}
+
+bool ft_backward_slice_supported(int F, int N, int A, int rps) {
+    const int n_slices = ceil_div(N, rps);
+    if (!(F % 32 == 0 && A <= 64 && rps <= INV_SORT_N && n_slices + 1 <= SORT_KEYS_LIMIT)) return false;
+    return bwd_layout(1024, A, rps).CH >= 64;
+}
+
+size_t ft_backward_slice_ints(int n_items, int A, int rps) { return bwd_layout(n_items, A, rps).total_ints; }
+
+// chunks of <= ipc consecutive slots of one slice; first[k] = index of slice k's first chunk, first[n_keys] = total
+__global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int ipc, FwdWork* __restrict__ work,
+                             int* __restrict__ n_work, int* __restrict__ first) {
+    __shared__ int s_base[SORT_KEYS_LIMIT + 1];
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int k = 0; k < n_keys; ++k) {
+            s_base[k] = run;
+            run += (item_seg[k + 1] - item_seg[k] + ipc - 1) / ipc;
+        }
+        s_base[n_keys] = run;
+        *n_work = run;
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k <= n_keys; k += blockDim.x) first[k] = s_base[k];
+    for (int k = 0; k < n_keys; ++k) {
+        const int b0 = item_seg[k], e0 = item_seg[k + 1];
+        const int n = s_base[k + 1] - s_base[k];
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            FwdWork w;
+            w.slice = k;
+            w.begin = b0 + i * ipc;
+            w.end = min(e0, w.begin + ipc);
+            w.pad = 0;
+            work[s_base[k] + i] = w;
+        }
+    }
+}
+
+// Inverse index of one chunk.  Shared memory: hist [32 warps][rps_h] 16-bit cells, rowoff [rps] ints, sort keys
+// [INV_SORT_N] ints, the chunk's row codes [CH][A_pad].  Warp w owns a contiguous range of the chunk's slots, so "warp, then step, then lane" is
+// ascending slot order and the ranked scatter is stable.
+// rowinfo (sorted by descending list length, so that the eight-lane groups of a warp get lists of similar length
+// and the long lists start first): row << 32 | list offset << 16 | list length; lists are padded to a multiple of
+// eight cells with the index of the chunk's row of zeros (CH).
+__global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __restrict__ codes, const FwdWork* __restrict__ work,
+                                                    const int* __restrict__ n_work, const int* __restrict__ outside_flag,
+                                                    int n_slices, int A_pad, int rps, int rps_pad, int CH, int region,
+                                                    unsigned short* __restrict__ lists, unsigned long long* __restrict__ rowinfo,
+                                                    int* __restrict__ len) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    if ((int)blockIdx.x >= *n_work || *outside_flag) return;
+    const FwdWork wk = work[blockIdx.x];
+    if (wk.slice >= n_slices) return;  // items without a slice have no rows
+    const int rps_h = (rps + 1) & ~1;
+    unsigned short* s_hist = reinterpret_cast<unsigned short*>(s_raw);                    // [32][rps_h]
+    int* s_rowoff = reinterpret_cast<int*>(s_raw + (size_t)32 * rps_h * 2);               // [rps]
+    unsigned* s_keys = reinterpret_cast<unsigned*>(s_rowoff + INV_SORT_N);                // [INV_SORT_N]
+    unsigned short* s_codes = reinterpret_cast<unsigned short*>(s_keys + INV_SORT_N);     // [CH][A_pad]
+    __shared__ int s_warp[32];
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int n = wk.end - wk.begin;
+    {   // the chunk's codes: n * A_pad cells, a multiple of 16 bytes from a 16-byte aligned start
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(codes + (size_t)wk.begin * A_pad);
+        for (int e = tid; e < n * A_pad / 8; e += 1024) cp_async16(reinterpret_cast<unsigned char*>(s_codes) + (size_t)e * 16, src + (size_t)e * 16, 16);
+        cp_async_commit();
+    }
+    for (int e = tid; e < 16 * rps_h; e += 1024) reinterpret_cast<unsigned*>(s_hist)[e] = 0u;
+    cp_async_wait<0>();
+    __syncthreads();
+
+    const int per = (n + 31) >> 5;
+    const int s0 = min(n, w * per), s1 = min(n, s0 + per);
+    const int n_e = (s1 - s0) * A_pad;
+    const unsigned short* cw = s_codes + (size_t)s0 * A_pad;
+    unsigned short* my_hist = s_hist + (size_t)w * rps_h;
+
+    // pass 1: per-warp histogram
+    for (int e0 = 0; e0 < n_e; e0 += 32) {
+        const int e = e0 + lane;
+        const unsigned code = e < n_e ? cw[e] : 0xFFFFu;
+        const bool valid = code < (unsigned)rps;
+        const unsigned m = __match_any_sync(0xffffffffu, valid ? code : (0x10000u | lane));
+        if (valid && lane == __ffs(m) - 1) my_hist[code] = (unsigned short)(my_hist[code] + __popc(m));
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // per row: counts of the warps -> exclusive prefix over the warps; list offsets by a block scan of padded lengths
+    const int rpt = (rps + 1023) >> 10;  // rows per thread (<= 2)
+    int cnt[2] = {0, 0}, padded = 0;
+    for (int u = 0; u < rpt; ++u) {
+        const int r = tid * rpt + u;
+        if (r < rps) {
+            int run = 0;
+            for (int ww = 0; ww < 32; ++ww) {
+                const int c = s_hist[(size_t)ww * rps_h + r];
+                s_hist[(size_t)ww * rps_h + r] = (unsigned short)run;
+                run += c;
+            }
+            cnt[u] = run;
+            padded += (run + 7) & ~7;
+        }
+    }
+    int incl = padded;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += t;
+    }
+    if (lane == 31) s_warp[w] = incl;
+    __syncthreads();
+    if (w == 0) {
+        const int t = s_warp[lane];
+        int ti = t;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, ti, d);
+            if (lane >= d) ti += u;
+        }
+        s_warp[lane] = ti - t;
+    }
+    __syncthreads();
+    unsigned short* my_lists = lists + (size_t)blockIdx.x * region;
+    int base = s_warp[w] + incl - padded;
+    for (int u = 0; u < rpt; ++u) {
+        const int r = tid * rpt + u;
+        if (r < rps) {
+            s_rowoff[r] = base;
+            const int pe = base + ((cnt[u] + 7) & ~7);
+            for (int i = base + cnt[u]; i < pe; ++i) my_lists[i] = (unsigned short)CH;
+            base = pe;
+        }
+    }
+    if (tid == 1023) len[blockIdx.x] = base;
+    // sort keys: ascending (65535 - length) << 11 | row, unused cells last
+    for (int i = tid; i < INV_SORT_N; i += 1024) s_keys[i] = 0xFFFFFFFFu;
+    __syncthreads();
+    for (int u = 0; u < rpt; ++u) {
+        const int r = tid * rpt + u;
+        if (r < rps) s_keys[r] = ((unsigned)(65535 - cnt[u]) << 11) | (unsigned)r;
+    }
+    __syncthreads();
+    for (int k = 2; k <= INV_SORT_N; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const int i = ((tid & ~(j - 1)) << 1) | (tid & (j - 1));
+            const int p = i | j;
+            const unsigned a = s_keys[i], b = s_keys[p];
+            const bool up = (i & k) == 0;
+            if ((a > b) == up) { s_keys[i] = b; s_keys[p] = a; }
+            __syncthreads();
+        }
+    }
+    unsigned long long* my_info = rowinfo + (size_t)blockIdx.x * rps_pad;
+    for (int i = tid; i < rps_pad; i += 1024) {
+        unsigned long long v = 0ull;  // row 0, empty list (cells past rps are never used)
+        if (i < rps) {
+            const unsigned key = s_keys[i];
+            const unsigned r = key & 2047u, c = 65535u - (key >> 11);
+            v = ((unsigned long long)r << 32) | ((unsigned long long)(unsigned)s_rowoff[r] << 16) | c;
+        }
+        my_info[i] = v;
+    }
+
+    // pass 2: stable ranked scatter of the chunk-local slot numbers
+    for (int e0 = 0; e0 < n_e; e0 += 32) {
+        const int e = e0 + lane;
+        const unsigned code = e < n_e ? cw[e] : 0xFFFFu;
+        const bool valid = code < (unsigned)rps;
+        const unsigned m = __match_any_sync(0xffffffffu, valid ? code : (0x10000u | lane));
+        int at = 0;
+        if (valid) at = s_rowoff[code] + my_hist[code] + __popc(m & ((1u << lane) - 1u));
+        __syncwarp();
+        if (valid) {
+            my_lists[at] = (unsigned short)(s0 + e / A_pad);
+            if (lane == __ffs(m) - 1) my_hist[code] = (unsigned short)(my_hist[code] + __popc(m));
+        }
+        __syncwarp();
+    }
+}
+
+// grad[row][32-column strip] for the rows of one slice; see the head of the file.
+__global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+                                                                const int* __restrict__ info, const FwdWork* __restrict__ work,
+                                                                const int* __restrict__ first, const int* __restrict__ len,
+                                                                const unsigned long long* __restrict__ rowinfo,
+                                                                const unsigned short* __restrict__ lists,
+                                                                const int* __restrict__ outside_flag, int B, int F, int N, int rps,
+                                                                int rps_pad, int CH, int region, float* __restrict__ grad) {
+    // dft strip [CH + 1][32] floats (the last row stays zero), row records [rps_pad] 64-bit, list cells [region] 16-bit
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    if (*outside_flag) return;
+    const int k = blockIdx.x, strip = blockIdx.y;
+    const int row0 = k * rps;
+    const int rows = min(rps, N - row0);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int j = lane & 7;
+    const int group = tid >> 3;  // 128 eight-lane groups
+    const int col = 32 * strip + 4 * j;
+    const int c_first = first[k], c_end = first[k + 1];
+    if (c_first == c_end) {  // no item reads this slice: its gradient rows are zero
+        for (int e = tid; e < rows * 8; e += 1024)
+            *reinterpret_cast<float4*>(grad + (size_t)(row0 + (e >> 3)) * F + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    unsigned char* s_dft = s_raw;
+    unsigned long long* s_info = reinterpret_cast<unsigned long long*>(s_raw + ((size_t)CH + 1) * 128);
+    unsigned char* s_lists = reinterpret_cast<unsigned char*>(s_info + rps_pad);
+    if (tid < 32) reinterpret_cast<float*>(s_dft)[CH * 32 + tid] = 0.f;
+    const unsigned char* s_lane = s_dft + 16 * j;
+
+    for (int c = c_first; c < c_end; ++c) {
+        const FwdWork wk = work[c];
+        const int n = wk.end - wk.begin;
+        const int L = len[c];
+        __syncthreads();  // the previous chunk's sums are done with the buffers (and its gradient rows are written)
+        for (int e = tid; e < n * 8; e += 1024) {  // thread e & 7 == j copies the 16 bytes of row e >> 3 it will read
+            const int it = __ldg(info + wk.begin + (e >> 3)) & ~SLICE_SLOW_BIT;
+            const int p = it >= B, b = it - p * B;
+            cp_async16(s_dft + (size_t)e * 16, (p ? dft_nstm : dft_stm) + (size_t)b * F + col, 16);
+        }
+        {
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(rowinfo + (size_t)c * rps_pad);
+            for (int e = tid; e < rps_pad / 2; e += 1024) cp_async16(reinterpret_cast<unsigned char*>(s_info) + (size_t)e * 16, src + (size_t)e * 16, 16);
+            const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(lists + (size_t)c * region);
+            for (int e = tid; e < L / 8; e += 1024) cp_async16(s_lists + (size_t)e * 16, lsrc + (size_t)e * 16, 16);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+
+        const bool first_chunk = c == c_first;
+        // the records are sorted by descending list length; group g takes records g, 255 - g, 256 + g, 511 - g, ...
+        // so that the groups' totals even out and the four groups of a warp run lists of similar length
+        for (int i0 = 0, turn = 0; i0 < rps; i0 += 128, turn ^= 1) {
+            const int i = i0 + (turn ? 127 - group : group);
+            if (i >= rps) continue;
+            const unsigned long long ri = s_info[i];
+            const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
+            if (r >= rows || (cnt == 0 && !first_chunk)) continue;
+            float* gp = grad + (size_t)(row0 + r) * F + col;
+            unsigned long long a0 = 0ull, a1 = 0ull;
+            if (!first_chunk) {
+                const ulonglong2 g = __ldcg(reinterpret_cast<const ulonglong2*>(gp));
+                a0 = g.x; a1 = g.y;
+            }
+            const unsigned char* lp = s_lists + 2 * off;
+            const int full = cnt & ~7;
+            for (int q = 0; q < full; q += 8) {
+                const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * q);
+                const ulonglong2 v0 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x & 0xffffu) * 128u);
+                const ulonglong2 v1 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x >> 16) * 128u);
+                const ulonglong2 v2 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.y & 0xffffu) * 128u);
+                const ulonglong2 v3 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.y >> 16) * 128u);
+                const ulonglong2 v4 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.z & 0xffffu) * 128u);
+                const ulonglong2 v5 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.z >> 16) * 128u);
+                const ulonglong2 v6 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.w & 0xffffu) * 128u);
+                const ulonglong2 v7 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.w >> 16) * 128u);
+                a0 = fadd2(a0, v0.x); a1 = fadd2(a1, v0.y);
+                a0 = fadd2(a0, v1.x); a1 = fadd2(a1, v1.y);
+                a0 = fadd2(a0, v2.x); a1 = fadd2(a1, v2.y);
+                a0 = fadd2(a0, v3.x); a1 = fadd2(a1, v3.y);
+                a0 = fadd2(a0, v4.x); a1 = fadd2(a1, v4.y);
+                a0 = fadd2(a0, v5.x); a1 = fadd2(a1, v5.y);
+                a0 = fadd2(a0, v6.x); a1 = fadd2(a1, v6.y);
+                a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
+            }
+            if (full < cnt) {  // the last one to seven entries; the padding cells behind them are not read as rows
+                const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * full);
+                const unsigned cell[8] = {cc.x & 0xffffu, cc.x >> 16, cc.y & 0xffffu, cc.y >> 16,
+                                          cc.z & 0xffffu, cc.z >> 16, cc.w & 0xffffu, cc.w >> 16};
+                const int rem = cnt - full;
+                ulonglong2 v[7];
+#pragma unroll
+                for (int u = 0; u < 7; ++u) {
+                    v[u] = make_ulonglong2(0ull, 0ull);
+                    if (u < rem) v[u] = *reinterpret_cast<const ulonglong2*>(s_lane + cell[u] * 128u);
+                }
+#pragma unroll
+                for (int u = 0; u < 7; ++u)
+                    if (u < rem) { a0 = fadd2(a0, v[u].x); a1 = fadd2(a1, v[u].y); }
+            }
+            __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(a0, a1));
+        }
+    }
+}
+
+struct BwdPointers {
+    FwdWork* chunks;
+    int *n_chunks, *first, *len;
+    unsigned long long* rowinfo;
+    unsigned short* lists;
+};
+static inline BwdPointers bwd_pointers(int* bwd_work, const BwdLayout& L) {
+    BwdPointers p;
+    p.chunks = reinterpret_cast<FwdWork*>(bwd_work);
+    p.n_chunks = bwd_work + 4 * (size_t)L.max_chunks;
+    p.first = bwd_work + L.off_first;
+    p.len = bwd_work + L.off_len;
+    p.rowinfo = reinterpret_cast<unsigned long long*>(bwd_work + L.off_rowinfo);
+    p.lists = reinterpret_cast<unsigned short*>(bwd_work + L.off_lists);
+    return p;
+}
+
+const int* ft_slice_outside_flag(int* fwd_work, int n_items, int N, int rps) {
+    return slice_buffers(fwd_work, n_items, ceil_div(N, rps) + 1).outside_flag;
+}
+
+int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int* bwd_work, int B, int A, int N, int rps,
+                         int n_persp) {
+    if (B <= 0) return 0;
+    const int n_items = n_persp * B;
+    const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
+    const int A_pad = slice_a_pad(A);
+    const SliceBuffers sb = slice_buffers(fwd_work, n_items, n_keys);
+    const BwdLayout L = bwd_layout(n_items, A, rps);
+    const BwdPointers P = bwd_pointers(bwd_work, L);
+    k_chunk_plan<<<1, 128, 0, s>>>(item_seg, n_keys, L.CH, P.chunks, P.n_chunks, P.first);
+    const int rps_h = (rps + 1) & ~1;
+    const size_t inv_smem = (size_t)32 * rps_h * 2 + (size_t)INV_SORT_N * 4 * 2 + (size_t)L.CH * A_pad * 2;
+    cudaFuncSetAttribute(k_inv_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)inv_smem);
+    k_inv_chunk<<<L.max_chunks, 1024, inv_smem, s>>>(reinterpret_cast<const unsigned short*>(sb.codes), P.chunks, P.n_chunks,
+                                                     sb.outside_flag, n_slices, A_pad, rps, L.rps_pad, L.CH, L.region, P.lists,
+                                                     P.rowinfo, P.len);
+    return 2;
+}
+
+int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
+                             int A, int N, int F, int rps, int n_persp, float* grad) {
+    if (B <= 0) return 0;
+    const int n_items = n_persp * B;
+    const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
+    const int A_pad = slice_a_pad(A);
+    const SliceBuffers sb = slice_buffers(fwd_work, n_items, n_keys);
+    const BwdLayout L = bwd_layout(n_items, A, rps);
+    const BwdPointers P = bwd_pointers(bwd_work, L);
+    const size_t smem = bwd_smem_bytes(L.CH, rps, A_pad);
+    cudaFuncSetAttribute(k_ft_backward_slice, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k_ft_backward_slice<<<dim3(n_slices, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len, P.rowinfo,
+                                                                   P.lists, sb.outside_flag, B, F, N, rps, L.rps_pad, L.CH, L.region,
+                                                                   grad);
+    return 1;
+}

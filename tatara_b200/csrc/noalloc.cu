@@ -90,7 +90,7 @@ extern "C" int tb_ft_backward_static_scratch(const float* d_dft, const int32_t* 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // launch_inverse_index clears the histogram and the long-list counter itself; offsets, cursors and lists are
     // fully rewritten for the rows and slots this call uses
-    launch_inverse_index(s, d_indices, d_indices, d_nnz, batch, max_active, ft_in, 1, counts, offsets, cursor, lists);
+    launch_inverse_index(s, nullptr, d_indices, d_indices, d_nnz, batch, max_active, ft_in, 1, counts, offsets, cursor, lists);
     launch_ft_backward(s, d_dft, d_dft, offsets, lists, batch, max_active, ft_in, ft_out, 1, d_grad);
     e = cudaGetLastError();
     if (e != cudaSuccess) {

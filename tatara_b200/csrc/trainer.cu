@@ -119,7 +119,8 @@ struct tb_trainer {
     TileDesc* tiles = nullptr;
     float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr;
     int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
-    int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr;
+    int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr, *bwd_slice = nullptr;
+    bool slice_fwd = false;  // this step's forward ran slice-resident (its row codes are in fwd_work)
     float* bwd_partial = nullptr;
     int last_n = 0;
     // loss ring (AsyncLossRing, trainer_common.rs:909-1000)
@@ -310,9 +311,9 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
       p.done(n); }
     { PhaseScope p(t, PH_FT_FWD);
       const int mode = ls ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
-      static const bool no_slice = getenv("TATARA_DEBUG_NO_SLICE_FWD") != nullptr;
       const int rps = c.piece_inputs > 0 ? c.piece_inputs : N;
-      if (!no_slice && ft_forward_slice_supported(F, N, A, rps))
+      t->slice_fwd = ft_forward_slice_supported(F, N, A, rps);
+      if (t->slice_fwd)
           p.done(launch_ft_forward_slice(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1],
                                          t->combined, t->items, t->item_seg, t->fwd_work, B, F, N, A, rps, FT_POST_SCALE, 2));
       else
@@ -371,16 +372,25 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
                                         FT_POST_SCALE, B, F, c.l1_out, 0, t->dft[0], t->dft[1], t->bias_partials,
                                         t->groups[1].grad, DGRAD_CTAS)); }
     }
+    // slice-resident path when this step's forward was; the generic kernels then run only for a batch with a row outside
+    // its item's slice (device-side gate)
+    const int rps = c.piece_inputs > 0 ? c.piece_inputs : N;
+    const bool slice_bwd = t->slice_fwd && t->bwd_slice != nullptr;
+    const int* gate = slice_bwd ? ft_slice_outside_flag(t->fwd_work, 2 * B, N, rps) : nullptr;
     { PhaseScope p(t, PH_INV_INDEX);
-      p.done(launch_inverse_index(t->stream, d.stm, d.nstm, d.nnz, B, A, N, 2, t->feat_counts, t->feat_offsets, t->feat_cursor,
-                                  t->feat_lists)); }
+      int n = 0;
+      if (slice_bwd) n += launch_inverse_slice(t->stream, t->item_seg, t->fwd_work, t->bwd_slice, B, A, N, rps, 2);
+      n += launch_inverse_index(t->stream, gate, d.stm, d.nstm, d.nnz, B, A, N, 2, t->feat_counts, t->feat_offsets, t->feat_cursor,
+                                t->feat_lists);
+      p.done(n); }
     { PhaseScope p(t, PH_FT_BWD);
-      static const bool old_bwd = getenv("TATARA_DEBUG_OLD_BWD") != nullptr;
-      if (old_bwd)
-          p.done(launch_ft_backward(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->groups[0].grad));
-      else
-      p.done(launch_ft_backward_split(t->stream, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->bwd_plan,
-                                      t->bwd_partial, t->groups[0].grad)); }
+      int n = 0;
+      if (slice_bwd)
+          n += launch_ft_backward_slice(t->stream, t->dft[0], t->dft[1], t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2,
+                                        t->groups[0].grad);
+      n += launch_ft_backward_split(t->stream, gate, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->bwd_plan,
+                                    t->bwd_partial, t->groups[0].grad);
+      p.done(n); }
     return TB_OK;
 }
 
@@ -518,7 +528,7 @@ void free_all(tb_trainer* t) {
     cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
     cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials);
     cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
-    cudaFree(t->fwd_work); cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
+    cudaFree(t->fwd_work); cudaFree(t->bwd_slice); cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
     if (t->ev_t0) cudaEventDestroy(t->ev_t0);
     if (t->ev_t1) cudaEventDestroy(t->ev_t1);
     for (int i = 0; i < PH_COUNT; ++i) {
@@ -622,6 +632,11 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
     CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
     CU(t, dalloc(&t->fwd_work, ft_forward_slice_work_ints((int)(2 * B), 129, A)));
+    {
+        const int rps = c.piece_inputs > 0 ? c.piece_inputs : (int)N;
+        if (ft_forward_slice_supported((int)F, (int)N, (int)A, rps) && ft_backward_slice_supported((int)F, (int)N, (int)A, rps))
+            CU(t, dalloc(&t->bwd_slice, ft_backward_slice_ints((int)(2 * B), (int)A, rps)));
+    }
     {
         const size_t max_work = (size_t)ft_backward_max_work((int)B, (int)A, 2);
         CU(t, dalloc(&t->bwd_plan, 2 + 2 * max_work + 3 * (size_t)N));
@@ -1018,8 +1033,8 @@ int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, c
     CUX(cudaEventCreate(&e0)); CUX(cudaEventCreate(&e1));
     for (int i = -1; i < iters; ++i) {
         if (i == 0) { CUX(cudaDeviceSynchronize()); CUX(cudaEventRecord(e0, 0)); }
-        launch_inverse_index(0, d_i, d_i, d_n, batch, max_active, ft_in, 1, d_cnt, d_off, d_cur, d_lists);
-        launch_ft_backward_split(0, d_d, d_d, d_off, d_lists, batch, max_active, ft_in, ft_out, 1, d_plan, d_part, d_g);
+        launch_inverse_index(0, nullptr, d_i, d_i, d_n, batch, max_active, ft_in, 1, d_cnt, d_off, d_cur, d_lists);
+        launch_ft_backward_split(0, nullptr, d_d, d_d, d_off, d_lists, batch, max_active, ft_in, ft_out, 1, d_plan, d_part, d_g);
     }
     CUX(cudaEventRecord(e1, 0));
     CUX(cudaEventSynchronize(e1));

@@ -389,3 +389,47 @@ def test_staged_batch_equals_host_batch():
     assert a.flush_pending_loss() == b.flush_pending_loss()
     assert np.array_equal(a.download_group("ft_w")["w"], b.download_group("ft_w")["w"])
     assert a.launch_count == b.launch_count and a.launch_count > 0
+
+
+def _sequential_ft_grad(stm, nstm, nnz, dft_stm, dft_nstm, N, F):
+    """Per feature row the one-by-one fp32 sum of the dft rows that hold it: stm items by ascending position, then
+    nstm items (the order of sparse_ft_backward_cpu, crates/gpu-kernels/src/sparse_ft_backward.rs)."""
+    grad = np.zeros((N, F), np.float32)
+    for idx, dft in ((stm, dft_stm), (nstm, dft_nstm)):
+        B, A = idx.shape
+        live = (np.arange(A)[None, :] < nnz[:, None]) & (idx >= 0) & (idx < N)
+        pos, _slot = np.nonzero(live)             # row-major: ascending position, then slot
+        np.add.at(grad, idx[live], dft.reshape(B, F)[pos])   # unbuffered: adds one by one in this order
+    return grad
+
+
+@pytest.mark.parametrize("outside", [False, True])
+def test_ft_slice_backward_many_chunks_bit_exact(outside):
+    """King-sliced index lists with thousands of items in two slices: the slice-resident weight gradient walks several
+    chunks per slice and must reproduce the sequential sum bit for bit; with one row outside its item's slice the
+    generic kernels take over and must do the same."""
+    F, l1, l2, B, A = 256, 8, 16, 2048, 40
+    fs = LS_FS.with_factorize(False)
+    pi, N = fs.piece_inputs, fs.ft_in
+    rng = np.random.default_rng(11)
+    init = _perturb(tb.layerstack_default_init(fs, F, l1, l2, 9), rng, ["ft_b", "l1_b", "l1_shared_bias", "l2_b", "l3_b"])
+    init["ft_w"] *= 30.0
+    d = random_index_batch(rng, B, A, pi, 25, A)
+    hot = rng.integers(0, pi, 3)
+    for key, slices in (("stm", (3, 44)), ("nstm", (3, 17))):
+        k = np.asarray(slices)[rng.integers(0, 2, B)]
+        idx = d[key]
+        idx[:, 1] = np.where(rng.random(B) < 0.9, hot[0], idx[:, 1])     # a row that nearly every item holds
+        idx[:, 2] = np.where(rng.random(B) < 0.5, hot[1], idx[:, 2])
+        idx[::9, 5] = idx[::9, 4]                                        # the same feature twice in one item
+        d[key] = np.where(idx >= 0, idx + k[:, None] * pi, idx).astype(np.int32)
+    if outside:
+        d["stm"][100, 7] = 20 * pi + 5
+    batch = tb.BatchData(d["stm"], d["nstm"], d["nnz"], d["score"], d["wdl"], d["bucket"])
+    tr = tb.GpuTrainer(B, F, l1, l2, 9, fs, optimizer="adamw", init=init)
+    tr.forward_backward(batch, 0.25, tb.LossKind.sigmoid())
+    dft_stm, dft_nstm = tr.read_buffer("dft_stm", B * F), tr.read_buffer("dft_nstm", B * F)
+    assert np.abs(dft_stm).max() > 0
+    want = _sequential_ft_grad(d["stm"], d["nstm"], d["nnz"], dft_stm, dft_nstm, N, F)
+    got = tr.download_grad("ft_w").reshape(-1, F)[:N]
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
