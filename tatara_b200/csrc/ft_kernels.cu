@@ -520,16 +520,15 @@ __global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict_
                                                            int* __restrict__ lists, int* __restrict__ long_queue,
                                                            int* __restrict__ long_count, const int* __restrict__ run_if) {
     if (run_if && *run_if == 0) return;  // gated: another path does this step's work
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (warp >= n_persp * N) return;
+    for (int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; warp < n_persp * N; warp += (gridDim.x * blockDim.x) >> 5) {
     const int p = warp / N, f = warp - p * N;
     const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
     const int len = end - beg;
-    if (len < 2) return;
+    if (len < 2) continue;
     if (len > 64) {
         if (lane == 0) long_queue[atomicAdd(long_count, 1)] = warp;
-        return;
+        continue;
     }
     int* L = lists + (size_t)p * B * A + beg;
     const int v0 = lane < len ? L[lane] : 0x7fffffff;
@@ -543,6 +542,7 @@ __global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict_
     __syncwarp();
     if (lane < len) L[r0] = v0;
     if (lane + 32 < len) L[r1] = v1;
+    }
 }
 
 __global__ void __launch_bounds__(256) k_lists_sort_long(const int* __restrict__ offsets, int N, int B, int A,
@@ -641,7 +641,7 @@ int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, 
     k_feat_fill<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, cursor, lists, run_if);
     int* scratch = lists + (size_t)2 * B * A;  // the list buffer carries a second copy's worth of room
     const long long warps = (long long)n_persp * N;
-    k_lists_sort_short<<<(int)((warps * 32 + 255) / 256), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count, run_if);
+    k_lists_sort_short<<<(int)((warps * 32 + 255) / 256 < 148 * 32 ? (warps * 32 + 255) / 256 : 148 * 32), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count, run_if);
     int words = (B + 31) / 32;
     if ((size_t)words * 4 > 160 * 1024) words = 0;
     static bool attr_set = false;
@@ -742,12 +742,12 @@ __global__ void __launch_bounds__(512) k_ft_backward_short(const float* __restri
                                                              const int* __restrict__ offsets, const int* __restrict__ lists,
                                                              int B, int A, int N, int F, int n_persp, float* __restrict__ grad, const int* __restrict__ run_if) {
     if (run_if && *run_if == 0) return;  // gated: another path does this step's work
-    const int f = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int row4 = F >> 2;
+    for (int f = blockIdx.x; f < N; f += gridDim.x) {
     int len = offsets[f + 1] - offsets[f];
     if (n_persp > 1) len += offsets[(size_t)(N + 1) + f + 1] - offsets[(size_t)(N + 1) + f];
-    if (len > BWD_PART) return;  // summed in parts by k_ft_backward_long
+    if (len > BWD_PART) continue;  // summed in parts by k_ft_backward_long
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < n_persp; ++p) {
         const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
@@ -769,6 +769,7 @@ __global__ void __launch_bounds__(512) k_ft_backward_short(const float* __restri
         }
     }
     reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
+    }
 }
 
 __global__ void __launch_bounds__(512) k_ft_backward_long(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
@@ -830,7 +831,7 @@ int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft
     cudaMemsetAsync(counters, 0, 2 * sizeof(int), s);
     k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf, run_if);
     const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
-    k_ft_backward_short<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
+    k_ft_backward_short<<<dim3(N < 148 * 32 ? N : 148 * 32, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
     k_ft_backward_long<<<dim3(148 * 4, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial, run_if);
     k_ft_backward_long_final<<<dim3(148 * 2, ny), bx, 0, s>>>(counters, longf, partial, F, grad, run_if);
     return 4;

@@ -16,6 +16,7 @@
 #include "ft_slice.cuh"
 
 #define INV_SORT_N 2048  // rows per slice limit (bitonic sort size)
+#define BWD_HOT 256      // list length from which a list is summed by a warp of its own
 
 struct BwdLayout {
     int CH;             // slots per chunk (multiple of 32)
@@ -127,14 +128,12 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
     const unsigned short* cw = s_codes + (size_t)s0 * A_pad;
     unsigned short* my_hist = s_hist + (size_t)w * rps_h;
 
-    // pass 1: per-warp histogram
-    for (int e0 = 0; e0 < n_e; e0 += 32) {
-        const int e = e0 + lane;
-        const unsigned code = e < n_e ? cw[e] : 0xFFFFu;
-        const bool valid = code < (unsigned)rps;
-        const unsigned m = __match_any_sync(0xffffffffu, valid ? code : (0x10000u | lane));
-        if (valid && lane == __ffs(m) - 1) my_hist[code] = (unsigned short)(my_hist[code] + __popc(m));
-        __syncwarp();
+    // pass 1: per-warp histogram (two 16-bit cells per shared-memory word, bumped by 32-bit atomics; a cell never
+    // reaches 65536, so no carry crosses into its neighbour)
+    unsigned* my_hist32 = reinterpret_cast<unsigned*>(my_hist);
+    for (int e = lane; e < n_e; e += 32) {
+        const unsigned code = cw[e];
+        if (code < (unsigned)rps) atomicAdd(my_hist32 + (code >> 1), 1u << ((code & 1u) * 16u));
     }
     __syncthreads();
 
@@ -214,18 +213,18 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
         my_info[i] = v;
     }
 
-    // pass 2: stable ranked scatter of the chunk-local slot numbers
-    for (int e0 = 0; e0 < n_e; e0 += 32) {
-        const int e = e0 + lane;
-        const unsigned code = e < n_e ? cw[e] : 0xFFFFu;
-        const bool valid = code < (unsigned)rps;
-        const unsigned m = __match_any_sync(0xffffffffu, valid ? code : (0x10000u | lane));
-        int at = 0;
-        if (valid) at = s_rowoff[code] + my_hist[code] + __popc(m & ((1u << lane) - 1u));
-        __syncwarp();
-        if (valid) {
-            my_lists[at] = (unsigned short)(s0 + e / A_pad);
-            if (lane == __ffs(m) - 1) my_hist[code] = (unsigned short)(my_hist[code] + __popc(m));
+    // pass 2: ranked scatter of the chunk-local slot numbers.  A warp walks its slots one after the other, the lanes
+    // take the slot's cells; the atomic's return value is the cell's rank inside the row's list.  Slots are visited in
+    // ascending order, so every list comes out ascending (two cells of one slot carry the same value: their order is
+    // immaterial).
+    for (int sl = s0; sl < s1; ++sl) {
+        for (int q = lane; q < A_pad; q += 32) {
+            const unsigned code = s_codes[(size_t)sl * A_pad + q];
+            if (code < (unsigned)rps) {
+                const unsigned sh = (code & 1u) * 16u;
+                const unsigned old = atomicAdd(my_hist32 + (code >> 1), 1u << sh);
+                my_lists[s_rowoff[code] + ((old >> sh) & 0xffffu)] = (unsigned short)sl;
+            }
         }
         __syncwarp();
     }
@@ -241,13 +240,13 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                                                                 int rps_pad, int CH, int region, float* __restrict__ grad) {
     // dft strip [CH + 1][32] floats (the last row stays zero), row records [rps_pad] 64-bit, list cells [region] 16-bit
     extern __shared__ __align__(16) unsigned char s_raw[];
+    __shared__ int s_ctl[4];
     if (*outside_flag) return;
     const int k = blockIdx.x, strip = blockIdx.y;
     const int row0 = k * rps;
     const int rows = min(rps, N - row0);
     const int tid = threadIdx.x, lane = tid & 31;
     const int j = lane & 7;
-    const int group = tid >> 3;  // 128 eight-lane groups
     const int col = 32 * strip + 4 * j;
     const int c_first = first[k], c_end = first[k + 1];
     if (c_first == c_end) {  // no item reads this slice: its gradient rows are zero
@@ -282,14 +281,32 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
         __syncthreads();
 
         const bool first_chunk = c == c_first;
-        // the records are sorted by descending list length; group g takes records g, 255 - g, 256 + g, 511 - g, ...
-        // so that the groups' totals even out and the four groups of a warp run lists of similar length
-        for (int i0 = 0, turn = 0; i0 < rps; i0 += 128, turn ^= 1) {
-            const int i = i0 + (turn ? 127 - group : group);
-            if (i >= rps) continue;
+        // The records are sorted by descending list length.  A list of BWD_HOT entries or more gets a warp of its own
+        // (one eight-lane group works, the other three wait): a warp's share of the shared-memory pipe does not
+        // depend on how many of its lanes are active, so the long sequential sums run four times faster than they
+        // would next to three other lists and end with the rest of the chunk instead of after it.  All other records
+        // are handed out four at a time (neighbours in the order, so of similar length) from a block-wide counter.
+        if (tid == 0) {
+            int lo = 0, hi = rps;  // first record with fewer than BWD_HOT entries
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if ((int)(s_info[mid] & 0xffffu) >= BWD_HOT) lo = mid + 1; else hi = mid;
+            }
+            s_ctl[0] = lo;
+            s_ctl[1] = lo;
+            int lo2 = lo; hi = rps;  // first record without entries
+            while (lo2 < hi) {
+                const int mid = (lo2 + hi) >> 1;
+                if ((int)(s_info[mid] & 0xffffu) > 0) lo2 = mid + 1; else hi = mid;
+            }
+            s_ctl[2] = first_chunk ? rps : lo2;
+        }
+        __syncthreads();
+        const int n_hot = s_ctl[0], n_rec = s_ctl[2];
+        auto process = [&](int i) {
             const unsigned long long ri = s_info[i];
             const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
-            if (r >= rows || (cnt == 0 && !first_chunk)) continue;
+            if (r >= rows) return;
             float* gp = grad + (size_t)(row0 + r) * F + col;
             unsigned long long a0 = 0ull, a1 = 0ull;
             if (!first_chunk) {
@@ -333,6 +350,16 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                     if (u < rem) { a0 = fadd2(a0, v[u].x); a1 = fadd2(a1, v[u].y); }
             }
             __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(a0, a1));
+        };
+        const int warp = tid >> 5, g = lane >> 3;
+        for (int h = warp; h < n_hot; h += 32)
+            if (g == 0) process(h);
+        for (;;) {
+            int base = 0;
+            if (lane == 0) base = atomicAdd(&s_ctl[1], 4);
+            base = __shfl_sync(0xffffffffu, base, 0);
+            if (base >= n_rec) break;
+            if (base + g < n_rec) process(base + g);
         }
     }
 }
