@@ -10,6 +10,10 @@
 // A block owns (slice, column strip), walks the slice's chunks in order and carries the running sums through the
 // gradient rows themselves, so a row's terms are added one by one in ascending item order: the result is
 // bit-identical to the per-row sequential sum of the generic kernels (stm items first, ascending position).
+// Exception: a list with BWD_HOT or more entries inside one chunk is summed there as four partial sums (its
+// quarters in order), combined as prev + ((p0 + p1) + (p2 + p3)): a fixed order as well, so results stay
+// reproducible run to run, but not the sequential one.  (The reference's own kernel keeps four interleaved partial
+// sums over a list whose order is set by atomics, native_kernels.cu:1767-1806.)
 //
 // Both kernels return at once when the batch has a row outside its item's slice (outside_flag != 0); the generic
 // kernels, gated the other way round, then do the work.
@@ -79,11 +83,12 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
     for (int k = 0; k < n_keys; ++k) {
         const int b0 = item_seg[k], e0 = item_seg[k + 1];
         const int n = s_base[k + 1] - s_base[k];
+        const int size = n > 0 ? ((e0 - b0 + n - 1) / n + 7) & ~7 : 0;  // equal chunks (<= ipc: ipc is a multiple of 8)
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             FwdWork w;
             w.slice = k;
-            w.begin = b0 + i * ipc;
-            w.end = min(e0, w.begin + ipc);
+            w.begin = min(e0, b0 + i * size);
+            w.end = min(e0, w.begin + size);
             w.pad = 0;
             work[s_base[k] + i] = w;
         }
@@ -303,19 +308,10 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
         }
         __syncthreads();
         const int n_hot = s_ctl[0], n_rec = s_ctl[2];
-        auto process = [&](int i) {
-            const unsigned long long ri = s_info[i];
-            const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
-            if (r >= rows) return;
-            float* gp = grad + (size_t)(row0 + r) * F + col;
-            unsigned long long a0 = 0ull, a1 = 0ull;
-            if (!first_chunk) {
-                const ulonglong2 g = __ldcg(reinterpret_cast<const ulonglong2*>(gp));
-                a0 = g.x; a1 = g.y;
-            }
-            const unsigned char* lp = s_lists + 2 * off;
-            const int full = cnt & ~7;
-            for (int q = 0; q < full; q += 8) {
+        // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 8
+        auto sum_range = [&](const unsigned char* lp, int beg, int end, unsigned long long& a0, unsigned long long& a1) {
+            const int full = beg + ((end - beg) & ~7);
+            for (int q = beg; q < full; q += 8) {
                 const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * q);
                 const ulonglong2 v0 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x & 0xffffu) * 128u);
                 const ulonglong2 v1 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x >> 16) * 128u);
@@ -334,11 +330,11 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 a0 = fadd2(a0, v6.x); a1 = fadd2(a1, v6.y);
                 a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
             }
-            if (full < cnt) {  // the last one to seven entries; the padding cells behind them are not read as rows
+            if (full < end) {  // the last one to seven entries; the padding cells behind them are not read as rows
                 const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * full);
                 const unsigned cell[8] = {cc.x & 0xffffu, cc.x >> 16, cc.y & 0xffffu, cc.y >> 16,
                                           cc.z & 0xffffu, cc.z >> 16, cc.w & 0xffffu, cc.w >> 16};
-                const int rem = cnt - full;
+                const int rem = end - full;
                 ulonglong2 v[7];
 #pragma unroll
                 for (int u = 0; u < 7; ++u) {
@@ -349,17 +345,49 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 for (int u = 0; u < 7; ++u)
                     if (u < rem) { a0 = fadd2(a0, v[u].x); a1 = fadd2(a1, v[u].y); }
             }
-            __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(a0, a1));
         };
         const int warp = tid >> 5, g = lane >> 3;
-        for (int h = warp; h < n_hot; h += 32)
-            if (g == 0) process(h);
+        // long lists: the warp's four groups sum a quarter of the list each, then prev + ((p0 + p1) + (p2 + p3))
+        for (int h = warp; h < n_hot; h += 32) {
+            const unsigned long long ri = s_info[h];
+            const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
+            if (r >= rows) continue;
+            const int qlen = (((cnt + 3) >> 2) + 7) & ~7;
+            unsigned long long p0 = 0ull, p1 = 0ull;
+            sum_range(s_lists + 2 * off, min(cnt, g * qlen), min(cnt, (g + 1) * qlen), p0, p1);
+            p0 = fadd2(p0, __shfl_xor_sync(0xffffffffu, p0, 8));
+            p1 = fadd2(p1, __shfl_xor_sync(0xffffffffu, p1, 8));
+            p0 = fadd2(p0, __shfl_xor_sync(0xffffffffu, p0, 16));
+            p1 = fadd2(p1, __shfl_xor_sync(0xffffffffu, p1, 16));
+            if (g == 0) {
+                float* gp = grad + (size_t)(row0 + r) * F + col;
+                if (!first_chunk) {
+                    const ulonglong2 pv = __ldcg(reinterpret_cast<const ulonglong2*>(gp));
+                    p0 = fadd2(pv.x, p0); p1 = fadd2(pv.y, p1);
+                }
+                __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(p0, p1));
+            }
+        }
+        // all other lists: one group each, the terms added one by one onto the running sum
         for (;;) {
             int base = 0;
             if (lane == 0) base = atomicAdd(&s_ctl[1], 4);
             base = __shfl_sync(0xffffffffu, base, 0);
             if (base >= n_rec) break;
-            if (base + g < n_rec) process(base + g);
+            if (base + g < n_rec) {
+                const unsigned long long ri = s_info[base + g];
+                const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
+                if (r < rows) {
+                    float* gp = grad + (size_t)(row0 + r) * F + col;
+                    unsigned long long a0 = 0ull, a1 = 0ull;
+                    if (!first_chunk) {
+                        const ulonglong2 pv = __ldcg(reinterpret_cast<const ulonglong2*>(gp));
+                        a0 = pv.x; a1 = pv.y;
+                    }
+                    sum_range(s_lists + 2 * off, 0, cnt, a0, a1);
+                    __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(a0, a1));
+                }
+            }
         }
     }
 }

@@ -406,8 +406,8 @@ def _sequential_ft_grad(stm, nstm, nnz, dft_stm, dft_nstm, N, F):
 @pytest.mark.parametrize("outside", [False, True])
 def test_ft_slice_backward_many_chunks_bit_exact(outside):
     """King-sliced index lists with thousands of items in two slices: the slice-resident weight gradient walks several
-    chunks per slice and must reproduce the sequential sum bit for bit; with one row outside its item's slice the
-    generic kernels take over and must do the same."""
+    chunks per slice and must reproduce the sequential sum bit for bit (lists of 256 entries or more: to rounding);
+    with one row outside its item's slice the generic kernels take over and must do the same."""
     F, l1, l2, B, A = 256, 8, 16, 2048, 40
     fs = LS_FS.with_factorize(False)
     pi, N = fs.piece_inputs, fs.ft_in
@@ -432,4 +432,10 @@ def test_ft_slice_backward_many_chunks_bit_exact(outside):
     assert np.abs(dft_stm).max() > 0
     want = _sequential_ft_grad(d["stm"], d["nstm"], d["nnz"], dft_stm, dft_nstm, N, F)
     got = tr.download_grad("ft_w").reshape(-1, F)[:N]
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # lists of 256 entries or more may be summed as four partial sums per chunk (fixed order, not the sequential one)
+    live = lambda idx: idx[(np.arange(A)[None, :] < d["nnz"][:, None]) & (idx >= 0) & (idx < N)]
+    count = np.bincount(np.concatenate([live(d["stm"]), live(d["nstm"])]), minlength=N)
+    short = count < 256
+    assert short.sum() > 1000 and (~short).sum() >= 4
+    assert np.array_equal(got[short].view(np.uint32), want[short].view(np.uint32))
+    assert_close_scaled(got[~short], want[~short], 1e-6, "long lists")
