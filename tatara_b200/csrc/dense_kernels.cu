@@ -1118,15 +1118,147 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
     if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
 }
 
-__global__ void k_bias_partials_reduce(const float* __restrict__ partials, int n_rows, int F, float* __restrict__ out) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+// Register-resident variant for l1 <= 16: a thread keeps the effective weights of its four columns ([L1] float4) in
+// registers for as long as the bucket does not change, reads a position's dl1 row with L1 / 4 broadcast loads from
+// shared memory and does 4 * L1 multiply-adds on them, so the shared-memory pipe is no longer the limit and the
+// kernel runs at the speed of its global loads and stores.  Four positions are in flight per thread.
+template <int MODE, int L1>
+__global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_reg(const float* __restrict__ dl1, const int* __restrict__ order,
+                                                              const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
+                                                              const float* __restrict__ wb, const float* __restrict__ ws,
+                                                              const float* __restrict__ pre_stm, const float* __restrict__ pre_nstm,
+                                                              const float* __restrict__ ft_bias, float scale, int F, int nb, int CW,
+                                                              float* __restrict__ dft_stm, float* __restrict__ dft_nstm,
+                                                              float* __restrict__ bias_partials) {
+    __shared__ __align__(16) float sdl[TB_TILE_M][L1];
+    __shared__ int s_pos[TB_TILE_M];
+    const int persp = blockIdx.y;
+    const int chunk = blockIdx.z;
+    const int half = F >> 1;
+    const int Kin = MODE == 1 ? F : 2 * F;                        // row length of the L1 input
+    const int cbase = (MODE == 1 ? persp * half : persp * F) + chunk * CW;  // first L1 input column of this block
+    const int wcol = chunk * CW + 4 * threadIdx.x;                // column inside the perspective
+    const float* __restrict__ pre = persp ? pre_nstm : pre_stm;
+    float* __restrict__ dft = persp ? dft_nstm : dft_stm;
+    const int nt = *n_tiles;
+    int cur_bucket = -1;
+    float4 w[L1];
+    float4 bacc0 = make_float4(0.f, 0.f, 0.f, 0.f), bacc1 = bacc0;
+    float4 bias0 = make_float4(0.f, 0.f, 0.f, 0.f), bias1 = bias0;
+    if (MODE == 1) {
+        bias0 = *reinterpret_cast<const float4*>(ft_bias + wcol);
+        bias1 = *reinterpret_cast<const float4*>(ft_bias + half + wcol);
+    }
+    for (int t = blockIdx.x; t < nt; t += gridDim.x) {
+        const TileDesc td = tiles[t];
+        if (td.bucket != cur_bucket) {
+            cur_bucket = td.bucket;
+            const bool use_b = wb != nullptr && td.bucket < nb;
+            const int c0 = cbase + 4 * threadIdx.x;
+#pragma unroll
+            for (int o = 0; o < L1; ++o) {
+                float4 v = make_float4(ws[(size_t)(c0 + 0) * L1 + o], ws[(size_t)(c0 + 1) * L1 + o], ws[(size_t)(c0 + 2) * L1 + o],
+                                       ws[(size_t)(c0 + 3) * L1 + o]);
+                if (use_b) {
+                    const float4 u = *reinterpret_cast<const float4*>(wb + ((size_t)td.bucket * L1 + o) * Kin + c0);
+                    v.x = u.x + v.x; v.y = u.y + v.y; v.z = u.z + v.z; v.w = u.w + v.w;
+                }
+                w[o] = v;
+            }
+        }
+        __syncthreads();  // the previous tile's dl1 rows are consumed
+        for (int i = threadIdx.x; i < TB_TILE_M; i += blockDim.x) s_pos[i] = i < td.count ? order[td.start + i] : -1;
+        __syncthreads();
+        for (int e = threadIdx.x; e < TB_TILE_M * L1; e += blockDim.x) {
+            const int r = e / L1, o = e - r * L1;
+            const int p = s_pos[r];
+            sdl[r][o] = p >= 0 ? dl1[(size_t)p * L1 + o] : 0.f;
+        }
+        __syncthreads();
+        for (int r0 = 0; r0 < td.count; r0 += 4) {
+            float4 xa[4], xb[4];
+            int pp[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
+                const int pl = pp[q] < 0 ? s_pos[r0] : pp[q];  // unconditional loads: all of them are in flight together
+                xa[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pl * F + wcol));
+                if (MODE == 1) xb[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pl * F + half + wcol));
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4* gr = reinterpret_cast<const float4*>(&sdl[r0 + q < TB_TILE_M ? r0 + q : r0][0]);
+#pragma unroll
+                for (int o4 = 0; o4 < L1 / 4; ++o4) {
+                    const float4 g = gr[o4];
+                    const float gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float4 ww = w[4 * o4 + u];
+                        d.x += gv[u] * ww.x; d.y += gv[u] * ww.y; d.z += gv[u] * ww.z; d.w += gv[u] * ww.w;
+                    }
+                }
+                if (pp[q] < 0) continue;
+                if (MODE == 1) {
+                    const float4 a = make_float4(xa[q].x + bias0.x, xa[q].y + bias0.y, xa[q].z + bias0.z, xa[q].w + bias0.w);
+                    const float4 b = make_float4(xb[q].x + bias1.x, xb[q].y + bias1.y, xb[q].z + bias1.z, xb[q].w + bias1.w);
+                    float4 ga, gb;
+                    ga.x = (a.x > 0.f && a.x < 1.f) ? d.x * crelu01(b.x) * scale : 0.f;
+                    ga.y = (a.y > 0.f && a.y < 1.f) ? d.y * crelu01(b.y) * scale : 0.f;
+                    ga.z = (a.z > 0.f && a.z < 1.f) ? d.z * crelu01(b.z) * scale : 0.f;
+                    ga.w = (a.w > 0.f && a.w < 1.f) ? d.w * crelu01(b.w) * scale : 0.f;
+                    gb.x = (b.x > 0.f && b.x < 1.f) ? d.x * crelu01(a.x) * scale : 0.f;
+                    gb.y = (b.y > 0.f && b.y < 1.f) ? d.y * crelu01(a.y) * scale : 0.f;
+                    gb.z = (b.z > 0.f && b.z < 1.f) ? d.z * crelu01(a.z) * scale : 0.f;
+                    gb.w = (b.w > 0.f && b.w < 1.f) ? d.w * crelu01(a.w) * scale : 0.f;
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = ga;   // read again by the FT backward: keep in L2
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + half + wcol) = gb;
+                    bacc0.x += ga.x; bacc0.y += ga.y; bacc0.z += ga.z; bacc0.w += ga.w;
+                    bacc1.x += gb.x; bacc1.y += gb.y; bacc1.z += gb.z; bacc1.w += gb.w;
+                } else {
+                    const float4 x = xa[q];
+                    float4 g;
+                    if (MODE == 2) {
+                        g.x = (x.x > 0.f && x.x < 1.f) ? d.x : 0.f;
+                        g.y = (x.y > 0.f && x.y < 1.f) ? d.y : 0.f;
+                        g.z = (x.z > 0.f && x.z < 1.f) ? d.z : 0.f;
+                        g.w = (x.w > 0.f && x.w < 1.f) ? d.w : 0.f;
+                    } else {
+                        const float4 a = make_float4(crelu01(x.x), crelu01(x.y), crelu01(x.z), crelu01(x.w));
+                        g.x = d.x * ((a.x > 0.f && a.x < 1.f) ? 2.0f * a.x : 0.f);
+                        g.y = d.y * ((a.y > 0.f && a.y < 1.f) ? 2.0f * a.y : 0.f);
+                        g.z = d.z * ((a.z > 0.f && a.z < 1.f) ? 2.0f * a.z : 0.f);
+                        g.w = d.w * ((a.w > 0.f && a.w < 1.f) ? 2.0f * a.w : 0.f);
+                    }
+                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = g;
+                    bacc0.x += g.x; bacc0.y += g.y; bacc0.z += g.z; bacc0.w += g.w;
+                }
+            }
+        }
+    }
+    // one partial row per (block, perspective): [n_ctas][2][F]
+    float* bp = bias_partials + ((size_t)blockIdx.x * 2 + persp) * F;
+    *reinterpret_cast<float4*>(bp + wcol) = bacc0;
+    if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
+}
+
+// out[c] = sum over the perspectives (stm first) and the blocks' partial rows; 32 lanes share a column's rows and
+// their partial sums are combined in lane order, a fixed order
+__global__ void __launch_bounds__(256) k_bias_partials_reduce(const float* __restrict__ partials, int n_rows, int F,
+                                                              float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // a warp per column
     if (c >= F) return;
-    // stm partials of every block first, then nstm: the accumulation order of the two
-    // ft_post_perspective_grad calls
     float sum = 0.f;
-    for (int p = 0; p < 2; ++p)
-        for (int r = 0; r < n_rows; ++r) sum += partials[((size_t)r * 2 + p) * F + c];
-    out[c] = sum;
+    const int total = 2 * n_rows;  // index i = p * n_rows + r
+    for (int i = lane; i < total; i += 32) {
+        const int p = i / n_rows, r = i - p * n_rows;
+        sum += partials[((size_t)r * 2 + p) * F + c];
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, d);
+    if (lane == 0) out[c] = sum;
 }
 
 int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int* order, const TileDesc* tiles,
@@ -1137,22 +1269,34 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
     (void)B;
     (void)max_tiles;
     const int work_cols = mode == 1 ? F / 2 : F;
-    int n_chunks = 1;
-    while ((size_t)(work_cols / n_chunks) * l1 * 4 > 64 * 1024 || work_cols / n_chunks > 1024) n_chunks *= 2;
-    const int CW = work_cols / n_chunks;
-    const size_t smem = (size_t)CW * l1 * sizeof(float);
-    dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
-    static const bool pf = getenv("TATARA_DEBUG_DGRAD_PF") != nullptr;
-#define DGRAD_LAUNCH(M, P)                                                                                               \
+    if (l1 == 8 || l1 == 16) {
+        int n_chunks = 1;
+        while (work_cols / n_chunks > 1024 || (work_cols / n_chunks) % 128 != 0 && (work_cols / n_chunks) > 256) n_chunks *= 2;
+        const int CW = work_cols / n_chunks;
+        dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
+#define DGRAD_REG(M, L)                                                                                              \
+        k_l1_dgrad_ftgrad_reg<M, L><<<grid, block, 0, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, \
+                                                           nb, CW, dft_stm, dft_nstm, bias_partials)
+        if (l1 == 16) { if (mode == 1) DGRAD_REG(1, 16); else if (mode == 2) DGRAD_REG(2, 16); else DGRAD_REG(3, 16); }
+        else { if (mode == 1) DGRAD_REG(1, 8); else if (mode == 2) DGRAD_REG(2, 8); else DGRAD_REG(3, 8); }
+#undef DGRAD_REG
+    } else {
+        int n_chunks = 1;
+        while ((size_t)(work_cols / n_chunks) * l1 * 4 > 64 * 1024 || work_cols / n_chunks > 1024) n_chunks *= 2;
+        const int CW = work_cols / n_chunks;
+        const size_t smem = (size_t)CW * l1 * sizeof(float);
+        dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
+#define DGRAD_LAUNCH(M)                                                                                                  \
     do {                                                                                                                 \
-        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<M, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);           \
-        k_l1_dgrad_ftgrad<M, P><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, \
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);       \
+        k_l1_dgrad_ftgrad<M, false><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, \
                                                          scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);        \
     } while (0)
-    if (mode == 1) { if (pf) DGRAD_LAUNCH(1, true); else DGRAD_LAUNCH(1, false); }
-    else if (mode == 2) { if (pf) DGRAD_LAUNCH(2, true); else DGRAD_LAUNCH(2, false); }
-    else { if (pf) DGRAD_LAUNCH(3, true); else DGRAD_LAUNCH(3, false); }
+        if (mode == 1) DGRAD_LAUNCH(1);
+        else if (mode == 2) DGRAD_LAUNCH(2);
+        else DGRAD_LAUNCH(3);
 #undef DGRAD_LAUNCH
-    k_bias_partials_reduce<<<ceil_div(F, 256), 256, 0, s>>>(bias_partials, n_ctas, F, ft_b_grad);
+    }
+    k_bias_partials_reduce<<<ceil_div(F, 8), 256, 0, s>>>(bias_partials, n_ctas, F, ft_b_grad);
     return 2;
 }

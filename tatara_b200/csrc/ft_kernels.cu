@@ -143,21 +143,21 @@ int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* i
 // forward, slice-resident variant.  The generic kernel above gathers every row from L2; with the items sorted
 // by king-bucket slice all of an item's rows lie in one slice of rows_per_slice rows, and a 32-column strip
 // of that slice (rows_per_slice * 128 bytes, 208 KB for 1629 rows) fits in shared memory.  A block owns
-// (run of <= 1024 items of one slice, column strip), loads the strip once and serves all of its items'
+// (run of <= SLICE_IPC items of one slice, column strip), loads the strip once and serves all of its items'
 // row reads from shared memory; eight lanes work on one item, a lane on four adjacent columns (128-bit
 // shared loads), rows are added in slot order as in the generic kernel, so the sums are bit-identical.
 // A row outside the block's slice (arbitrary index lists) is read from the table in global memory instead.
 // LayerStack strips hold columns [16s, 16s+16) and their pair partners [F/2 + 16s, F/2 + 16s + 16); the other
 // modes 32 adjacent columns.
 // ------------------------------------------------------------------------------------------------
-__global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork* __restrict__ work, int* __restrict__ n_work) {
+__global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, int ipc, FwdWork* __restrict__ work, int* __restrict__ n_work) {
     // n_keys = slices + 1 (the last key collects items without a usable first index)
     __shared__ int s_base[SORT_KEYS_MAX + 1];
     if (threadIdx.x == 0) {
         int run = 0;
         for (int k = 0; k < n_keys; ++k) {
             s_base[k] = run;
-            run += (item_seg[k + 1] - item_seg[k] + SLICE_IPC - 1) / SLICE_IPC;
+            run += (item_seg[k + 1] - item_seg[k] + ipc - 1) / ipc;
         }
         s_base[n_keys] = run;
         n_work[0] = run;
@@ -167,11 +167,13 @@ __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, FwdWork
     for (int k = 0; k < n_keys; ++k) {
         const int b0 = item_seg[k], e0 = item_seg[k + 1];
         const int n = s_base[k + 1] - s_base[k];
+        // equal runs, a multiple of the 128 items a block handles per round (<= ipc, itself such a multiple)
+        const int size = n > 0 ? ((e0 - b0 + n - 1) / n + 127) & ~127 : 0;
         for (int i = threadIdx.x; i < n; i += blockDim.x) {
             FwdWork w;
             w.slice = k;
-            w.begin = b0 + i * SLICE_IPC;
-            w.end = min(e0, w.begin + SLICE_IPC);
+            w.begin = min(e0, b0 + i * size);
+            w.end = min(e0, w.begin + size);
             w.pad = 0;
             work[s_base[k] + i] = w;
         }
@@ -391,7 +393,7 @@ int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const 
     int* n_work = sb.n_work;
     int* info = sb.info;
     uint4* codes = sb.codes;
-    k_fwd_plan<<<1, 128, 0, s>>>(item_seg, n_keys, wk, n_work);
+    k_fwd_plan<<<1, 128, 0, s>>>(item_seg, n_keys, SLICE_IPC, wk, n_work);
     k_fwd_codes<<<ceil_div(n_items, 256), 256, 0, s>>>(idx_stm, idx_nstm, nnz, items, item_seg, n_keys, n_items, B, N, A, A_pad,
                                                        rps, codes, info, sb.outside_flag);
     const size_t smem = slice_smem_bytes(rps, A);
@@ -641,7 +643,7 @@ int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, 
     k_feat_fill<<<blocks, 256, 0, s>>>(idx_stm, idx_nstm, nnz, B, A, N, n_persp, cursor, lists, run_if);
     int* scratch = lists + (size_t)2 * B * A;  // the list buffer carries a second copy's worth of room
     const long long warps = (long long)n_persp * N;
-    k_lists_sort_short<<<(int)((warps * 32 + 255) / 256 < 148 * 32 ? (warps * 32 + 255) / 256 : 148 * 32), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count, run_if);
+    k_lists_sort_short<<<(int)(run_if && (warps * 32 + 255) / 256 > 148 * 32 ? 148 * 32 : (warps * 32 + 255) / 256), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count, run_if);
     int words = (B + 31) / 32;
     if ((size_t)words * 4 > 160 * 1024) words = 0;
     static bool attr_set = false;
@@ -690,6 +692,7 @@ __global__ void __launch_bounds__(512) k_ft_backward(const float* __restrict__ d
 int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
                        const int* lists, int B, int A, int N, int F, int n_persp, float* grad) {
     const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
+    // a gated launch (run_if) normally returns at once: a small grid of row-striding blocks keeps that cheap
     k_ft_backward<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
     return 1;
 }
@@ -831,7 +834,8 @@ int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft
     cudaMemsetAsync(counters, 0, 2 * sizeof(int), s);
     k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf, run_if);
     const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
-    k_ft_backward_short<<<dim3(N < 148 * 32 ? N : 148 * 32, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
+    // a gated launch (run_if) normally returns at once: a small grid of row-striding blocks keeps that cheap
+    k_ft_backward_short<<<dim3(run_if && N > 148 * 32 ? 148 * 32 : N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
     k_ft_backward_long<<<dim3(148 * 4, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial, run_if);
     k_ft_backward_long_final<<<dim3(148 * 2, ny), bx, 0, s>>>(counters, longf, partial, F, grad, run_if);
     return 4;

@@ -2,7 +2,7 @@
 #pragma once
 #include "common.cuh"
 
-#define SLICE_IPC 1024           // items per block of the forward
+#define SLICE_IPC 2048           // items per block of the forward (a multiple of 128)
 #define SORT_KEYS_LIMIT 128      // key limit of the small-key sorts (sort_kernels.cu): slices + 1
 #define SLICE_OUTSIDE 0xFFFFu    // row code: the feature's table row lies outside the item's slice
 #define SLICE_SLOW_BIT 0x40000000  // info[slot] bit: the item has such a row
