@@ -1118,20 +1118,29 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
     if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
 }
 
-// Register-resident variant for l1 <= 16: a thread keeps the effective weights of its four columns ([L1] float4) in
-// registers for as long as the bucket does not change, reads a position's dl1 row with L1 / 4 broadcast loads from
-// shared memory and does 4 * L1 multiply-adds on them, so the shared-memory pipe is no longer the limit and the
-// kernel runs at the speed of its global loads and stores.  Four positions are in flight per thread.
+// Streaming variant for l1 = 8 or 16.  A thread keeps the effective weights of its four columns ([L1] float4) in
+// registers, so a position costs L1 / 4 broadcast loads of its dl1 row from shared memory and 4 * L1 multiply-adds:
+// the shared-memory pipe is not the limit.  A block owns half a work unit (<= DG_POS consecutive positions of the
+// bucket order, one bucket) and one perspective; the pre-activations arrive through a private ring of asynchronous
+// copies (every thread copies exactly the 16-byte pieces it reads itself, so no barrier is needed), DG_STAGES rounds
+// of four positions ahead of the arithmetic, which keeps the global loads in flight back to back.
+#define DG_POS 128     // positions per block
+#define DG_STAGES 3
+static __device__ __forceinline__ void dg_cp16(void* dst_shared, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
 template <int MODE, int L1>
-__global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_reg(const float* __restrict__ dl1, const int* __restrict__ order,
-                                                              const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
-                                                              const float* __restrict__ wb, const float* __restrict__ ws,
-                                                              const float* __restrict__ pre_stm, const float* __restrict__ pre_nstm,
-                                                              const float* __restrict__ ft_bias, float scale, int F, int nb, int CW,
-                                                              float* __restrict__ dft_stm, float* __restrict__ dft_nstm,
-                                                              float* __restrict__ bias_partials) {
-    __shared__ __align__(16) float sdl[TB_TILE_M][L1];
-    __shared__ int s_pos[TB_TILE_M];
+__global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __restrict__ dl1, const int* __restrict__ order,
+                                                                 const TileDesc* __restrict__ tiles, const TileDesc* __restrict__ units,
+                                                                 const int* __restrict__ n_units, const float* __restrict__ wb,
+                                                                 const float* __restrict__ ws, const float* __restrict__ pre_stm,
+                                                                 const float* __restrict__ pre_nstm, const float* __restrict__ ft_bias,
+                                                                 float scale, int F, int nb, int CW, float* __restrict__ dft_stm,
+                                                                 float* __restrict__ dft_nstm, float* __restrict__ bias_partials) {
+    constexpr int NP = MODE == 1 ? 2 : 1;  // 16-byte pieces per position and thread
+    extern __shared__ __align__(16) unsigned char s_dyn[];  // ring [DG_STAGES][4 positions][NP][threads] float4
+    __shared__ __align__(16) float sdl[DG_POS][L1];
+    __shared__ int s_pos[DG_POS];
     const int persp = blockIdx.y;
     const int chunk = blockIdx.z;
     const int half = F >> 1;
@@ -1140,105 +1149,145 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_reg(const float* __rest
     const int wcol = chunk * CW + 4 * threadIdx.x;                // column inside the perspective
     const float* __restrict__ pre = persp ? pre_nstm : pre_stm;
     float* __restrict__ dft = persp ? dft_nstm : dft_stm;
-    const int nt = *n_tiles;
-    int cur_bucket = -1;
-    float4 w[L1];
     float4 bacc0 = make_float4(0.f, 0.f, 0.f, 0.f), bacc1 = bacc0;
+    float* bp = bias_partials + ((size_t)blockIdx.x * 2 + persp) * F;  // one partial row per (block, perspective)
+
+    // the block's positions: tiles [first, last) of unit blockIdx.x / 2, contiguous in the bucket order
+    const int u = blockIdx.x >> 1, h = blockIdx.x & 1;
+    int p_begin = 0, n = 0, bucket = 0;
+    if (u < *n_units) {
+        const TileDesc ud = units[u];
+        const int per = DG_POS / TB_TILE_M;
+        const int first = ud.start + h * per, last = min(ud.start + ud.count, first + per);
+        if (first < last) {
+            p_begin = tiles[first].start;
+            n = tiles[last - 1].start + tiles[last - 1].count - p_begin;
+            bucket = ud.bucket;
+        }
+    }
+    if (n == 0) {  // the bias reduction reads every row
+        *reinterpret_cast<float4*>(bp + wcol) = bacc0;
+        if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
+        return;
+    }
+    for (int i = threadIdx.x; i < DG_POS; i += blockDim.x) s_pos[i] = i < n ? order[p_begin + i] : -1;
+    // effective weights of the thread's four columns
+    float4 w[L1];
+    {
+        const bool use_b = wb != nullptr && bucket < nb;
+        const int c0 = cbase + 4 * threadIdx.x;
+#pragma unroll
+        for (int o4 = 0; o4 < L1 / 4; ++o4) {
+            const float4 r0 = *reinterpret_cast<const float4*>(ws + (size_t)(c0 + 0) * L1 + 4 * o4);
+            const float4 r1 = *reinterpret_cast<const float4*>(ws + (size_t)(c0 + 1) * L1 + 4 * o4);
+            const float4 r2 = *reinterpret_cast<const float4*>(ws + (size_t)(c0 + 2) * L1 + 4 * o4);
+            const float4 r3 = *reinterpret_cast<const float4*>(ws + (size_t)(c0 + 3) * L1 + 4 * o4);
+            w[4 * o4 + 0] = make_float4(r0.x, r1.x, r2.x, r3.x);
+            w[4 * o4 + 1] = make_float4(r0.y, r1.y, r2.y, r3.y);
+            w[4 * o4 + 2] = make_float4(r0.z, r1.z, r2.z, r3.z);
+            w[4 * o4 + 3] = make_float4(r0.w, r1.w, r2.w, r3.w);
+        }
+        if (use_b) {
+#pragma unroll
+            for (int o = 0; o < L1; ++o) {
+                const float4 v = *reinterpret_cast<const float4*>(wb + ((size_t)bucket * L1 + o) * Kin + c0);
+                w[o].x = v.x + w[o].x; w[o].y = v.y + w[o].y; w[o].z = v.z + w[o].z; w[o].w = v.w + w[o].w;
+            }
+        }
+    }
     float4 bias0 = make_float4(0.f, 0.f, 0.f, 0.f), bias1 = bias0;
     if (MODE == 1) {
         bias0 = *reinterpret_cast<const float4*>(ft_bias + wcol);
         bias1 = *reinterpret_cast<const float4*>(ft_bias + half + wcol);
     }
-    for (int t = blockIdx.x; t < nt; t += gridDim.x) {
-        const TileDesc td = tiles[t];
-        if (td.bucket != cur_bucket) {
-            cur_bucket = td.bucket;
-            const bool use_b = wb != nullptr && td.bucket < nb;
-            const int c0 = cbase + 4 * threadIdx.x;
-#pragma unroll
-            for (int o = 0; o < L1; ++o) {
-                float4 v = make_float4(ws[(size_t)(c0 + 0) * L1 + o], ws[(size_t)(c0 + 1) * L1 + o], ws[(size_t)(c0 + 2) * L1 + o],
-                                       ws[(size_t)(c0 + 3) * L1 + o]);
-                if (use_b) {
-                    const float4 u = *reinterpret_cast<const float4*>(wb + ((size_t)td.bucket * L1 + o) * Kin + c0);
-                    v.x = u.x + v.x; v.y = u.y + v.y; v.z = u.z + v.z; v.w = u.w + v.w;
-                }
-                w[o] = v;
-            }
-        }
-        __syncthreads();  // the previous tile's dl1 rows are consumed
-        for (int i = threadIdx.x; i < TB_TILE_M; i += blockDim.x) s_pos[i] = i < td.count ? order[td.start + i] : -1;
-        __syncthreads();
-        for (int e = threadIdx.x; e < TB_TILE_M * L1; e += blockDim.x) {
-            const int r = e / L1, o = e - r * L1;
-            const int p = s_pos[r];
-            sdl[r][o] = p >= 0 ? dl1[(size_t)p * L1 + o] : 0.f;
-        }
-        __syncthreads();
-        for (int r0 = 0; r0 < td.count; r0 += 4) {
-            float4 xa[4], xb[4];
-            int pp[4];
+    __syncthreads();
+    for (int e = threadIdx.x; e < DG_POS * L1 / 4; e += blockDim.x) {
+        const int r = e / (L1 / 4), o4 = e - r * (L1 / 4);
+        const int p = s_pos[r];
+        reinterpret_cast<float4*>(&sdl[r][0])[o4] = p >= 0 ? *reinterpret_cast<const float4*>(dl1 + (size_t)p * L1 + 4 * o4)
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // ring slot of (stage, position q, piece k) of this thread
+    float4* ring = reinterpret_cast<float4*>(s_dyn);
+    const int T = blockDim.x;
+    auto slot = [&](int stage, int q, int k) { return ring + ((size_t)(stage * 4 + q) * NP + k) * T + threadIdx.x; };
+    auto issue = [&](int round) {  // copies of positions 4 * round .. + 3 (a missing position repeats the block's first)
+        if (4 * round < n) {
+            const int stage = round % DG_STAGES;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
-                const int pl = pp[q] < 0 ? s_pos[r0] : pp[q];  // unconditional loads: all of them are in flight together
-                xa[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pl * F + wcol));
-                if (MODE == 1) xb[q] = __ldcs(reinterpret_cast<const float4*>(pre + (size_t)pl * F + half + wcol));
+                const int r = 4 * round + q;
+                const int pl = s_pos[r < n ? r : 0];
+                dg_cp16(slot(stage, q, 0), pre + (size_t)pl * F + wcol);
+                if (MODE == 1) dg_cp16(slot(stage, q, 1), pre + (size_t)pl * F + half + wcol);
             }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per round, empty past the end
+    };
+    const int n_rounds = (n + 3) >> 2;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float4* gr = reinterpret_cast<const float4*>(&sdl[r0 + q < TB_TILE_M ? r0 + q : r0][0]);
+    for (int r = 0; r < DG_STAGES - 1; ++r) issue(r);
+    __syncthreads();  // dl1 rows staged
+    for (int round = 0; round < n_rounds; ++round) {
+        issue(round + DG_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(DG_STAGES - 1) : "memory");  // this round's copies have landed
+        const int stage = round % DG_STAGES;
 #pragma unroll
-                for (int o4 = 0; o4 < L1 / 4; ++o4) {
-                    const float4 g = gr[o4];
-                    const float gv[4] = {g.x, g.y, g.z, g.w};
+        for (int q = 0; q < 4; ++q) {
+            const int r = 4 * round + q;
+            if (r >= n) break;
+            const int pp = s_pos[r];
+            float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4* gr = reinterpret_cast<const float4*>(&sdl[r][0]);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float4 ww = w[4 * o4 + u];
-                        d.x += gv[u] * ww.x; d.y += gv[u] * ww.y; d.z += gv[u] * ww.z; d.w += gv[u] * ww.w;
-                    }
+            for (int o4 = 0; o4 < L1 / 4; ++o4) {
+                const float4 g = gr[o4];
+                const float gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                for (int uu = 0; uu < 4; ++uu) {
+                    const float4 ww = w[4 * o4 + uu];
+                    d.x += gv[uu] * ww.x; d.y += gv[uu] * ww.y; d.z += gv[uu] * ww.z; d.w += gv[uu] * ww.w;
                 }
-                if (pp[q] < 0) continue;
-                if (MODE == 1) {
-                    const float4 a = make_float4(xa[q].x + bias0.x, xa[q].y + bias0.y, xa[q].z + bias0.z, xa[q].w + bias0.w);
-                    const float4 b = make_float4(xb[q].x + bias1.x, xb[q].y + bias1.y, xb[q].z + bias1.z, xb[q].w + bias1.w);
-                    float4 ga, gb;
-                    ga.x = (a.x > 0.f && a.x < 1.f) ? d.x * crelu01(b.x) * scale : 0.f;
-                    ga.y = (a.y > 0.f && a.y < 1.f) ? d.y * crelu01(b.y) * scale : 0.f;
-                    ga.z = (a.z > 0.f && a.z < 1.f) ? d.z * crelu01(b.z) * scale : 0.f;
-                    ga.w = (a.w > 0.f && a.w < 1.f) ? d.w * crelu01(b.w) * scale : 0.f;
-                    gb.x = (b.x > 0.f && b.x < 1.f) ? d.x * crelu01(a.x) * scale : 0.f;
-                    gb.y = (b.y > 0.f && b.y < 1.f) ? d.y * crelu01(a.y) * scale : 0.f;
-                    gb.z = (b.z > 0.f && b.z < 1.f) ? d.z * crelu01(a.z) * scale : 0.f;
-                    gb.w = (b.w > 0.f && b.w < 1.f) ? d.w * crelu01(a.w) * scale : 0.f;
-                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = ga;   // read again by the FT backward: keep in L2
-                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + half + wcol) = gb;
-                    bacc0.x += ga.x; bacc0.y += ga.y; bacc0.z += ga.z; bacc0.w += ga.w;
-                    bacc1.x += gb.x; bacc1.y += gb.y; bacc1.z += gb.z; bacc1.w += gb.w;
+            }
+            const float4 xa = *slot(stage, q, 0);
+            if (MODE == 1) {
+                const float4 xb = *slot(stage, q, 1);
+                const float4 a = make_float4(xa.x + bias0.x, xa.y + bias0.y, xa.z + bias0.z, xa.w + bias0.w);
+                const float4 b = make_float4(xb.x + bias1.x, xb.y + bias1.y, xb.z + bias1.z, xb.w + bias1.w);
+                float4 ga, gb;
+                ga.x = (a.x > 0.f && a.x < 1.f) ? d.x * crelu01(b.x) * scale : 0.f;
+                ga.y = (a.y > 0.f && a.y < 1.f) ? d.y * crelu01(b.y) * scale : 0.f;
+                ga.z = (a.z > 0.f && a.z < 1.f) ? d.z * crelu01(b.z) * scale : 0.f;
+                ga.w = (a.w > 0.f && a.w < 1.f) ? d.w * crelu01(b.w) * scale : 0.f;
+                gb.x = (b.x > 0.f && b.x < 1.f) ? d.x * crelu01(a.x) * scale : 0.f;
+                gb.y = (b.y > 0.f && b.y < 1.f) ? d.y * crelu01(a.y) * scale : 0.f;
+                gb.z = (b.z > 0.f && b.z < 1.f) ? d.z * crelu01(a.z) * scale : 0.f;
+                gb.w = (b.w > 0.f && b.w < 1.f) ? d.w * crelu01(a.w) * scale : 0.f;
+                *reinterpret_cast<float4*>(dft + (size_t)pp * F + wcol) = ga;   // read again by the FT backward: keep in L2
+                *reinterpret_cast<float4*>(dft + (size_t)pp * F + half + wcol) = gb;
+                bacc0.x += ga.x; bacc0.y += ga.y; bacc0.z += ga.z; bacc0.w += ga.w;
+                bacc1.x += gb.x; bacc1.y += gb.y; bacc1.z += gb.z; bacc1.w += gb.w;
+            } else {
+                const float4 x = xa;
+                float4 g;
+                if (MODE == 2) {
+                    g.x = (x.x > 0.f && x.x < 1.f) ? d.x : 0.f;
+                    g.y = (x.y > 0.f && x.y < 1.f) ? d.y : 0.f;
+                    g.z = (x.z > 0.f && x.z < 1.f) ? d.z : 0.f;
+                    g.w = (x.w > 0.f && x.w < 1.f) ? d.w : 0.f;
                 } else {
-                    const float4 x = xa[q];
-                    float4 g;
-                    if (MODE == 2) {
-                        g.x = (x.x > 0.f && x.x < 1.f) ? d.x : 0.f;
-                        g.y = (x.y > 0.f && x.y < 1.f) ? d.y : 0.f;
-                        g.z = (x.z > 0.f && x.z < 1.f) ? d.z : 0.f;
-                        g.w = (x.w > 0.f && x.w < 1.f) ? d.w : 0.f;
-                    } else {
-                        const float4 a = make_float4(crelu01(x.x), crelu01(x.y), crelu01(x.z), crelu01(x.w));
-                        g.x = d.x * ((a.x > 0.f && a.x < 1.f) ? 2.0f * a.x : 0.f);
-                        g.y = d.y * ((a.y > 0.f && a.y < 1.f) ? 2.0f * a.y : 0.f);
-                        g.z = d.z * ((a.z > 0.f && a.z < 1.f) ? 2.0f * a.z : 0.f);
-                        g.w = d.w * ((a.w > 0.f && a.w < 1.f) ? 2.0f * a.w : 0.f);
-                    }
-                    *reinterpret_cast<float4*>(dft + (size_t)pp[q] * F + wcol) = g;
-                    bacc0.x += g.x; bacc0.y += g.y; bacc0.z += g.z; bacc0.w += g.w;
+                    const float4 a = make_float4(crelu01(x.x), crelu01(x.y), crelu01(x.z), crelu01(x.w));
+                    g.x = d.x * ((a.x > 0.f && a.x < 1.f) ? 2.0f * a.x : 0.f);
+                    g.y = d.y * ((a.y > 0.f && a.y < 1.f) ? 2.0f * a.y : 0.f);
+                    g.z = d.z * ((a.z > 0.f && a.z < 1.f) ? 2.0f * a.z : 0.f);
+                    g.w = d.w * ((a.w > 0.f && a.w < 1.f) ? 2.0f * a.w : 0.f);
                 }
+                *reinterpret_cast<float4*>(dft + (size_t)pp * F + wcol) = g;
+                bacc0.x += g.x; bacc0.y += g.y; bacc0.z += g.z; bacc0.w += g.w;
             }
         }
     }
-    // one partial row per (block, perspective): [n_ctas][2][F]
-    float* bp = bias_partials + ((size_t)blockIdx.x * 2 + persp) * F;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     *reinterpret_cast<float4*>(bp + wcol) = bacc0;
     if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
 }
@@ -1269,14 +1318,22 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
     (void)B;
     (void)max_tiles;
     const int work_cols = mode == 1 ? F / 2 : F;
-    if (l1 == 8 || l1 == 16) {
+    const int max_units = sort_max_units(max_tiles);
+    int bias_rows = n_ctas;
+    if ((l1 == 8 || l1 == 16) && n_ctas >= 2 * max_units) {
         int n_chunks = 1;
         while (work_cols / n_chunks > 1024 || (work_cols / n_chunks) % 128 != 0 && (work_cols / n_chunks) > 256) n_chunks *= 2;
         const int CW = work_cols / n_chunks;
-        dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
-#define DGRAD_REG(M, L)                                                                                              \
-        k_l1_dgrad_ftgrad_reg<M, L><<<grid, block, 0, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, scale, F, \
-                                                           nb, CW, dft_stm, dft_nstm, bias_partials)
+        bias_rows = 2 * max_units;
+        dim3 grid(bias_rows, 2, n_chunks), block(CW / 4);
+        const size_t smem = (size_t)DG_STAGES * 4 * (mode == 1 ? 2 : 1) * (CW / 4) * 16;
+#define DGRAD_REG(M, L)                                                                                                  \
+    do {                                                                                                                 \
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad_stream<M, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);   \
+        k_l1_dgrad_ftgrad_stream<M, L><<<grid, block, smem, s>>>(dl1, order, tiles, tiles + max_tiles, n_tiles + 1, wb, ws, pre_stm, \
+                                                                 pre_nstm, ft_bias, scale, F, nb, CW, dft_stm, dft_nstm,  \
+                                                                 bias_partials);                                         \
+    } while (0)
         if (l1 == 16) { if (mode == 1) DGRAD_REG(1, 16); else if (mode == 2) DGRAD_REG(2, 16); else DGRAD_REG(3, 16); }
         else { if (mode == 1) DGRAD_REG(1, 8); else if (mode == 2) DGRAD_REG(2, 8); else DGRAD_REG(3, 8); }
 #undef DGRAD_REG
@@ -1297,6 +1354,6 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
         else DGRAD_LAUNCH(3);
 #undef DGRAD_LAUNCH
     }
-    k_bias_partials_reduce<<<ceil_div(F, 8), 256, 0, s>>>(bias_partials, n_ctas, F, ft_b_grad);
+    k_bias_partials_reduce<<<ceil_div(F, 8), 256, 0, s>>>(bias_partials, bias_rows, F, ft_b_grad);
     return 2;
 }

@@ -120,6 +120,7 @@ struct tb_trainer {
     float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr;
     int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
     int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr, *bwd_slice = nullptr;
+    int dgrad_rows = 0;
     bool slice_fwd = false;  // this step's forward ran slice-resident (its row codes are in fwd_work)
     float* bwd_partial = nullptr;
     int last_n = 0;
@@ -357,7 +358,7 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
         { PhaseScope p(t, PH_L1_DGRAD);
           p.done(launch_l1_dgrad_ftgrad(t->stream, 1, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
                                         t->groups[4].w, t->pre[0], t->pre[1], t->groups[1].w, FT_POST_SCALE, B, F, c.l1_out,
-                                        c.num_buckets, t->dft[0], t->dft[1], t->bias_partials, t->groups[1].grad, DGRAD_CTAS)); }
+                                        c.num_buckets, t->dft[0], t->dft[1], t->bias_partials, t->groups[1].grad, t->dgrad_rows)); }
     } else {
         { PhaseScope p(t, PH_SMALL_WGRAD);
           p.done(launch_small_wgrad_simple(t->stream, t->order, t->seg_start, B, c.l1_out, c.l2_out, t->tail_a, t->tail_b,
@@ -370,7 +371,7 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
           p.done(launch_l1_dgrad_ftgrad(t->stream, c.activation == TB_ACT_CRELU ? 2 : 3, t->dl1, t->order, t->tiles, t->n_tiles,
                                         t->max_tiles, nullptr, t->groups[2].w, t->pre[0], t->pre[1], t->groups[1].w,
                                         FT_POST_SCALE, B, F, c.l1_out, 0, t->dft[0], t->dft[1], t->bias_partials,
-                                        t->groups[1].grad, DGRAD_CTAS)); }
+                                        t->groups[1].grad, t->dgrad_rows)); }
     }
     // slice-resident path when this step's forward was; the generic kernels then run only for a batch with a row outside
     // its item's slice (device-side gate)
@@ -628,7 +629,8 @@ int create_impl(tb_trainer* t) {
     const size_t n_cells = ls ? (size_t)(l2 * t->l2in + 2 * l2 + 1 + l1) : (size_t)(l1 * l2 + 2 * l2 + 1 + l1);
     CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 16 : (size_t)128) * n_cells));
     CU(t, dalloc(&t->l1w_partials, ((size_t)t->max_units + 1) * l1 * t->K));
-    CU(t, dalloc(&t->bias_partials, (size_t)DGRAD_CTAS * 2 * F));
+    t->dgrad_rows = DGRAD_CTAS > 2 * t->max_units ? DGRAD_CTAS : 2 * t->max_units;  // partial FT bias rows: one per block
+    CU(t, dalloc(&t->bias_partials, (size_t)t->dgrad_rows * 2 * F));
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
     CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
     CU(t, dalloc(&t->fwd_work, ft_forward_slice_work_ints((int)(2 * B), 129, A)));
