@@ -8,6 +8,7 @@
 #define TB_MAX_L1 32
 #define TB_MAX_L2 64
 #define TB_TILE_M 32      // positions per dense tile; a tile never mixes LayerStack buckets
+#define TB_UNIT_TILES 8   // tiles per work unit (consecutive tiles of one bucket)
 
 // One tile of positions for the bucket-grouped dense kernels: positions order[start .. start+count).
 // bucket == num_buckets marks positions whose bucket id is out of range (their per-bucket layers

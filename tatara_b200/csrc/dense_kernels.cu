@@ -8,6 +8,11 @@
 // rows through `order` and write results back at the position's own row.
 #include "common.cuh"
 
+// asynchronous 16-byte copy global -> shared (both 16-byte aligned)
+static __device__ __forceinline__ void dg_cp16(void* dst_shared, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
+
 #include <stdlib.h>
 
 #define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
@@ -787,7 +792,7 @@ int launch_small_wgrad_simple(cudaStream_t s, const int* order, const int* seg_s
 // ------------------------------------------------------------------------------------------------
 // L1 weight gradient.  gw_bucket[g][o][k] = sum over positions of bucket g of dl1[b][o] * x[b][k]
 // (dense_mm_bucket.rs:112-135); gw_shared[k][o] = the same sum over every position (dense_mm.rs:75-92),
-// obtained as the sum of the per-bucket results.  Work unit = up to UNIT_TILES tiles of one bucket;
+// obtained as the sum of the per-bucket results.  Work unit = up to TB_UNIT_TILES tiles of one bucket;
 // block (column chunk of 128, unit) writes partials[unit][o][k]; the second kernel adds the units of
 // each bucket in order.
 // ------------------------------------------------------------------------------------------------
@@ -948,19 +953,107 @@ __global__ void __launch_bounds__(256) k_l1_wgrad_v4(const float* __restrict__ x
     }
 }
 
+// Streaming form of the kernel above: the unit's positions (consecutive in the bucket order) and their dl1 rows are
+// staged once, then the x rows arrive through a private ring of asynchronous copies (a thread copies the 16 bytes it
+// reads itself), WG_STAGES rounds of four positions ahead of the arithmetic.
+#define WG_POS (TB_UNIT_TILES * TB_TILE_M)
+#define WG_STAGES 3
+template <int OPT>
+__global__ void __launch_bounds__(256) k_l1_wgrad_stream(const float* __restrict__ x, int K, const float* __restrict__ dl1,
+                                                          const int* __restrict__ order, const TileDesc* __restrict__ tiles,
+                                                          const TileDesc* __restrict__ units, const int* __restrict__ n_units, int l1,
+                                                          float* __restrict__ partials) {
+    extern __shared__ __align__(16) unsigned char s_dyn[];  // sdl [WG_POS][l1] floats, then the ring [WG_STAGES][4][threads] float4
+    __shared__ int s_pos[WG_POS];
+    const int u = blockIdx.y;
+    if (u >= *n_units) return;
+    const TileDesc ud = units[u];
+    const int K4 = K >> 2;
+    const int tcol = threadIdx.x & 127, og = threadIdx.x >> 7;
+    const int col4 = min(blockIdx.x * 128 + tcol, K4 - 1);  // a thread past the last column repeats it and drops its result
+    const bool active = blockIdx.x * 128 + tcol < K4;
+    const int p_begin = tiles[ud.start].start;
+    const TileDesc tl = tiles[ud.start + ud.count - 1];
+    const int n = tl.start + tl.count - p_begin;
+    float* sdl = reinterpret_cast<float*>(s_dyn);
+    float4* ring = reinterpret_cast<float4*>(s_dyn + (size_t)WG_POS * l1 * sizeof(float));
+    for (int i = threadIdx.x; i < WG_POS; i += blockDim.x) s_pos[i] = i < n ? order[p_begin + i] : -1;
+    __syncthreads();
+    const int l1q = l1 >> 2;
+    for (int e = threadIdx.x; e < n * l1q; e += blockDim.x) {
+        const int r = e / l1q, o4 = e - r * l1q;
+        reinterpret_cast<float4*>(sdl + (size_t)r * l1)[o4] = *reinterpret_cast<const float4*>(dl1 + (size_t)s_pos[r] * l1 + 4 * o4);
+    }
+    const int T = blockDim.x;
+    const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x);
+    auto issue = [&](int round) {
+        if (4 * round < n) {
+            const int stage = round % WG_STAGES;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int r = 4 * round + q;
+                dg_cp16(ring + (size_t)(stage * 4 + q) * T + threadIdx.x, x4 + (size_t)s_pos[r < n ? r : 0] * K4 + col4);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float4 acc[OPT];
+#pragma unroll
+    for (int j = 0; j < OPT; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int n_rounds = (n + 3) >> 2;
+#pragma unroll
+    for (int r = 0; r < WG_STAGES - 1; ++r) issue(r);
+    __syncthreads();  // dl1 rows staged
+    for (int round = 0; round < n_rounds; ++round) {
+        issue(round + WG_STAGES - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(WG_STAGES - 1) : "memory");
+        const int stage = round % WG_STAGES;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int r = 4 * round + q;
+            if (r >= n) break;
+            const float4 xv = ring[(size_t)(stage * 4 + q) * T + threadIdx.x];
+#pragma unroll
+            for (int j4 = 0; j4 < OPT / 4; ++j4) {
+                const float4 g = *reinterpret_cast<const float4*>(sdl + (size_t)r * l1 + og * OPT + 4 * j4);
+                const float gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[4 * j4 + j].x += gv[j] * xv.x;
+                    acc[4 * j4 + j].y += gv[j] * xv.y;
+                    acc[4 * j4 + j].z += gv[j] * xv.z;
+                    acc[4 * j4 + j].w += gv[j] * xv.w;
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (!active) return;
+#pragma unroll
+    for (int j = 0; j < OPT; ++j) {
+        const int o = og * OPT + j;
+        reinterpret_cast<float4*>(partials + ((size_t)u * l1 + o) * K)[col4] = acc[j];
+    }
+}
+
 int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, const int* order,
                     const TileDesc* tiles, const int* n_tiles, int max_tiles, int l1, int nb, float* partials,
                     float* gw_bucket, float* gw_shared) {
     const TileDesc* units = tiles + max_tiles;
     const int* n_units = n_tiles + 1;
     const int max_units = sort_max_units(max_tiles);
-    if (l1 == 8)
-        k_l1_wgrad_v4<8><<<dim3(ceil_div(K / 4, 128), max_units), 128, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
-    else if (l1 == 16)
-        k_l1_wgrad_v4<16><<<dim3(ceil_div(K / 4, 128), max_units), 128, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
-    else if (l1 == 32)
-        k_l1_wgrad_v4<16><<<dim3(ceil_div(K / 4, 128), max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
-    else
+    if (l1 == 8 || l1 == 16 || l1 == 32) {
+        const int threads = l1 == 32 ? 256 : 128;
+        const size_t smem = (size_t)WG_POS * l1 * sizeof(float) + (size_t)WG_STAGES * 4 * threads * 16;
+        const dim3 grid(ceil_div(K / 4, 128), max_units);
+        if (l1 == 8) {
+            cudaFuncSetAttribute(k_l1_wgrad_stream<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            k_l1_wgrad_stream<8><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+        } else {
+            cudaFuncSetAttribute(k_l1_wgrad_stream<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            k_l1_wgrad_stream<16><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+        }
+    } else
         k_l1_wgrad<<<dim3(K / 128, max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
     float* rest = partials + (size_t)max_units * l1 * K;  // one more [l1][K] row behind the unit partials
     k_l1_wgrad_final<<<dim3(ceil_div(l1 * K, 256), nb + 1), 256, 0, s>>>(partials, units, n_units, K, l1, nb, gw_bucket, rest);
@@ -1126,9 +1219,7 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
 // of four positions ahead of the arithmetic, which keeps the global loads in flight back to back.
 #define DG_POS 128     // positions per block
 #define DG_STAGES 3
-static __device__ __forceinline__ void dg_cp16(void* dst_shared, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
-}
+static_assert(2 * DG_POS == TB_UNIT_TILES * TB_TILE_M, "a block of the streaming kernel owns half a work unit");
 template <int MODE, int L1>
 __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __restrict__ dl1, const int* __restrict__ order,
                                                                  const TileDesc* __restrict__ tiles, const TileDesc* __restrict__ units,

@@ -9,7 +9,6 @@
 
 #define SORT_BLOCK 1024
 #define SORT_MAX_KEYS 128
-#define UNIT_TILES 8  // tiles per work unit of the L1 weight-gradient kernel
 
 struct BucketKey {
     const int* bucket;  // may be NULL: one group
@@ -109,7 +108,7 @@ __global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, in
     if (key >= 0) out[base[key * G + blockIdx.x] + s_cnt[w][key] + rank] = i;
 }
 
-// tiles: runs of <= TB_TILE_M positions of one bucket; units: runs of <= UNIT_TILES tiles of one bucket
+// tiles: runs of <= TB_TILE_M positions of one bucket; units: runs of <= TB_UNIT_TILES tiles of one bucket
 __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_start, int K, TileDesc* __restrict__ tiles,
                                                      int* __restrict__ n_tiles, TileDesc* __restrict__ units,
                                                      int* __restrict__ n_units) {
@@ -121,7 +120,7 @@ __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_
             s_unit_base[k] = urun;
             const int nt = (seg_start[k + 1] - seg_start[k] + TB_TILE_M - 1) / TB_TILE_M;
             trun += nt;
-            urun += (nt + UNIT_TILES - 1) / UNIT_TILES;
+            urun += (nt + TB_UNIT_TILES - 1) / TB_UNIT_TILES;
         }
         *n_tiles = trun;
         *n_units = urun;
@@ -138,11 +137,11 @@ __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_
             d.pad = 0;
             tiles[s_tile_base[k] + t] = d;
         }
-        const int nu = (nt + UNIT_TILES - 1) / UNIT_TILES;
+        const int nu = (nt + TB_UNIT_TILES - 1) / TB_UNIT_TILES;
         for (int u = threadIdx.x; u < nu; u += blockDim.x) {
             TileDesc d;
-            d.start = s_tile_base[k] + u * UNIT_TILES;
-            d.count = min(UNIT_TILES, nt - u * UNIT_TILES);
+            d.start = s_tile_base[k] + u * TB_UNIT_TILES;
+            d.count = min(TB_UNIT_TILES, nt - u * TB_UNIT_TILES);
             d.bucket = k;
             d.pad = 0;
             units[s_unit_base[k] + u] = d;
@@ -150,7 +149,7 @@ __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_
     }
 }
 
-int sort_max_units(int max_tiles) { return max_tiles / UNIT_TILES + TB_MAX_BUCKETS + 2; }
+int sort_max_units(int max_tiles) { return max_tiles / TB_UNIT_TILES + TB_MAX_BUCKETS + 2; }
 
 // hist: scratch of (nb + 1) * ceil(B / 1024) ints
 int launch_bucket_sort(cudaStream_t s, const int* bucket, int B, int nb, int* order, TileDesc* tiles, int* n_tiles,
