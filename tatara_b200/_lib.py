@@ -105,7 +105,7 @@ def load():
         raise ImportError(
             "tatara_b200: %s is missing; build it with `python -m tatara_b200.build` (needs nvcc). "
             "There is no CPU fallback." % LIB_PATH)
-    lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL | os.RTLD_NOW)  # RTLD_NOW: an unresolved symbol fails here, not mid-run
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError names the missing symbol
         fn.restype = res

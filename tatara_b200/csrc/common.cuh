@@ -112,7 +112,7 @@ int launch_bucket_sort(cudaStream_t s, const int* bucket /*may be NULL*/, int B,
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb /*[nb][l1][K] or NULL*/,
                       const float* bb, const float* ws /*[K][l1]*/, const float* bs, float* y /*[B][l1]*/,
-                      int l1, int nb);
+                      int l1, int nb, float* weff /*scratch [(nb + 1) * l1 * (K + 1)] or NULL*/);
 int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
                            const float* wdl, const float* l2_w, const float* l2_b, const float* l3_w,
                            const float* l3_b, LossParams lp, int B, int l1, int l2, int nb, float* net_output,

@@ -224,9 +224,137 @@ __global__ void __launch_bounds__(64) k_l1_forward_tiled(const float* __restrict
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// L1 forward, streaming form for l1 = 8, 16 or 32.  The per-bucket and the shared layer see the same input and their
+// outputs are added, so they are one contraction with the effective weights weff[g] = wb[g] + ws^T (weff[nb] = ws^T for
+// positions without a bucket), built once per step by k_l1_weff.  A block owns 128 consecutive positions of the bucket
+// order (half a work unit); x rows and the weight rows arrive in K chunks of 16 through a three-stage ring of
+// asynchronous copies; a thread keeps a 4-position x 8-output tile of sums in registers and reads both operands as
+// 128-bit rows along k (row stride 20 floats: the rows a quarter warp touches fall into different banks).
+// ------------------------------------------------------------------------------------------------
+__global__ void k_l1_weff(const float* __restrict__ wb, const float* __restrict__ bb, const float* __restrict__ ws,
+                          const float* __restrict__ bs, int K, int l1, int nb, float* __restrict__ weff, float* __restrict__ beff) {
+    const int g = blockIdx.y;
+    const size_t n = (size_t)l1 * K;
+    const bool use_b = wb != nullptr && g < nb;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int o = (int)(i / K), k = (int)(i - (size_t)o * K);
+        float v = ws[(size_t)k * l1 + o];
+        if (use_b) v = wb[(size_t)g * n + i] + v;
+        weff[(size_t)g * n + i] = v;
+    }
+    if (blockIdx.x == 0 && (int)threadIdx.x < l1) {
+        float b = bs ? bs[threadIdx.x] : 0.f;
+        if (use_b && bb) b = bb[(size_t)g * l1 + threadIdx.x] + b;
+        beff[(size_t)g * l1 + threadIdx.x] = b;
+    }
+}
+
+#define LF_POS 128
+#define LF_KC 16
+#define LF_LD 20
+#define LF_STAGES 3
+static_assert(2 * LF_POS == TB_UNIT_TILES * TB_TILE_M, "a block of the streaming forward owns half a work unit");
+template <int L1>
+__global__ void __launch_bounds__(4 * L1) k_l1_forward_stream(const float* __restrict__ x, int K, const int* __restrict__ order,
+                                                              const TileDesc* __restrict__ tiles, const TileDesc* __restrict__ units,
+                                                              const int* __restrict__ n_units, const float* __restrict__ weff,
+                                                              const float* __restrict__ beff, float* __restrict__ y, int nb) {
+    constexpr int TX = L1 / 8, TY = 32 / TX, NT = 32 * TX;
+    constexpr int STAGE_FLOATS = (LF_POS + L1) * LF_LD;
+    extern __shared__ __align__(16) float s_ring[];  // [LF_STAGES][LF_POS + L1][LF_LD]
+    __shared__ int s_pos[LF_POS];
+    const int u = blockIdx.x >> 1, h = blockIdx.x & 1;
+    if (u >= *n_units) return;
+    const TileDesc ud = units[u];
+    const int per = LF_POS / TB_TILE_M;
+    const int first = ud.start + h * per, last = min(ud.start + ud.count, first + per);
+    if (first >= last) return;
+    const int p_begin = tiles[first].start;
+    const int n = tiles[last - 1].start + tiles[last - 1].count - p_begin;
+    const int g = ud.bucket < nb ? ud.bucket : nb;
+    const int tid = threadIdx.x;
+    for (int i = tid; i < LF_POS; i += NT) s_pos[i] = order[p_begin + (i < n ? i : 0)];  // rows past the end repeat the first
+    __syncthreads();
+    const float* __restrict__ wg = weff + (size_t)g * L1 * K;
+    const int nk = K / LF_KC;
+    auto issue = [&](int it) {
+        if (it < nk) {
+            float* st = s_ring + (size_t)(it % LF_STAGES) * STAGE_FLOATS;
+            const int k0 = it * LF_KC;
+            for (int e = tid; e < LF_POS * 4; e += NT) {
+                const int r = e >> 2, pc = e & 3;
+                dg_cp16(st + r * LF_LD + 4 * pc, x + (size_t)s_pos[r] * K + k0 + 4 * pc);
+            }
+            for (int e = tid; e < L1 * 4; e += NT) {
+                const int o = e >> 2, pc = e & 3;
+                dg_cp16(st + (LF_POS + o) * LF_LD + 4 * pc, wg + (size_t)o * K + k0 + 4 * pc);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int lane = tid & 31, warp = tid >> 5;
+    const int tx = lane % TX, ty = lane / TX;
+    const int row0 = warp * (4 * TY) + ty;  // the thread's positions: row0 + TY * i
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+#pragma unroll
+    for (int it = 0; it < LF_STAGES - 1; ++it) issue(it);
+    for (int it = 0; it < nk; ++it) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(LF_STAGES - 2) : "memory");
+        __syncthreads();  // chunk `it` has landed for every thread; chunk it - 1 has been consumed by every thread
+        issue(it + LF_STAGES - 1);
+        const float* st = s_ring + (size_t)(it % LF_STAGES) * STAGE_FLOATS;
+#pragma unroll
+        for (int kk = 0; kk < LF_KC; kk += 4) {
+            float4 xv[4], wv[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(st + (row0 + TY * i) * LF_LD + kk);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wv[j] = *reinterpret_cast<const float4*>(st + (LF_POS + tx + TX * j) * LF_LD + kk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[i][j] += xv[i].x * wv[j].x;
+                    acc[i][j] += xv[i].y * wv[j].y;
+                    acc[i][j] += xv[i].z * wv[j].z;
+                    acc[i][j] += xv[i].w * wv[j].w;
+                }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = row0 + TY * i;
+        if (r >= n) continue;
+        float* yr = y + (size_t)s_pos[r] * L1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int o = tx + TX * j;
+            yr[o] = acc[i][j] + beff[(size_t)g * L1 + o];
+        }
+    }
+}
+
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb, const float* bb, const float* ws,
-                      const float* bs, float* y, int l1, int nb) {
+                      const float* bs, float* y, int l1, int nb, float* weff) {
+    if ((l1 == 8 || l1 == 16 || l1 == 32) && K % LF_KC == 0 && weff != nullptr) {
+        float* beff = weff + (size_t)(nb + 1) * l1 * K;
+        k_l1_weff<<<dim3(ceil_div(l1 * K, 256 * 4), nb + 1), 256, 0, s>>>(wb, bb, ws, bs, K, l1, wb ? nb : 0, weff, beff);
+        const int max_units = sort_max_units(max_tiles);
+        const size_t smem = (size_t)LF_STAGES * (LF_POS + l1) * LF_LD * sizeof(float);
+        const TileDesc* units = tiles + max_tiles;
+        const int nbe = wb ? nb : 0;
+        if (l1 == 8) k_l1_forward_stream<8><<<2 * max_units, 32, smem, s>>>(x, K, order, tiles, units, n_tiles + 1, weff, beff, y, nbe);
+        else if (l1 == 16) k_l1_forward_stream<16><<<2 * max_units, 64, smem, s>>>(x, K, order, tiles, units, n_tiles + 1, weff, beff, y, nbe);
+        else k_l1_forward_stream<32><<<2 * max_units, 128, smem, s>>>(x, K, order, tiles, units, n_tiles + 1, weff, beff, y, nbe);
+        return 2;
+    }
     const int nout = wb ? 2 * l1 : l1;
     if (l1 % 4 == 0 && nout <= 64) {
         if (wb) {

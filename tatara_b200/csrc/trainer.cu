@@ -117,7 +117,7 @@ struct tb_trainer {
     double *loss_partials = nullptr, *loss_acc = nullptr;
     int *order = nullptr, *n_tiles = nullptr, *seg_start = nullptr;
     TileDesc* tiles = nullptr;
-    float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr;
+    float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr, *l1_weff = nullptr;
     int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
     int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr, *bwd_slice = nullptr;
     int dgrad_rows = 0;
@@ -324,7 +324,7 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     if (ls) {
         { PhaseScope p(t, PH_L1_FWD);
           p.done(launch_l1_forward(t->stream, t->combined, F, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
-                                   t->groups[3].w, t->groups[4].w, t->groups[5].w, t->l1_out, c.l1_out, c.num_buckets)); }
+                                   t->groups[3].w, t->groups[4].w, t->groups[5].w, t->l1_out, c.l1_out, c.num_buckets, t->l1_weff)); }
         { PhaseScope p(t, PH_TAIL);
           p.done(launch_tail_layerstack(t->stream, t->l1_out, d.bucket, d.score, d.wdl, t->groups[6].w, t->groups[7].w,
                                         t->groups[8].w, t->groups[9].w, lp, B, c.l1_out, c.l2_out, c.num_buckets,
@@ -333,7 +333,7 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     } else {
         { PhaseScope p(t, PH_L1_FWD);
           p.done(launch_l1_forward(t->stream, t->combined, 2 * F, t->order, t->tiles, t->n_tiles, t->max_tiles, nullptr, nullptr,
-                                   t->groups[2].w, t->groups[3].w, t->l1_out, c.l1_out, 0)); }
+                                   t->groups[2].w, t->groups[3].w, t->l1_out, c.l1_out, 0, t->l1_weff)); }
         { PhaseScope p(t, PH_TAIL);
           p.done(launch_tail_simple(t->stream, t->l1_out, d.score, d.wdl, t->groups[4].w, t->groups[5].w, t->groups[6].w,
                                     t->groups[7].w, lp, c.activation, B, c.l1_out, c.l2_out, t->net_output, t->dy, t->dl1,
@@ -527,7 +527,7 @@ void free_all(tb_trainer* t) {
     cudaFree(t->combined); cudaFree(t->l1_out); cudaFree(t->dl1); cudaFree(t->net_output); cudaFree(t->dy);
     cudaFree(t->tail_a); cudaFree(t->tail_b); cudaFree(t->tail_c); cudaFree(t->loss_partials); cudaFree(t->loss_acc);
     cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
-    cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials);
+    cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials); cudaFree(t->l1_weff);
     cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
     cudaFree(t->fwd_work); cudaFree(t->bwd_slice); cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
     if (t->ev_t0) cudaEventDestroy(t->ev_t0);
@@ -629,6 +629,7 @@ int create_impl(tb_trainer* t) {
     const size_t n_cells = ls ? (size_t)(l2 * t->l2in + 2 * l2 + 1 + l1) : (size_t)(l1 * l2 + 2 * l2 + 1 + l1);
     CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 16 : (size_t)128) * n_cells));
     CU(t, dalloc(&t->l1w_partials, ((size_t)t->max_units + 1) * l1 * t->K));
+    CU(t, dalloc(&t->l1_weff, (size_t)(nb + 1) * l1 * (t->K + 1)));  // effective L1 weights and biases per bucket
     t->dgrad_rows = DGRAD_CTAS > 2 * t->max_units ? DGRAD_CTAS : 2 * t->max_units;  // partial FT bias rows: one per block
     CU(t, dalloc(&t->bias_partials, (size_t)t->dgrad_rows * 2 * F));
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
