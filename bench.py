@@ -44,7 +44,11 @@ CONFIG_INDEX = {"cfg1": 1, "cfg2": 2, "cfg3": 3}
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (bytes at the benchmark's full size; None = not captured yet)
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/step_cfg3_launch_list.md: full-size launches of the dominant kernel of each phase (the metrics take one pass)
+    ("cfg3", "ft_backward"): 1621.8e6, ("cfg3", "ft_forward"): 1748.1e6, ("cfg3", "opt_ft"): 3943.4e6,
+    ("cfg3", "l1_dgrad_ftgrad"): 1583.0e6, ("cfg3", "l1_forward"): 404.6e6, ("cfg3", "l1_wgrad"): 425.6e6,
+}
 
 
 def peak_hbm():
@@ -305,6 +309,9 @@ def main():
             "roofline": {"bound": "hbm", "kernel": dominant, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                          "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, dominant)),
                          "algorithmic_bytes": alg[dominant], "kernel_ms": phases[dominant],
+                         # not graded: what a cache-less gather would move; the slice-resident FT kernels serve these
+                         # bytes from shared memory
+                         "lookup_bytes": 2.0 * B * fs.max_active * w["F"] * 4.0 if dominant in ("ft_forward", "ft_backward") else None,
                          "step": {"algorithmic_bytes": alg["step"], "achieved": step_ach, "frac": step_ach / peak}},
             "kernels_ms": {k: round(v, 4) for k, v in phases.items()},
         }
