@@ -94,8 +94,9 @@ size_t ft_backward_slice_ints(int n_items, int A, int rows_per_slice);
 const int* ft_slice_outside_flag(int* fwd_work, int n_items, int N, int rows_per_slice);
 int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int* bwd_work, int B, int A, int N,
                          int rows_per_slice, int n_persp);
+// the rows of slices [slice_begin, slice_begin + slice_count)
 int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
-                             int A, int N, int F, int rows_per_slice, int n_persp, float* grad);
+                             int A, int N, int F, int rows_per_slice, int n_persp, int slice_begin, int slice_count, float* grad);
 // items of both perspectives sorted by the table slice of their features; hist: [(slices + 1) * ceil(n_persp*B/1024)],
 // seg: [slices + 2]
 int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,

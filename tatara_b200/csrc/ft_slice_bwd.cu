@@ -242,12 +242,13 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                                                                 const unsigned long long* __restrict__ rowinfo,
                                                                 const unsigned short* __restrict__ lists,
                                                                 const int* __restrict__ outside_flag, int B, int F, int N, int rps,
-                                                                int rps_pad, int CH, int region, float* __restrict__ grad) {
+                                                                int rps_pad, int CH, int region, int slice_begin,
+                                                                float* __restrict__ grad) {
     // dft strip [CH + 1][32] floats (the last row stays zero), row records [rps_pad] 64-bit, list cells [region] 16-bit
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ int s_ctl[4];
     if (*outside_flag) return;
-    const int k = blockIdx.x, strip = blockIdx.y;
+    const int k = slice_begin + blockIdx.x, strip = blockIdx.y;
     const int row0 = k * rps;
     const int rows = min(rps, N - row0);
     const int tid = threadIdx.x, lane = tid & 31;
@@ -433,7 +434,7 @@ int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int
 }
 
 int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
-                             int A, int N, int F, int rps, int n_persp, float* grad) {
+                             int A, int N, int F, int rps, int n_persp, int slice_begin, int slice_count, float* grad) {
     if (B <= 0) return 0;
     const int n_items = n_persp * B;
     const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
@@ -443,8 +444,9 @@ int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* 
     const BwdPointers P = bwd_pointers(bwd_work, L);
     const size_t smem = bwd_smem_bytes(L.CH, rps, A_pad);
     cudaFuncSetAttribute(k_ft_backward_slice, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k_ft_backward_slice<<<dim3(n_slices, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len, P.rowinfo,
-                                                                   P.lists, sb.outside_flag, B, F, N, rps, L.rps_pad, L.CH, L.region,
-                                                                   grad);
+    if (slice_begin < 0 || slice_count <= 0 || slice_begin + slice_count > n_slices) return 0;
+    k_ft_backward_slice<<<dim3(slice_count, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len, P.rowinfo,
+                                                                      P.lists, sb.outside_flag, B, F, N, rps, L.rps_pad, L.CH,
+                                                                      L.region, slice_begin, grad);
     return 1;
 }

@@ -24,6 +24,7 @@
 #define RANGER_K 6
 #define N_SMA_THRESHOLD 5.0f
 #define DGRAD_CTAS (148 * 2)
+#define AR_PARTS 3  // launches of the FT weight gradient whose all-reduces overlap the next launch (data parallel)
 
 namespace {
 
@@ -121,6 +122,9 @@ struct tb_trainer {
     int *feat_counts = nullptr, *feat_offsets = nullptr, *feat_cursor = nullptr, *feat_lists = nullptr;
     int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr, *bwd_slice = nullptr;
     int dgrad_rows = 0;
+    cudaStream_t comm_stream = nullptr;  // data parallel: all-reduces behind the FT weight gradient
+    cudaEvent_t ev_part[AR_PARTS] = {}, ev_comm_done = nullptr;
+    bool ar_pipelined = false;
     bool slice_fwd = false;  // this step's forward ran slice-resident (its row codes are in fwd_work)
     float* bwd_partial = nullptr;
     int last_n = 0;
@@ -385,12 +389,40 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
                                 t->feat_lists);
       p.done(n); }
     { PhaseScope p(t, PH_FT_BWD);
-      int n = 0;
-      if (slice_bwd)
-          n += launch_ft_backward_slice(t->stream, t->dft[0], t->dft[1], t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2,
-                                        t->groups[0].grad);
-      n += launch_ft_backward_split(t->stream, gate, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2, t->bwd_plan,
-                                    t->bwd_partial, t->groups[0].grad);
+      int n = launch_ft_backward_split(t->stream, gate, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2,
+                                       t->bwd_plan, t->bwd_partial, t->groups[0].grad);
+      if (slice_bwd) {
+          // Data parallel: the slices are done in AR_PARTS launches and the gradient rows of each part are all-reduced on a
+          // second stream while the next part is computed (the small groups, ready since the dense backward, ride with the
+          // first part, the loss with the last).  Whichever path wrote the rows (the gated generic kernels come first), they
+          // are final when the part's event is recorded.
+          const int n_slices = (N + rps - 1) / rps;
+          const bool pipeline = c.world_size > 1 && n_slices >= 8 && n_slices >= 2 * AR_PARTS;  // every part has slices
+          const int parts = pipeline ? AR_PARTS : 1;
+          const int64_t ft_off = t->groups[0].grad - t->grad_arena;
+          int rc = 0;
+          for (int part = 0; part < parts; ++part) {
+              // equal parts measured best on two B200s (a smaller last part or more parts cost more than they hid)
+              const int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
+              n += launch_ft_backward_slice(t->stream, t->dft[0], t->dft[1], t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
+                                            t->groups[0].grad);
+              if (!pipeline) continue;
+              CU(t, cudaEventRecord(t->ev_part[part], t->stream));
+              CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_part[part], 0));
+              const int64_t e0 = part == 0 ? 0 : ft_off + (int64_t)(k0 * rps < N ? k0 * rps : N) * F;
+              const int64_t e1 = ft_off + (int64_t)(k1 * rps < N ? k1 * rps : N) * F;
+              if (rc == 0) rc = g_nccl.GroupStart();
+              if (rc == 0) rc = g_nccl.AllReduce(t->grad_arena + e0, t->grad_arena + e0, (size_t)(e1 - e0), /*ncclFloat*/ 7, /*ncclSum*/ 0, t->comm, t->comm_stream);
+              if (rc == 0 && part == parts - 1) rc = g_nccl.AllReduce(t->loss_acc, t->loss_acc, 1, /*ncclDouble*/ 8, 0, t->comm, t->comm_stream);
+              const int rc2 = g_nccl.GroupEnd();
+              if (rc == 0) rc = rc2;
+          }
+          if (pipeline) {
+              if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString(rc));
+              CU(t, cudaEventRecord(t->ev_comm_done, t->comm_stream));
+              t->ar_pipelined = true;
+          }
+      }
       p.done(n); }
     return TB_OK;
 }
@@ -399,6 +431,12 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
 int run_allreduce(tb_trainer* t) {
     if (t->cfg.world_size <= 1) return TB_OK;
     PhaseScope p(t, PH_ALLREDUCE);
+    if (t->ar_pipelined) {  // issued part by part behind the FT weight gradient: only the tail is waited for here
+        t->ar_pipelined = false;
+        CU(t, cudaStreamWaitEvent(t->stream, t->ev_comm_done, 0));
+        p.done(0);
+        return TB_OK;
+    }
     int rc = g_nccl.GroupStart();
     if (rc == 0) rc = g_nccl.AllReduce(t->grad_arena, t->grad_arena, (size_t)t->arena_reduce_len, /*ncclFloat*/ 7, /*ncclSum*/ 0, t->comm, t->stream);
     if (rc == 0) rc = g_nccl.AllReduce(t->loss_acc, t->loss_acc, 1, /*ncclDouble*/ 8, 0, t->comm, t->stream);
@@ -536,6 +574,9 @@ void free_all(tb_trainer* t) {
         if (t->ph_start[i]) cudaEventDestroy(t->ph_start[i]);
         if (t->ph_stop[i]) cudaEventDestroy(t->ph_stop[i]);
     }
+    if (t->comm_stream) cudaStreamDestroy(t->comm_stream);
+    for (auto& e : t->ev_part) if (e) cudaEventDestroy(e);
+    if (t->ev_comm_done) cudaEventDestroy(t->ev_comm_done);
     if (t->copy_stream) cudaStreamDestroy(t->copy_stream);
     if (t->stream) cudaStreamDestroy(t->stream);
     delete t;
@@ -657,6 +698,13 @@ int create_impl(tb_trainer* t) {
         memcpy(id.internal, c.nccl_unique_id, 128);
         const int rc = g_nccl.CommInitRank(&t->comm, c.world_size, id, c.rank);
         if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(rc));
+        {   // highest priority: when an SM frees up, the waiting all-reduce gets it before the next gradient block does
+            int lo = 0, hi = 0;
+            CU(t, cudaDeviceGetStreamPriorityRange(&lo, &hi));
+            CU(t, cudaStreamCreateWithPriority(&t->comm_stream, cudaStreamNonBlocking, hi));
+        }
+        for (auto& e : t->ev_part) CU(t, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        CU(t, cudaEventCreateWithFlags(&t->ev_comm_done, cudaEventDisableTiming));
     }
     CU(t, cudaDeviceSynchronize());
     return TB_OK;
