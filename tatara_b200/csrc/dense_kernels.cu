@@ -515,10 +515,13 @@ __global__ void __launch_bounds__(128) k_tail_layerstack(const float* __restrict
     block_loss_partial(e2, loss_partials);
 }
 
-// Warp-per-position variant for l2 <= 32 and 2 (l1 - 1) <= 32: lane o owns output o of L2, lane i input i; the
-// vectors travel between lanes through shuffles, every store of a per-position vector is one coalesced row.
-// Sums over the L2 inputs / outputs run in index order, like the oracle; only the 32-term L3 dot product is
-// a butterfly reduction.
+// Warp-per-position variant for l2 <= 32 and 2 (l1 - 1) <= 32: lane o owns output o of L2, lane i input i.  Shared
+// memory holds every bucket's L2 weights by output row with a row stride of TW_LD floats (rows 16-byte aligned, eight
+// neighbouring rows in different banks), and a 32-float vector per warp through which a position's L2 input and L2
+// output gradient reach all lanes with 128-bit broadcast loads; the forward reads a weight row with 128-bit loads, the
+// backward a weight column.  Sums over the L2 inputs / outputs run in index order, like the
+// oracle; only the 32-term L3 dot product is a butterfly reduction.
+#define TW_LD 36
 __global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __restrict__ l1_total, const int* __restrict__ bucket,
                                                                const float* __restrict__ score, const float* __restrict__ wdl,
                                                                const float* __restrict__ l2_w, const float* __restrict__ l2_b,
@@ -528,19 +531,25 @@ __global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __res
                                                                float* __restrict__ dl1_total, float* __restrict__ l2_input_o,
                                                                float* __restrict__ dl2_out_o, float* __restrict__ l2_acted_o,
                                                                double* __restrict__ loss_partials, int backward) {
-    extern __shared__ float s_w[];
+    extern __shared__ __align__(16) float s_w[];
     const int l1e = l1 - 1, l2in = 2 * l1e;
-    float* sw2 = s_w;                   // [nb][l2][l2in]
-    float* sb2 = sw2 + nb * l2 * l2in;  // [nb][l2]
-    float* sw3 = sb2 + nb * l2;         // [nb][l2]
-    float* sb3 = sw3 + nb * l2;         // [nb]
-    for (int i = threadIdx.x; i < nb * l2 * l2in; i += blockDim.x) sw2[i] = l2_w[i];
+    float* swr = s_w;                            // [nb][32 outputs][TW_LD]: swr[g][o][i] = l2_w[g][o][i], zero padded
+    float* sb2 = swr + (size_t)nb * 32 * TW_LD;  // [nb][l2]
+    float* sw3 = sb2 + nb * l2;               // [nb][l2]
+    float* sb3 = sw3 + nb * l2;               // [nb]
+    float* svec = sb3 + ((nb + 3) & ~3);      // [warps][32]
+    for (int e = threadIdx.x; e < nb * 32 * TW_LD; e += blockDim.x) {
+        const int g = e / (32 * TW_LD), r = (e / TW_LD) & 31, c = e % TW_LD;
+        swr[e] = (r < l2 && c < l2in) ? l2_w[((size_t)g * l2 + r) * l2in + c] : 0.f;
+    }
     for (int i = threadIdx.x; i < nb * l2; i += blockDim.x) { sb2[i] = l2_b[i]; sw3[i] = l3_w[i]; }
     for (int i = threadIdx.x; i < nb; i += blockDim.x) sb3[i] = l3_b[i];
     __syncthreads();
     const int lane = threadIdx.x & 31;
     const int wpb = blockDim.x >> 5;
     const unsigned full = 0xffffffffu;
+    float* vec = svec + (threadIdx.x >> 5) * 32;
+    const float4* vec4 = reinterpret_cast<const float4*>(vec);
     double e2 = 0.0;
     for (int b = blockIdx.x * wpb + (threadIdx.x >> 5); b < B; b += gridDim.x * wpb) {
         const int g = bucket[b];
@@ -553,9 +562,16 @@ __global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __res
         const float in = lane < l2in ? crelu01(pre) : 0.f;
         float d2 = 0.f, a2 = 0.f, l3 = 0.f;
         if (valid) {
-            const float* wr = sw2 + ((size_t)g * l2 + (lane < l2 ? lane : 0)) * l2in;
+            __syncwarp();
+            vec[lane] = in;
+            __syncwarp();
+            const float4* wr = reinterpret_cast<const float4*>(swr + ((size_t)g * 32 + lane) * TW_LD);
             float sum = lane < l2 ? sb2[g * l2 + lane] : 0.f;
-            for (int i = 0; i < l2in; ++i) sum += __shfl_sync(full, in, i) * wr[i];
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+                const float4 x = vec4[i4], w = wr[i4];
+                sum += x.x * w.x; sum += x.y * w.y; sum += x.z * w.z; sum += x.w * w.w;
+            }
             d2 = lane < l2 ? sum : 0.f;
             a2 = lane < l2 ? crelu01(d2) : 0.f;
             float part = lane < l2 ? a2 * sw3[g * l2 + lane] : 0.f;
@@ -579,8 +595,16 @@ __global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __res
             }
             float sum = 0.f;
             if (valid) {
-                const float* wc = sw2 + (size_t)g * l2 * l2in + (lane < l2in ? lane : 0);
-                for (int o = 0; o < l2; ++o) sum += __shfl_sync(full, dl2o, o) * wc[o * l2in];
+                __syncwarp();
+                vec[lane] = dl2o;
+                __syncwarp();
+                const float* wc = swr + (size_t)g * 32 * TW_LD + lane;  // column `lane`: neighbouring lanes, neighbouring banks
+#pragma unroll
+                for (int o4 = 0; o4 < 8; ++o4) {
+                    const float4 x = vec4[o4];
+                    sum += x.x * wc[(4 * o4 + 0) * TW_LD]; sum += x.y * wc[(4 * o4 + 1) * TW_LD];
+                    sum += x.z * wc[(4 * o4 + 2) * TW_LD]; sum += x.w * wc[(4 * o4 + 3) * TW_LD];
+                }
             }
             const float dpre = (lane < l2in && pre > 0.f && pre < 1.0f) ? sum : 0.f;  // crelu_grad on l2_pre
             // lane i < l1e: d(main_i) = dpre[l1e + i] + 2 main_i scale dpre[i]
@@ -606,11 +630,12 @@ int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* buc
     const int l2in = 2 * (l1 - 1);
     const size_t smem = sizeof(float) * ((size_t)nb * l2 * l2in + 2 * (size_t)nb * l2 + nb);
     cudaFuncSetAttribute(k_tail_layerstack, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (l2 <= 32 && l2in <= 32 && smem <= 96 * 1024) {
-        cudaFuncSetAttribute(k_tail_layerstack_warp, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    const size_t wsmem = sizeof(float) * ((size_t)nb * 32 * TW_LD + 2 * (size_t)nb * l2 + ((nb + 3) & ~3) + 8 * 32);
+    if (l2 <= 32 && l2 % 4 == 0 && l2in <= 32 && wsmem <= 110 * 1024) {
+        cudaFuncSetAttribute(k_tail_layerstack_warp, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
         int blocks = ceil_div(B, 8);
         if (blocks > 148 * 4) blocks = 148 * 4;
-        k_tail_layerstack_warp<<<blocks, 256, smem, s>>>(l1_total, bucket, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, B, l1, l2, nb,
+        k_tail_layerstack_warp<<<blocks, 256, wsmem, s>>>(l1_total, bucket, score, wdl, l2_w, l2_b, l3_w, l3_b, lp, B, l1, l2, nb,
                                                         net_output, dy, dl1_total, l2_input, dl2_out, l2_acted, loss_partials,
                                                         backward);
         k_reduce_double<<<1, 256, 0, s>>>(loss_partials, blocks, loss_acc);
@@ -783,6 +808,7 @@ int launch_tail_simple(cudaStream_t s, const float* l1_pre, const float* score, 
 // (dense_mm_bucket.rs:112-161; native_kernels.cu:2591-2744 use register accumulators + atomics.)
 // ------------------------------------------------------------------------------------------------
 #define SW_CMAX 5
+#define SW_SPLIT_LS 64  // blocks per bucket segment (LayerStack); the Simple net splits its one segment in 128
 __global__ void __launch_bounds__(1024) k_small_wgrad(const int* __restrict__ order, const int* __restrict__ seg_start,
                                                        const float* __restrict__ U, int dimU, const float* __restrict__ V,
                                                        int dimV, const float* __restrict__ Bsrc, const float* __restrict__ l2_acted,
@@ -903,7 +929,7 @@ int launch_small_wgrad_layerstack(cudaStream_t s, const int* order, const int* s
                                   float* l1s_b_grad) {
     (void)B;
     // L2 weight cell (o, i) = sum dl2_out[b][o] * l2_input[b][i]
-    return small_wgrad(s, order, seg_start, nb + 1, 1, 16, dl2_out, l2, l2_input, 2 * (l1 - 1), dl2_out, l2_acted, l2, dy,
+    return small_wgrad(s, order, seg_start, nb + 1, 1, SW_SPLIT_LS, dl2_out, l2, l2_input, 2 * (l1 - 1), dl2_out, l2_acted, l2, dy,
                        dl1_total, l1, partials, l2_w_grad, l2_b_grad, l3_w_grad, l3_b_grad, l1_b_grad, l1s_b_grad);
 }
 

@@ -152,12 +152,14 @@ int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* i
 // ------------------------------------------------------------------------------------------------
 __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, int ipc, FwdWork* __restrict__ work, int* __restrict__ n_work) {
     // n_keys = slices + 1 (the last key collects items without a usable first index)
-    __shared__ int s_base[SORT_KEYS_MAX + 1];
+    __shared__ int s_base[SORT_KEYS_MAX + 1], s_seg[SORT_KEYS_MAX + 2];
+    for (int k = threadIdx.x; k <= n_keys; k += blockDim.x) s_seg[k] = item_seg[k];  // one round trip, not n_keys
+    __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
         for (int k = 0; k < n_keys; ++k) {
             s_base[k] = run;
-            run += (item_seg[k + 1] - item_seg[k] + ipc - 1) / ipc;
+            run += (s_seg[k + 1] - s_seg[k] + ipc - 1) / ipc;
         }
         s_base[n_keys] = run;
         n_work[0] = run;

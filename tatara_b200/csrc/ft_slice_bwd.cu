@@ -42,6 +42,8 @@ static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
     for (int c = 32; c <= 4096; c += 32) {
         if (bwd_smem_bytes(c, rps, A_pad) > 227 * 1024) break;
         if ((size_t)c * A_pad + 8 * (size_t)rps > 65535) break;
+        // k_inv_chunk: histograms, offsets and sort keys, the chunk's lists
+        if ((size_t)64 * ((rps + 1) & ~1) + (size_t)INV_SORT_N * 8 + ((size_t)c * A_pad + 8 * (size_t)rps) * 2 > 227 * 1024) break;
         CH = c;
     }
     L.CH = CH;
@@ -68,12 +70,14 @@ size_t ft_backward_slice_ints(int n_items, int A, int rps) { return bwd_layout(n
 // chunks of <= ipc consecutive slots of one slice; first[k] = index of slice k's first chunk, first[n_keys] = total
 __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int ipc, FwdWork* __restrict__ work,
                              int* __restrict__ n_work, int* __restrict__ first) {
-    __shared__ int s_base[SORT_KEYS_LIMIT + 1];
+    __shared__ int s_base[SORT_KEYS_LIMIT + 1], s_seg[SORT_KEYS_LIMIT + 2];
+    for (int k = threadIdx.x; k <= n_keys; k += blockDim.x) s_seg[k] = item_seg[k];  // one round trip, not n_keys
+    __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
         for (int k = 0; k < n_keys; ++k) {
             s_base[k] = run;
-            run += (item_seg[k + 1] - item_seg[k] + ipc - 1) / ipc;
+            run += (s_seg[k + 1] - s_seg[k] + ipc - 1) / ipc;
         }
         s_base[n_keys] = run;
         *n_work = run;
@@ -96,7 +100,7 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
 }
 
 // Inverse index of one chunk.  Shared memory: hist [32 warps][rps_h] 16-bit cells, rowoff [rps] ints, sort keys
-// [INV_SORT_N] ints, the chunk's row codes [CH][A_pad].  Warp w owns a contiguous range of the chunk's slots, so "warp, then step, then lane" is
+// [INV_SORT_N] ints, the chunk's lists [region] 16-bit cells (copied out at the end in 16-byte pieces).  Warp w owns a contiguous range of the chunk's slots, so "warp, then step, then lane" is
 // ascending slot order and the ranked scatter is stable.
 // rowinfo (sorted by descending list length, so that the eight-lane groups of a warp get lists of similar length
 // and the long lists start first): row << 32 | list offset << 16 | list length; lists are padded to a multiple of
@@ -114,23 +118,17 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
     unsigned short* s_hist = reinterpret_cast<unsigned short*>(s_raw);                    // [32][rps_h]
     int* s_rowoff = reinterpret_cast<int*>(s_raw + (size_t)32 * rps_h * 2);               // [rps]
     unsigned* s_keys = reinterpret_cast<unsigned*>(s_rowoff + INV_SORT_N);                // [INV_SORT_N]
-    unsigned short* s_codes = reinterpret_cast<unsigned short*>(s_keys + INV_SORT_N);     // [CH][A_pad]
-    __shared__ int s_warp[32];
+    unsigned short* s_lists = reinterpret_cast<unsigned short*>(s_keys + INV_SORT_N);     // [region]: the chunk's lists
+    __shared__ int s_warp[32], s_total;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int n = wk.end - wk.begin;
-    {   // the chunk's codes: n * A_pad cells, a multiple of 16 bytes from a 16-byte aligned start
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(codes + (size_t)wk.begin * A_pad);
-        for (int e = tid; e < n * A_pad / 8; e += 1024) cp_async16(reinterpret_cast<unsigned char*>(s_codes) + (size_t)e * 16, src + (size_t)e * 16, 16);
-        cp_async_commit();
-    }
     for (int e = tid; e < 16 * rps_h; e += 1024) reinterpret_cast<unsigned*>(s_hist)[e] = 0u;
-    cp_async_wait<0>();
     __syncthreads();
 
     const int per = (n + 31) >> 5;
     const int s0 = min(n, w * per), s1 = min(n, s0 + per);
     const int n_e = (s1 - s0) * A_pad;
-    const unsigned short* cw = s_codes + (size_t)s0 * A_pad;
+    const unsigned short* cw = codes + (size_t)(wk.begin + s0) * A_pad;  // the warp's cells, consecutive in global memory
     unsigned short* my_hist = s_hist + (size_t)w * rps_h;
 
     // pass 1: per-warp histogram (two 16-bit cells per shared-memory word, bumped by 32-bit atomics; a cell never
@@ -177,7 +175,7 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
         s_warp[lane] = ti - t;
     }
     __syncthreads();
-    unsigned short* my_lists = lists + (size_t)blockIdx.x * region;
+    unsigned short* my_lists = s_lists;
     int base = s_warp[w] + incl - padded;
     for (int u = 0; u < rpt; ++u) {
         const int r = tid * rpt + u;
@@ -188,7 +186,7 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
             base = pe;
         }
     }
-    if (tid == 1023) len[blockIdx.x] = base;
+    if (tid == 1023) { len[blockIdx.x] = base; s_total = base; }
     // sort keys: ascending (65535 - length) << 11 | row, unused cells last
     for (int i = tid; i < INV_SORT_N; i += 1024) s_keys[i] = 0xFFFFFFFFu;
     __syncthreads();
@@ -222,9 +220,23 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
     // take the slot's cells; the atomic's return value is the cell's rank inside the row's list.  Slots are visited in
     // ascending order, so every list comes out ascending (two cells of one slot carry the same value: their order is
     // immaterial).
+    // (A_pad <= 64: a lane holds at most two cells of a slot; the next slot's cells are fetched while this one is placed)
+    const int q1 = lane + 32;
+    unsigned c0 = 0xFFFFu, c1 = 0xFFFFu;
+    if (s0 < s1) {
+        c0 = lane < A_pad ? cw[lane] : 0xFFFFu;
+        c1 = q1 < A_pad ? cw[q1] : 0xFFFFu;
+    }
     for (int sl = s0; sl < s1; ++sl) {
-        for (int q = lane; q < A_pad; q += 32) {
-            const unsigned code = s_codes[(size_t)sl * A_pad + q];
+        unsigned n0 = 0xFFFFu, n1 = 0xFFFFu;
+        if (sl + 1 < s1) {
+            const unsigned short* nx = cw + (size_t)(sl + 1 - s0) * A_pad;
+            n0 = lane < A_pad ? nx[lane] : 0xFFFFu;
+            n1 = q1 < A_pad ? nx[q1] : 0xFFFFu;
+        }
+#pragma unroll
+        for (int hq = 0; hq < 2; ++hq) {
+            const unsigned code = hq ? c1 : c0;
             if (code < (unsigned)rps) {
                 const unsigned sh = (code & 1u) * 16u;
                 const unsigned old = atomicAdd(my_hist32 + (code >> 1), 1u << sh);
@@ -232,6 +244,15 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
             }
         }
         __syncwarp();
+        c0 = n0; c1 = n1;
+    }
+    __syncthreads();
+    // the finished lists leave in 16-byte pieces (the total length is a multiple of eight cells)
+    {
+        const int total = s_total;
+        uint4* dst = reinterpret_cast<uint4*>(lists + (size_t)blockIdx.x * region);
+        const uint4* src = reinterpret_cast<const uint4*>(s_lists);
+        for (int e = tid; e < total / 8; e += 1024) dst[e] = src[e];
     }
 }
 
@@ -425,7 +446,7 @@ int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int
     const BwdPointers P = bwd_pointers(bwd_work, L);
     k_chunk_plan<<<1, 128, 0, s>>>(item_seg, n_keys, L.CH, P.chunks, P.n_chunks, P.first);
     const int rps_h = (rps + 1) & ~1;
-    const size_t inv_smem = (size_t)32 * rps_h * 2 + (size_t)INV_SORT_N * 4 * 2 + (size_t)L.CH * A_pad * 2;
+    const size_t inv_smem = (size_t)32 * rps_h * 2 + (size_t)INV_SORT_N * 4 * 2 + (size_t)L.region * 2;
     cudaFuncSetAttribute(k_inv_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)inv_smem);
     k_inv_chunk<<<L.max_chunks, 1024, inv_smem, s>>>(reinterpret_cast<const unsigned short*>(sb.codes), P.chunks, P.n_chunks,
                                                      sb.outside_flag, n_slices, A_pad, rps, L.rps_pad, L.CH, L.region, P.lists,

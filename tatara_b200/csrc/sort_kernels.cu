@@ -112,13 +112,15 @@ __global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, in
 __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_start, int K, TileDesc* __restrict__ tiles,
                                                      int* __restrict__ n_tiles, TileDesc* __restrict__ units,
                                                      int* __restrict__ n_units) {
-    __shared__ int s_tile_base[SORT_MAX_KEYS + 1], s_unit_base[SORT_MAX_KEYS + 1];
+    __shared__ int s_tile_base[SORT_MAX_KEYS + 1], s_unit_base[SORT_MAX_KEYS + 1], s_seg[SORT_MAX_KEYS + 2];
+    for (int k = threadIdx.x; k <= K; k += blockDim.x) s_seg[k] = seg_start[k];  // one round trip, not K
+    __syncthreads();
     if (threadIdx.x == 0) {
         int trun = 0, urun = 0;
         for (int k = 0; k < K; ++k) {
             s_tile_base[k] = trun;
             s_unit_base[k] = urun;
-            const int nt = (seg_start[k + 1] - seg_start[k] + TB_TILE_M - 1) / TB_TILE_M;
+            const int nt = (s_seg[k + 1] - s_seg[k] + TB_TILE_M - 1) / TB_TILE_M;
             trun += nt;
             urun += (nt + TB_UNIT_TILES - 1) / TB_UNIT_TILES;
         }

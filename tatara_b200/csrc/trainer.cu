@@ -668,7 +668,7 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->order, B)); CU(t, dalloc(&t->n_tiles, 2)); CU(t, dalloc(&t->seg_start, TB_MAX_BUCKETS + 3));
     CU(t, dalloc(&t->tiles, (size_t)t->max_tiles + t->max_units));
     const size_t n_cells = ls ? (size_t)(l2 * t->l2in + 2 * l2 + 1 + l1) : (size_t)(l1 * l2 + 2 * l2 + 1 + l1);
-    CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 16 : (size_t)128) * n_cells));
+    CU(t, dalloc(&t->small_partials, (ls ? (size_t)(nb + 1) * 64 : (size_t)128) * n_cells));  // SW_SPLIT_LS partial rows per segment
     CU(t, dalloc(&t->l1w_partials, ((size_t)t->max_units + 1) * l1 * t->K));
     CU(t, dalloc(&t->l1_weff, (size_t)(nb + 1) * l1 * (t->K + 1)));  // effective L1 weights and biases per bucket
     t->dgrad_rows = DGRAD_CTAS > 2 * t->max_units ? DGRAD_CTAS : 2 * t->max_units;  // partial FT bias rows: one per block
