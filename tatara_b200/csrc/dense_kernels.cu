@@ -1043,73 +1043,9 @@ __global__ void __launch_bounds__(256) k_l1_wgrad_shared(const float* __restrict
 
 // Variant for l1 % 8 == 0: a thread owns four adjacent columns and OPT outputs (OPT = 8 or 16; two thread groups
 // split the outputs when l1 = 32), so that one 128-bit load of x feeds 4 * OPT multiply-adds and the dl1 values
-// come as broadcast 128-bit shared-memory loads.
-template <int OPT>
-__global__ void __launch_bounds__(256) k_l1_wgrad_v4(const float* __restrict__ x, int K, const float* __restrict__ dl1,
-                                                      const int* __restrict__ order, const TileDesc* __restrict__ tiles,
-                                                      const TileDesc* __restrict__ units, const int* __restrict__ n_units, int l1,
-                                                      float* __restrict__ partials) {
-    const int u = blockIdx.y;
-    if (u >= *n_units) return;
-    const TileDesc ud = units[u];
-    __shared__ __align__(16) float sdl[TB_TILE_M][TB_MAX_L1];
-    __shared__ int s_pos[TB_TILE_M];
-    const int K4 = K >> 2;
-    const int tcol = threadIdx.x & 127, og = threadIdx.x >> 7;
-    const int col4 = blockIdx.x * 128 + tcol;
-    const bool active = col4 < K4;
-    const float4* __restrict__ x4 = reinterpret_cast<const float4*>(x);
-    float4 acc[OPT];
-#pragma unroll
-    for (int j = 0; j < OPT; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int t = ud.start; t < ud.start + ud.count; ++t) {
-        const TileDesc td = tiles[t];
-        __syncthreads();
-        for (int i = threadIdx.x; i < TB_TILE_M; i += blockDim.x) s_pos[i] = i < td.count ? order[td.start + i] : -1;
-        __syncthreads();
-        for (int e = threadIdx.x; e < TB_TILE_M * l1; e += blockDim.x) {
-            const int r = e / l1, o = e - r * l1;
-            const int p = s_pos[r];
-            sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
-        }
-        __syncthreads();
-        if (!active) continue;
-        for (int r0 = 0; r0 < td.count; r0 += 4) {
-            float4 xv[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int p = r0 + q < td.count ? s_pos[r0 + q] : -1;
-                xv[q] = p >= 0 ? __ldg(x4 + (size_t)p * K4 + col4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                if (r0 + q >= td.count) break;
-#pragma unroll
-                for (int j4 = 0; j4 < OPT / 4; ++j4) {
-                    const float4 g = *reinterpret_cast<const float4*>(&sdl[r0 + q][og * OPT + 4 * j4]);
-                    const float gv[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        acc[4 * j4 + j].x += gv[j] * xv[q].x;
-                        acc[4 * j4 + j].y += gv[j] * xv[q].y;
-                        acc[4 * j4 + j].z += gv[j] * xv[q].z;
-                        acc[4 * j4 + j].w += gv[j] * xv[q].w;
-                    }
-                }
-            }
-        }
-    }
-    if (!active) return;
-#pragma unroll
-    for (int j = 0; j < OPT; ++j) {
-        const int o = og * OPT + j;
-        reinterpret_cast<float4*>(partials + ((size_t)u * l1 + o) * K)[col4] = acc[j];
-    }
-}
-
-// Streaming form of the kernel above: the unit's positions (consecutive in the bucket order) and their dl1 rows are
-// staged once, then the x rows arrive through a private ring of asynchronous copies (a thread copies the 16 bytes it
-// reads itself), WG_STAGES rounds of four positions ahead of the arithmetic.
+// come as broadcast 128-bit shared-memory loads.  The unit's positions (consecutive in the bucket order) and their dl1
+// rows are staged once, then the x rows arrive through a private ring of asynchronous copies (a thread copies the 16
+// bytes it reads itself), WG_STAGES rounds of four positions ahead of the arithmetic.
 #define WG_POS (TB_UNIT_TILES * TB_TILE_M)
 #define WG_STAGES 3
 template <int OPT>
@@ -1228,7 +1164,7 @@ int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, con
 // grid (n_ctas, 2 perspectives, column chunks); a block walks the tiles t = blockIdx.x, += gridDim.x and
 // keeps the effective weights of the current bucket in shared memory.
 // ------------------------------------------------------------------------------------------------
-template <int MODE, bool PF>
+template <int MODE>
 __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict__ dl1, const int* __restrict__ order,
                                                           const TileDesc* __restrict__ tiles, const int* __restrict__ n_tiles,
                                                           const float* __restrict__ wb, const float* __restrict__ ws,
@@ -1276,39 +1212,15 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
             sdl[r][o] = p >= 0 ? dl1[(size_t)p * l1 + o] : 0.f;
         }
         __syncthreads();
-        // PF: the pre-activations of the next two positions are requested before the current two are processed
-        float4 xa_n[2], xb_n[2];
-        int pp_n[2];
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            pp_n[q] = -1;
-            xa_n[q] = xb_n[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (PF) {
-                pp_n[q] = q < td.count ? s_pos[q] : -1;
-                if (pp_n[q] >= 0) {
-                    xa_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol);
-                    if (MODE == 1) xb_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol);
-                }
-            }
-        }
         for (int r0 = 0; r0 < td.count; r0 += 2) {
             float4 xa[2], xb[2];
             int pp[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-                if (PF) {
-                    xa[q] = xa_n[q]; xb[q] = xb_n[q]; pp[q] = pp_n[q];
-                    pp_n[q] = r0 + 2 + q < td.count ? s_pos[r0 + 2 + q] : -1;
-                    if (pp_n[q] >= 0) {
-                        xa_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + wcol);
-                        if (MODE == 1) xb_n[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp_n[q] * F + half + wcol);
-                    }
-                } else {
-                    pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
-                    if (pp[q] >= 0) {
-                        xa[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + wcol);
-                        if (MODE == 1) xb[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + half + wcol);
-                    }
+                pp[q] = r0 + q < td.count ? s_pos[r0 + q] : -1;
+                if (pp[q] >= 0) {
+                    xa[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + wcol);
+                    if (MODE == 1) xb[q] = *reinterpret_cast<const float4*>(pre + (size_t)pp[q] * F + half + wcol);
                 }
             }
             float4 dd[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
@@ -1590,8 +1502,8 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
         dim3 grid(n_ctas, 2, n_chunks), block(CW / 4);
 #define DGRAD_LAUNCH(M)                                                                                                  \
     do {                                                                                                                 \
-        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<M, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);       \
-        k_l1_dgrad_ftgrad<M, false><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, \
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);       \
+        k_l1_dgrad_ftgrad<M><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, \
                                                          scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);        \
     } while (0)
         if (mode == 1) DGRAD_LAUNCH(1);

@@ -439,3 +439,37 @@ def test_ft_slice_backward_many_chunks_bit_exact(outside):
     assert short.sum() > 1000 and (~short).sum() >= 4
     assert np.array_equal(got[short].view(np.uint32), want[short].view(np.uint32))
     assert_close_scaled(got[~short], want[~short], 1e-6, "long lists")
+
+
+def test_config3_full_size_step_matches_oracle():
+    """The benchmark's own shapes (LayerStack F=1536, l1=16, l2=32, halfka-hm-merged, B = 65 536, factorizer on): one
+    forward/backward and one Ranger step against the oracle.  About 8 GB of host memory and 20 s of CPU time."""
+    F, l1, l2, B, nb = 1536, 16, 32, 65536, 9
+    fs = LS_FS
+    rng = np.random.default_rng(65536)
+    init = _perturb(tb.layerstack_default_init(fs, F, l1, l2, nb), rng, ["ft_b", "l1_b", "l1_shared_bias", "l2_b", "l3_b"])
+    init["ft_w"][:fs.ft_in * F] *= 30.0
+    init["ft_w"][fs.ft_in * F:] = (rng.standard_normal(fs.piece_inputs * F) * 0.02).astype(np.float32)
+    tr = tb.GpuTrainer(B, F, l1, l2, nb, fs, optimizer="ranger", init=init)
+    ot = _oracle_for(tr, "layerstack", fs, F, l1, l2, nb, "ranger", (0.01, 0.01, 0.01), B)
+    _sync_weights(tr, ot, init)
+    batch = tb.synthetic_batch(tb.SYNTH_SEED + 3, B, fs)
+    lr = 8.75e-4
+    l_gpu = tr.forward_backward(batch, 0.0, tb.LossKind.sigmoid(1.0 / 290.0))
+    l_cpu = ot.step(_batch_dict(batch), lr, 0.0, O.sigmoid_loss(1.0 / 290.0), do_optimizer=False)
+    for name in ("ft_stm", "ft_nstm"):
+        assert np.array_equal(tr.read_buffer(name, B * F).view(np.uint32), ot.buffer(name).view(np.uint32)), name
+    assert_close(tr.read_buffer("net_output", B), ot.buffer("net_output"), TOL_FWD, "net_output")
+    assert abs(l_gpu - l_cpu) <= TOL_FWD * (1 + abs(l_cpu)), (l_gpu, l_cpu)
+    assert_close_scaled(tr.read_buffer("dft_stm", B * F), ot.buffer("dft_stm"), TOL_GRAD, "dft_stm")
+    for name in ot.names:
+        assert_close_scaled(tr.download_grad(name), ot.group(name, "grad"), TOL_GRAD, "grad " + name)
+    tr.apply_optimizer(lr); ot.apply_optimizer(lr)
+    for name in ot.names:
+        got = tr.download_group(name, ("w", "m", "v"))
+        assert_close(got["w"], ot.group(name, "w"), TOL_FWD, "w " + name)
+        assert_close_scaled(got["m"], ot.group(name, "m"), TOL_GRAD, "m " + name)
+        assert_close_scaled(got["v"], ot.group(name, "v"), TOL_GRAD, "v " + name)
+    w = ot.group("ft_w")
+    want_comb = (w[:fs.ft_in * F].reshape(-1, fs.piece_inputs, F) + w[fs.ft_in * F:].reshape(1, fs.piece_inputs, F)).reshape(-1)
+    assert_close(tr.read_buffer("comb", fs.ft_in * F), want_comb, TOL_FWD, "comb")
