@@ -142,7 +142,7 @@ def make_trainer(tb, w, device, world, rank, nccl_id, capacity=BATCH):
     return tr, loss, fs
 
 
-def run_cpu(w, wname, threads, sample_b, steps, warmup, budget_s=None):
+def run_cpu(w, wname, threads, sample_b, steps, warmup, limit_s=None):
     """Times the oracle's whole step on `sample_b` synthetic positions; returns (pos/s, steps done, ms/step)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as O
@@ -166,7 +166,7 @@ def run_cpu(w, wname, threads, sample_b, steps, warmup, budget_s=None):
     for _ in range(steps):
         ot.step(batch, LR, 0.0, loss)
         done += 1
-        if budget_s is not None and time.time() - t0 > budget_s:
+        if limit_s is not None and time.time() - t0 > limit_s:
             break
     dt = time.time() - t0
     return sample_b * done / dt, done, dt / done * 1e3
@@ -193,7 +193,7 @@ def main():
         if rank != 0:
             return
         sample_b = 4096
-        value, done, ms = run_cpu(w, args.workload, threads, sample_b, K, min(Wm, 1), budget_s=150.0)
+        value, done, ms = run_cpu(w, args.workload, threads, sample_b, K, min(Wm, 1), limit_s=150.0)
         line = {"impl": "reference", "metric": "train_positions_per_second", "value": value, "unit": "pos/s", "n_gpus": 0,
                 "steps": done, "warmup": min(Wm, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -317,7 +317,7 @@ def main():
         }
         if world == 1 and not args.no_cpu_baseline:
             tr.close()
-            v, done, cms = run_cpu(w, args.workload, threads, 4096, 3, 1, budget_s=25.0)
+            v, done, cms = run_cpu(w, args.workload, threads, 4096, 3, 1, limit_s=25.0)
             line["cpu_baseline"] = {"value": v, "unit": "pos/s", "cores": threads, "kind": "port",
                                     "sample": "%d steps of 4096 synthetic positions on the CPU restatement of the reference step (%.0f ms/step)" % (done, cms)}
         print(json.dumps(line), flush=True)

@@ -118,7 +118,9 @@ def features(stm, bk, wk, board, hands, merged_hm):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
+    ref = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     raw = open(os.path.join(ref, "crates/shogi-format/tests/data/sample.psv"), "rb").read()
     assert len(raw) == 4000
