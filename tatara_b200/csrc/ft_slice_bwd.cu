@@ -21,6 +21,7 @@
 
 #define INV_SORT_N 2048  // rows per slice limit (bitonic sort size)
 #define BWD_HOT 256      // list length from which a list is summed by a warp of its own
+#define BWD_DESC 64      // chunk descriptors a block stages in shared memory
 
 struct BwdLayout {
     int CH;             // slots per chunk (multiple of 32)
@@ -40,10 +41,10 @@ static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
     const int A_pad = slice_a_pad(A);
     int CH = 0;
     for (int c = 32; c <= 4096; c += 32) {
-        if (bwd_smem_bytes(c, rps, A_pad) > 227 * 1024) break;
+        if (bwd_smem_bytes(c, rps, A_pad) + 2048 > 227 * 1024) break;  // 2 KB stay free for the kernels' static arrays
         if ((size_t)c * A_pad + 8 * (size_t)rps > 65535) break;
         // k_inv_chunk: histograms, offsets and sort keys, the chunk's lists
-        if ((size_t)64 * ((rps + 1) & ~1) + (size_t)INV_SORT_N * 8 + ((size_t)c * A_pad + 8 * (size_t)rps) * 2 > 227 * 1024) break;
+        if ((size_t)64 * ((rps + 1) & ~1) + (size_t)INV_SORT_N * 8 + ((size_t)c * A_pad + 8 * (size_t)rps) * 2 + 2048 > 227 * 1024) break;
         CH = c;
     }
     L.CH = CH;
@@ -52,7 +53,7 @@ static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
     L.max_chunks = CH > 0 ? n_items / CH + SORT_KEYS_LIMIT + 2 : 0;
     size_t o = 4 * (size_t)L.max_chunks + 4;            // chunk records + their count
     L.off_first = o; o += SORT_KEYS_LIMIT + 4;          // first chunk of every slice (+ end)
-    L.off_len = o; o += ((size_t)L.max_chunks + 3) / 4 * 4;
+    L.off_len = o; o += 4 * (size_t)L.max_chunks;  // per chunk {list cells, long-list records, non-empty records, 0}
     L.off_rowinfo = o; o += 2 * (size_t)L.max_chunks * L.rps_pad;
     L.off_lists = o; o += ((size_t)L.max_chunks * L.region + 1) / 2 + 4;
     L.total_ints = o;
@@ -186,7 +187,8 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
             base = pe;
         }
     }
-    if (tid == 1023) { len[blockIdx.x] = base; s_total = base; }
+    if (tid == 1023) { len[4 * blockIdx.x] = base; s_total = base; }
+    if (tid == 0) { len[4 * blockIdx.x + 1] = 0; len[4 * blockIdx.x + 2] = 0; len[4 * blockIdx.x + 3] = 0; }
     // sort keys: ascending (65535 - length) << 11 | row, unused cells last
     for (int i = tid; i < INV_SORT_N; i += 1024) s_keys[i] = 0xFFFFFFFFu;
     __syncthreads();
@@ -204,6 +206,13 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
             if ((a > b) == up) { s_keys[i] = b; s_keys[p] = a; }
             __syncthreads();
         }
+    }
+    // the sorted order starts with the long lists and ends with the empty ones: where each group ends
+    for (int i = tid; i < rps; i += 1024) {
+        const int ci = 65535 - (int)(s_keys[i] >> 11);
+        const int cn = i + 1 < rps ? 65535 - (int)(s_keys[i + 1] >> 11) : -1;
+        if (ci >= BWD_HOT && cn < BWD_HOT) len[4 * blockIdx.x + 1] = i + 1;
+        if (ci > 0 && cn <= 0) len[4 * blockIdx.x + 2] = i + 1;
     }
     unsigned long long* my_info = rowinfo + (size_t)blockIdx.x * rps_pad;
     for (int i = tid; i < rps_pad; i += 1024) {
@@ -268,6 +277,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
     // dft strip [CH + 1][32] floats (the last row stays zero), row records [rps_pad] 64-bit, list cells [region] 16-bit
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ int s_ctl[4];
+    __shared__ int s_desc[BWD_DESC][5];
     if (*outside_flag) return;
     const int k = slice_begin + blockIdx.x, strip = blockIdx.y;
     const int row0 = k * rps;
@@ -287,49 +297,58 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
     if (tid < 32) reinterpret_cast<float*>(s_dft)[CH * 32 + tid] = 0.f;
     const unsigned char* s_lane = s_dft + 16 * j;
 
+    // the slice's chunk descriptors, fetched once (BWD_DESC at most; a slice with more chunks reads the rest as it goes)
+    for (int i = tid; i < min(c_end - c_first, BWD_DESC); i += 1024) {
+        const FwdWork wk = work[c_first + i];
+        s_desc[i][0] = wk.begin; s_desc[i][1] = wk.end;
+        s_desc[i][2] = len[4 * (c_first + i)]; s_desc[i][3] = len[4 * (c_first + i) + 1]; s_desc[i][4] = len[4 * (c_first + i) + 2];
+    }
+    __syncthreads();
     for (int c = c_first; c < c_end; ++c) {
-        const FwdWork wk = work[c];
-        const int n = wk.end - wk.begin;
-        const int L = len[c];
+        const int ci = c - c_first;
+        const int wk_begin = ci < BWD_DESC ? s_desc[ci][0] : work[c].begin;
+        const int wk_end = ci < BWD_DESC ? s_desc[ci][1] : work[c].end;
+        const int n = wk_end - wk_begin;
+        const int L = ci < BWD_DESC ? s_desc[ci][2] : len[4 * c];
+        const int n_hot = ci < BWD_DESC ? s_desc[ci][3] : len[4 * c + 1];
+        const int n_live = ci < BWD_DESC ? s_desc[ci][4] : len[4 * c + 2];
         __syncthreads();  // the previous chunk's sums are done with the buffers (and its gradient rows are written)
-        for (int e = tid; e < n * 8; e += 1024) {  // thread e & 7 == j copies the 16 bytes of row e >> 3 it will read
-            const int it = __ldg(info + wk.begin + (e >> 3)) & ~SLICE_SLOW_BIT;
-            const int p = it >= B, b = it - p * B;
-            cp_async16(s_dft + (size_t)e * 16, (p ? dft_nstm : dft_stm) + (size_t)b * F + col, 16);
-        }
         {
             const unsigned char* src = reinterpret_cast<const unsigned char*>(rowinfo + (size_t)c * rps_pad);
             for (int e = tid; e < rps_pad / 2; e += 1024) cp_async16(reinterpret_cast<unsigned char*>(s_info) + (size_t)e * 16, src + (size_t)e * 16, 16);
             const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(lists + (size_t)c * region);
             for (int e = tid; e < L / 8; e += 1024) cp_async16(s_lists + (size_t)e * 16, lsrc + (size_t)e * 16, 16);
         }
+        // dft rows: thread e & 7 == j copies the 16 bytes of row e >> 3 it will read.  The item numbers the addresses
+        // depend on are fetched eight at a time before the copies, so that the copies go out back to back.
+        for (int e0 = tid; e0 < n * 8; e0 += 8 * 1024) {
+            int itv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = e0 + u * 1024;
+                itv[u] = e < n * 8 ? __ldg(info + wk_begin + (e >> 3)) : 0;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = e0 + u * 1024;
+                if (e < n * 8) {
+                    const int it = itv[u] & ~SLICE_SLOW_BIT;
+                    const int p = it >= B, b = it - p * B;
+                    cp_async16(s_dft + (size_t)e * 16, (p ? dft_nstm : dft_stm) + (size_t)b * F + col, 16);
+                }
+            }
+        }
+        if (tid == 0) s_ctl[1] = n_hot;  // the counter the records behind the long lists are handed out from
         cp_async_commit();
         cp_async_wait<0>();
         __syncthreads();
 
         const bool first_chunk = c == c_first;
-        // The records are sorted by descending list length.  A list of BWD_HOT entries or more gets a warp of its own
-        // (one eight-lane group works, the other three wait): a warp's share of the shared-memory pipe does not
-        // depend on how many of its lanes are active, so the long sequential sums run four times faster than they
-        // would next to three other lists and end with the rest of the chunk instead of after it.  All other records
-        // are handed out four at a time (neighbours in the order, so of similar length) from a block-wide counter.
-        if (tid == 0) {
-            int lo = 0, hi = rps;  // first record with fewer than BWD_HOT entries
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if ((int)(s_info[mid] & 0xffffu) >= BWD_HOT) lo = mid + 1; else hi = mid;
-            }
-            s_ctl[0] = lo;
-            s_ctl[1] = lo;
-            int lo2 = lo; hi = rps;  // first record without entries
-            while (lo2 < hi) {
-                const int mid = (lo2 + hi) >> 1;
-                if ((int)(s_info[mid] & 0xffffu) > 0) lo2 = mid + 1; else hi = mid;
-            }
-            s_ctl[2] = first_chunk ? rps : lo2;
-        }
-        __syncthreads();
-        const int n_hot = s_ctl[0], n_rec = s_ctl[2];
+        // The records are sorted by descending list length.  A list of BWD_HOT entries or more gets a warp of its own,
+        // whose four groups sum a quarter of it each: left to one group, its long chain of dependent additions would end
+        // after the rest of the chunk.  All other records are handed out four at a time (neighbours in the order, so of
+        // similar length) from a block-wide counter.
+        const int n_rec = first_chunk ? rps : n_live;
         // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 8
         auto sum_range = [&](const unsigned char* lp, int beg, int end, unsigned long long& a0, unsigned long long& a1) {
             const int full = beg + ((end - beg) & ~7);
