@@ -1009,23 +1009,26 @@ __global__ void __launch_bounds__(256) k_l1_wgrad_final(const float* __restrict_
                                                          float* __restrict__ gw_bucket, float* __restrict__ rest) {
     __shared__ int s_range[2];
     const int g = blockIdx.y;
-    if (threadIdx.x == 0) {
-        const int nu = *n_units;
-        int first = nu, last = nu;
-        for (int u = 0; u < nu; ++u) {
-            const int bk = units[u].bucket;
-            if (bk == g && first == nu) first = u;
-            if (bk > g) { last = u; break; }
-        }
-        if (first == nu) last = nu;
-        s_range[0] = first;
-        s_range[1] = last;
+    const int nu = *n_units;
+    if (threadIdx.x == 0) { s_range[0] = nu; s_range[1] = nu; }
+    __syncthreads();
+    for (int u = threadIdx.x; u < nu; u += blockDim.x) {  // first unit of bucket g, first unit of a later bucket
+        const int bk = units[u].bucket;
+        if (bk == g) atomicMin(&s_range[0], u);
+        if (bk > g) atomicMin(&s_range[1], u);
     }
     __syncthreads();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= l1 * K) return;
+    const int u0 = s_range[0], u1 = s_range[1];
     float sum = 0.f;
-    for (int u = s_range[0]; u < s_range[1]; ++u) sum += partials[(size_t)u * l1 * K + i];
+    int u = u0;
+    for (; u + 4 <= u1; u += 4) {  // four loads in flight, added in unit order
+        const float a = partials[(size_t)u * l1 * K + i], b = partials[(size_t)(u + 1) * l1 * K + i];
+        const float c = partials[(size_t)(u + 2) * l1 * K + i], d = partials[(size_t)(u + 3) * l1 * K + i];
+        sum += a; sum += b; sum += c; sum += d;
+    }
+    for (; u < u1; ++u) sum += partials[(size_t)u * l1 * K + i];
     if (g < nb) gw_bucket[(size_t)g * l1 * K + i] = sum;
     else rest[i] = sum;
 }

@@ -103,8 +103,10 @@ int launch_radam_small(cudaStream_t s, const SmallGroups& groups, int max_n, Opt
 //   pass 2: comb[kb*pi + v] = w[kb*pi + v] + w[N + v] (ft_fold_virtual, sparse/ft_factorize.rs:78-99);
 //           the real rows were written a moment ago by this block and are read back from L2.
 // Replaces radam_step on N_t*F elements + ft_reduce_virtual_grad + ranger_lookahead_lerp + ft_fold_virtual.
+// Two builds: rows of up to 384 float4 (F <= 1536) run three blocks per SM (56 registers), longer rows one or two.
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) k_radam_factorized(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v,
+template <int MAX_THREADS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) k_radam_factorized(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v,
                                                             float4* __restrict__ g, float4* __restrict__ slow,
                                                             float4* __restrict__ comb, int N, int pi, int row4, OptScalars sc) {
     const int vr = blockIdx.x;
@@ -151,8 +153,9 @@ __global__ void __launch_bounds__(1024) k_radam_factorized(float4* __restrict__ 
 
 int launch_radam_factorized(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb, int N,
                             int pi, int F, OptScalars sc) {
-    k_radam_factorized<<<pi, F / 4, 0, s>>>(reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m),
-                                            reinterpret_cast<float4*>(v), reinterpret_cast<float4*>(g),
-                                            reinterpret_cast<float4*>(slow), reinterpret_cast<float4*>(comb), N, pi, F / 4, sc);
+    float4 *w4 = reinterpret_cast<float4*>(w), *m4 = reinterpret_cast<float4*>(m), *v4 = reinterpret_cast<float4*>(v);
+    float4 *g4 = reinterpret_cast<float4*>(g), *s4 = reinterpret_cast<float4*>(slow), *c4 = reinterpret_cast<float4*>(comb);
+    if (F / 4 <= 384) k_radam_factorized<384, 3><<<pi, F / 4, 0, s>>>(w4, m4, v4, g4, s4, c4, N, pi, F / 4, sc);
+    else k_radam_factorized<1024, 1><<<pi, F / 4, 0, s>>>(w4, m4, v4, g4, s4, c4, N, pi, F / 4, sc);
     return 1;
 }
