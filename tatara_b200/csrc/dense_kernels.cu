@@ -1280,7 +1280,7 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
     if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
 }
 
-// Streaming variant for l1 = 8 or 16.  A thread keeps the effective weights of its four columns ([L1] float4) in
+// Streaming variant for l1 = 8, 16 or 32.  A thread keeps the effective weights of its four columns ([L1] float4) in
 // registers, so a position costs L1 / 4 broadcast loads of its dl1 row from shared memory and 4 * L1 multiply-adds:
 // the shared-memory pipe is not the limit.  A block owns half a work unit (<= DG_POS consecutive positions of the
 // bucket order, one bucket) and one perspective; the pre-activations arrive through a private ring of asynchronous
@@ -1480,7 +1480,7 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
     const int work_cols = mode == 1 ? F / 2 : F;
     const int max_units = sort_max_units(max_tiles);
     int bias_rows = n_ctas;
-    if ((l1 == 8 || l1 == 16) && n_ctas >= 2 * max_units) {
+    if ((l1 == 8 || l1 == 16 || l1 == 32) && n_ctas >= 2 * max_units) {
         int n_chunks = 1;
         while (work_cols / n_chunks > 1024 || (work_cols / n_chunks) % 128 != 0 && (work_cols / n_chunks) > 256) n_chunks *= 2;
         const int CW = work_cols / n_chunks;
@@ -1494,7 +1494,8 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
                                                                  pre_nstm, ft_bias, scale, F, nb, CW, dft_stm, dft_nstm,  \
                                                                  bias_partials);                                         \
     } while (0)
-        if (l1 == 16) { if (mode == 1) DGRAD_REG(1, 16); else if (mode == 2) DGRAD_REG(2, 16); else DGRAD_REG(3, 16); }
+        if (l1 == 32) { if (mode == 1) DGRAD_REG(1, 32); else if (mode == 2) DGRAD_REG(2, 32); else DGRAD_REG(3, 32); }
+        else if (l1 == 16) { if (mode == 1) DGRAD_REG(1, 16); else if (mode == 2) DGRAD_REG(2, 16); else DGRAD_REG(3, 16); }
         else { if (mode == 1) DGRAD_REG(1, 8); else if (mode == 2) DGRAD_REG(2, 8); else DGRAD_REG(3, 8); }
 #undef DGRAD_REG
     } else {

@@ -24,32 +24,34 @@
 #define BWD_DESC 64      // chunk descriptors a block stages in shared memory
 
 struct BwdLayout {
-    int CH;             // slots per chunk (multiple of 32)
+    int CH;             // slots per chunk (multiple of 8)
     int rps_pad;        // row records per chunk
-    int region;         // 16-bit list cells per chunk (multiple of 8)
+    int region;         // 16-bit list cells per chunk (multiple of 8; every list is padded to a multiple of 4 cells)
     int max_chunks;
     size_t off_first, off_len, off_rowinfo, off_lists, total_ints;
 };
 
+static inline size_t bwd_region(int CH, int rps, int A_pad) { return ((size_t)CH * A_pad + 4 * (size_t)rps + 7) / 8 * 8; }
+
 static inline size_t bwd_smem_bytes(int CH, int rps, int A_pad) {
     const int rps_pad = (rps + 3) / 4 * 4;
-    return ((size_t)CH + 1) * 128 + (size_t)rps_pad * 8 + ((size_t)CH * A_pad + 8 * (size_t)rps) * 2;
+    return ((size_t)CH + 1) * 128 + (size_t)rps_pad * 8 + bwd_region(CH, rps, A_pad) * 2;
 }
 
 static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
     BwdLayout L;
     const int A_pad = slice_a_pad(A);
     int CH = 0;
-    for (int c = 32; c <= 4096; c += 32) {
+    for (int c = 32; c <= 4096; c += 8) {
         if (bwd_smem_bytes(c, rps, A_pad) + 2048 > 227 * 1024) break;  // 2 KB stay free for the kernels' static arrays
-        if ((size_t)c * A_pad + 8 * (size_t)rps > 65535) break;
+        if (bwd_region(c, rps, A_pad) > 65535) break;
         // k_inv_chunk: histograms, offsets and sort keys, the chunk's lists
-        if ((size_t)64 * ((rps + 1) & ~1) + (size_t)INV_SORT_N * 8 + ((size_t)c * A_pad + 8 * (size_t)rps) * 2 + 2048 > 227 * 1024) break;
+        if ((size_t)64 * ((rps + 1) & ~1) + (size_t)INV_SORT_N * 8 + bwd_region(c, rps, A_pad) * 2 + 2048 > 227 * 1024) break;
         CH = c;
     }
     L.CH = CH;
     L.rps_pad = (rps + 3) / 4 * 4;
-    L.region = CH * A_pad + 8 * rps;
+    L.region = (int)bwd_region(CH, rps, A_pad);
     L.max_chunks = CH > 0 ? n_items / CH + SORT_KEYS_LIMIT + 2 : 0;
     size_t o = 4 * (size_t)L.max_chunks + 4;            // chunk records + their count
     L.off_first = o; o += SORT_KEYS_LIMIT + 4;          // first chunk of every slice (+ end)
@@ -105,7 +107,7 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
 // ascending slot order and the ranked scatter is stable.
 // rowinfo (sorted by descending list length, so that the eight-lane groups of a warp get lists of similar length
 // and the long lists start first): row << 32 | list offset << 16 | list length; lists are padded to a multiple of
-// eight cells with the index of the chunk's row of zeros (CH).
+// four cells with the index of the chunk's row of zeros (CH).
 __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __restrict__ codes, const FwdWork* __restrict__ work,
                                                     const int* __restrict__ n_work, const int* __restrict__ outside_flag,
                                                     int n_slices, int A_pad, int rps, int rps_pad, int CH, int region,
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
                 run += c;
             }
             cnt[u] = run;
-            padded += (run + 7) & ~7;
+            padded += (run + 3) & ~3;
         }
     }
     int incl = padded;
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
         const int r = tid * rpt + u;
         if (r < rps) {
             s_rowoff[r] = base;
-            const int pe = base + ((cnt[u] + 7) & ~7);
+            const int pe = base + ((cnt[u] + 3) & ~3);
             for (int i = base + cnt[u]; i < pe; ++i) my_lists[i] = (unsigned short)CH;
             base = pe;
         }
@@ -256,12 +258,12 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
         c0 = n0; c1 = n1;
     }
     __syncthreads();
-    // the finished lists leave in 16-byte pieces (the total length is a multiple of eight cells)
+    // the finished lists leave in 16-byte pieces (the last piece may carry up to four cells nobody reads)
     {
         const int total = s_total;
         uint4* dst = reinterpret_cast<uint4*>(lists + (size_t)blockIdx.x * region);
         const uint4* src = reinterpret_cast<const uint4*>(s_lists);
-        for (int e = tid; e < total / 8; e += 1024) dst[e] = src[e];
+        for (int e = tid; e < (total + 7) / 8; e += 1024) dst[e] = src[e];
     }
 }
 
@@ -317,7 +319,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
             const unsigned char* src = reinterpret_cast<const unsigned char*>(rowinfo + (size_t)c * rps_pad);
             for (int e = tid; e < rps_pad / 2; e += 1024) cp_async16(reinterpret_cast<unsigned char*>(s_info) + (size_t)e * 16, src + (size_t)e * 16, 16);
             const unsigned char* lsrc = reinterpret_cast<const unsigned char*>(lists + (size_t)c * region);
-            for (int e = tid; e < L / 8; e += 1024) cp_async16(s_lists + (size_t)e * 16, lsrc + (size_t)e * 16, 16);
+            for (int e = tid; e < (L + 7) / 8; e += 1024) cp_async16(s_lists + (size_t)e * 16, lsrc + (size_t)e * 16, 16);
         }
         // dft rows: thread e & 7 == j copies the 16 bytes of row e >> 3 it will read.  The item numbers the addresses
         // depend on are fetched eight at a time before the copies, so that the copies go out back to back.
@@ -349,11 +351,13 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
         // after the rest of the chunk.  All other records are handed out four at a time (neighbours in the order, so of
         // similar length) from a block-wide counter.
         const int n_rec = first_chunk ? rps : n_live;
-        // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 8
+        // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 4 (lists start on
+        // 8-byte boundaries: the eight cells of a step are read as two 8-byte halves)
         auto sum_range = [&](const unsigned char* lp, int beg, int end, unsigned long long& a0, unsigned long long& a1) {
             const int full = beg + ((end - beg) & ~7);
             for (int q = beg; q < full; q += 8) {
-                const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * q);
+                const uint2 ca = *reinterpret_cast<const uint2*>(lp + 2 * q), cb = *reinterpret_cast<const uint2*>(lp + 2 * q + 8);
+                const uint4 cc = make_uint4(ca.x, ca.y, cb.x, cb.y);
                 const ulonglong2 v0 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x & 0xffffu) * 128u);
                 const ulonglong2 v1 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x >> 16) * 128u);
                 const ulonglong2 v2 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.y & 0xffffu) * 128u);
@@ -372,7 +376,8 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
             }
             if (full < end) {  // the last one to seven entries; the padding cells behind them are not read as rows
-                const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * full);
+                const uint2 ca = *reinterpret_cast<const uint2*>(lp + 2 * full), cb = *reinterpret_cast<const uint2*>(lp + 2 * full + 8);
+                const uint4 cc = make_uint4(ca.x, ca.y, cb.x, cb.y);
                 const unsigned cell[8] = {cc.x & 0xffffu, cc.x >> 16, cc.y & 0xffffu, cc.y >> 16,
                                           cc.z & 0xffffu, cc.z >> 16, cc.w & 0xffffu, cc.w >> 16};
                 const int rem = end - full;
@@ -393,7 +398,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
             const unsigned long long ri = s_info[h];
             const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
             if (r >= rows) continue;
-            const int qlen = (((cnt + 3) >> 2) + 7) & ~7;
+            const int qlen = (((cnt + 3) >> 2) + 3) & ~3;
             unsigned long long p0 = 0ull, p1 = 0ull;
             sum_range(s_lists + 2 * off, min(cnt, g * qlen), min(cnt, (g + 1) * qlen), p0, p1);
             p0 = fadd2(p0, __shfl_xor_sync(0xffffffffu, p0, 8));

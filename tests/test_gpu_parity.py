@@ -473,3 +473,35 @@ def test_config3_full_size_step_matches_oracle():
     w = ot.group("ft_w")
     want_comb = (w[:fs.ft_in * F].reshape(-1, fs.piece_inputs, F) + w[fs.ft_in * F:].reshape(1, fs.piece_inputs, F)).reshape(-1)
     assert_close(tr.read_buffer("comb", fs.ft_in * F), want_comb, TOL_FWD, "comb")
+
+
+def test_ft_slice_backward_one_huge_slice_checksum():
+    """Every item in one king-bucket slice: more chunks than a block stages descriptors for, one list as long as the
+    batch.  Column sums of the gradient equal the dft rows weighted by their number of live features."""
+    F, l1, l2, B, A = 256, 8, 16, 36864, 40
+    fs = LS_FS.with_factorize(False)
+    pi, N = fs.piece_inputs, fs.ft_in
+    rng = np.random.default_rng(12)
+    init = _perturb(tb.layerstack_default_init(fs, F, l1, l2, 9), rng, ["ft_b", "l1_b", "l1_shared_bias", "l2_b", "l3_b"])
+    init["ft_w"] *= 30.0
+    nnz = rng.integers(20, A + 1, B).astype(np.int32)
+    def lists():
+        idx = rng.integers(0, pi, (B, A)).astype(np.int32)      # duplicates inside an item are allowed
+        idx[:, 0] = 7                                           # one row in every item
+        idx[np.arange(A)[None, :] >= nnz[:, None]] = -1
+        return np.where(idx >= 0, idx + 5 * pi, idx).astype(np.int32)
+    stm, nstm = lists(), lists()
+    batch = tb.BatchData(stm, nstm, nnz, np.clip(np.round(rng.normal(0, 400, B)), -3000, 3000).astype(np.float32),
+                         rng.choice(np.array([0.0, 0.5, 1.0], np.float32), B), rng.integers(0, 9, B).astype(np.int32))
+    tr = tb.GpuTrainer(B, F, l1, l2, 9, fs, optimizer="adamw", init=init)
+    tr.forward_backward(batch, 0.25, tb.LossKind.sigmoid())
+    dft = tr.read_buffer("dft_stm", B * F).reshape(B, F).astype(np.float64) + tr.read_buffer("dft_nstm", B * F).reshape(B, F)
+    grad = tr.download_grad("ft_w").reshape(-1, F)[:N]
+    assert not grad[:5 * pi].any() and not grad[6 * pi:].any()             # rows of the other slices stay zero
+    want = (dft * nnz[:, None]).sum(axis=0)
+    got = grad.astype(np.float64).sum(axis=0)
+    assert_close_scaled(got, want, 1e-5, "column sums")
+    live = np.arange(A)[None, :] < nnz[:, None]
+    hits = ((stm == 5 * pi + 7) & live).sum(axis=1)[:, None] * tr.read_buffer("dft_stm", B * F).reshape(B, F).astype(np.float64) + \
+        ((nstm == 5 * pi + 7) & live).sum(axis=1)[:, None] * tr.read_buffer("dft_nstm", B * F).reshape(B, F).astype(np.float64)
+    assert_close_scaled(grad[5 * pi + 7].astype(np.float64), hits.sum(axis=0), 1e-5, "the row every item holds")
