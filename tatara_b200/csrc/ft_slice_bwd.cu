@@ -414,26 +414,40 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(p0, p1));
             }
         }
-        // all other lists: one group each, the terms added one by one onto the running sum
-        for (;;) {
+        // all other lists: one group each, the terms added one by one onto the running sum.  The next record and its
+        // running sum (a gradient row written by the previous chunk) are fetched while the current record is summed.
+        auto grab = [&]() {
             int base = 0;
             if (lane == 0) base = atomicAdd(&s_ctl[1], 4);
-            base = __shfl_sync(0xffffffffu, base, 0);
-            if (base >= n_rec) break;
+            return __shfl_sync(0xffffffffu, base, 0);
+        };
+        auto fetch = [&](int base, unsigned long long& ri, ulonglong2& prev) {
+            ri = ~0ull;  // no record
+            prev = make_ulonglong2(0ull, 0ull);
             if (base + g < n_rec) {
-                const unsigned long long ri = s_info[base + g];
-                const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
-                if (r < rows) {
-                    float* gp = grad + (size_t)(row0 + r) * F + col;
-                    unsigned long long a0 = 0ull, a1 = 0ull;
-                    if (!first_chunk) {
-                        const ulonglong2 pv = __ldcg(reinterpret_cast<const ulonglong2*>(gp));
-                        a0 = pv.x; a1 = pv.y;
-                    }
-                    sum_range(s_lists + 2 * off, 0, cnt, a0, a1);
-                    __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(a0, a1));
+                const unsigned long long x = s_info[base + g];
+                if ((int)(x >> 32) < rows) {
+                    ri = x;
+                    if (!first_chunk) prev = __ldcg(reinterpret_cast<const ulonglong2*>(grad + (size_t)(row0 + (int)(x >> 32)) * F + col));
                 }
             }
+        };
+        int base = grab();
+        unsigned long long ri;
+        ulonglong2 prev;
+        fetch(base, ri, prev);
+        while (base < n_rec) {
+            const int base_n = grab();
+            unsigned long long ri_n;
+            ulonglong2 prev_n;
+            fetch(base_n, ri_n, prev_n);
+            if (ri != ~0ull) {
+                const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
+                unsigned long long a0 = prev.x, a1 = prev.y;
+                sum_range(s_lists + 2 * off, 0, cnt, a0, a1);
+                __stcg(reinterpret_cast<ulonglong2*>(grad + (size_t)(row0 + r) * F + col), make_ulonglong2(a0, a1));
+            }
+            base = base_n; ri = ri_n; prev = prev_n;
         }
     }
 }
