@@ -26,12 +26,12 @@
 struct BwdLayout {
     int CH;             // slots per chunk (multiple of 8)
     int rps_pad;        // row records per chunk
-    int region;         // 16-bit list cells per chunk (multiple of 8; every list is padded to a multiple of 4 cells)
+    int region;         // 16-bit list cells per chunk (every list is padded to a multiple of 8 cells: 16-byte code loads)
     int max_chunks;
     size_t off_first, off_len, off_rowinfo, off_lists, total_ints;
 };
 
-static inline size_t bwd_region(int CH, int rps, int A_pad) { return ((size_t)CH * A_pad + 4 * (size_t)rps + 7) / 8 * 8; }
+static inline size_t bwd_region(int CH, int rps, int A_pad) { return (size_t)CH * A_pad + 8 * (size_t)rps; }
 
 static inline size_t bwd_smem_bytes(int CH, int rps, int A_pad) {
     const int rps_pad = (rps + 3) / 4 * 4;
@@ -107,7 +107,7 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
 // ascending slot order and the ranked scatter is stable.
 // rowinfo (sorted by descending list length, so that the eight-lane groups of a warp get lists of similar length
 // and the long lists start first): row << 32 | list offset << 16 | list length; lists are padded to a multiple of
-// four cells with the index of the chunk's row of zeros (CH).
+// eight cells with the index of the chunk's row of zeros (CH).
 __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __restrict__ codes, const FwdWork* __restrict__ work,
                                                     const int* __restrict__ n_work, const int* __restrict__ outside_flag,
                                                     int n_slices, int A_pad, int rps, int rps_pad, int CH, int region,
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
                 run += c;
             }
             cnt[u] = run;
-            padded += (run + 3) & ~3;
+            padded += (run + 7) & ~7;
         }
     }
     int incl = padded;
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
         const int r = tid * rpt + u;
         if (r < rps) {
             s_rowoff[r] = base;
-            const int pe = base + ((cnt[u] + 3) & ~3);
+            const int pe = base + ((cnt[u] + 7) & ~7);
             for (int i = base + cnt[u]; i < pe; ++i) my_lists[i] = (unsigned short)CH;
             base = pe;
         }
@@ -351,13 +351,12 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
         // after the rest of the chunk.  All other records are handed out four at a time (neighbours in the order, so of
         // similar length) from a block-wide counter.
         const int n_rec = first_chunk ? rps : n_live;
-        // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 4 (lists start on
-        // 8-byte boundaries: the eight cells of a step are read as two 8-byte halves)
+        // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 8.  Called by all
+        // 32 lanes together (a group without a list passes an empty range)
         auto sum_range = [&](const unsigned char* lp, int beg, int end, unsigned long long& a0, unsigned long long& a1) {
             const int full = beg + ((end - beg) & ~7);
             for (int q = beg; q < full; q += 8) {
-                const uint2 ca = *reinterpret_cast<const uint2*>(lp + 2 * q), cb = *reinterpret_cast<const uint2*>(lp + 2 * q + 8);
-                const uint4 cc = make_uint4(ca.x, ca.y, cb.x, cb.y);
+                const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * q);
                 const ulonglong2 v0 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x & 0xffffu) * 128u);
                 const ulonglong2 v1 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.x >> 16) * 128u);
                 const ulonglong2 v2 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.y & 0xffffu) * 128u);
@@ -375,21 +374,32 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 a0 = fadd2(a0, v6.x); a1 = fadd2(a1, v6.y);
                 a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
             }
-            if (full < end) {  // the last one to seven entries; the padding cells behind them are not read as rows
-                const uint2 ca = *reinterpret_cast<const uint2*>(lp + 2 * full), cb = *reinterpret_cast<const uint2*>(lp + 2 * full + 8);
-                const uint4 cc = make_uint4(ca.x, ca.y, cb.x, cb.y);
+            // the last one to seven entries (the padding cells behind them are not read as rows).  All lanes of the warp
+            // come here together: the loop runs as far as the longest remainder of the warp's four lists, so that no
+            // load instruction is issued that none of them needs (the kernel is bound by the number of shared-memory
+            // load instructions, not by their width).
+            const int rem = end - full;
+            const int rem_w = __reduce_max_sync(0xffffffffu, rem);
+            if (rem_w > 0) {
+                const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * (rem > 0 ? full : 0));
                 const unsigned cell[8] = {cc.x & 0xffffu, cc.x >> 16, cc.y & 0xffffu, cc.y >> 16,
                                           cc.z & 0xffffu, cc.z >> 16, cc.w & 0xffffu, cc.w >> 16};
-                const int rem = end - full;
-                ulonglong2 v[7];
+                const ulonglong2 zero2 = make_ulonglong2(0ull, 0ull);
 #pragma unroll
-                for (int u = 0; u < 7; ++u) {
-                    v[u] = make_ulonglong2(0ull, 0ull);
-                    if (u < rem) v[u] = *reinterpret_cast<const ulonglong2*>(s_lane + cell[u] * 128u);
+                for (int h = 0; h < 8; h += 4) {  // two halves of up to four loads, then their additions
+                    if (h >= rem_w) break;
+                    ulonglong2 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        v[u] = zero2;
+                        if (h + u < 7 && h + u < rem_w) {
+                            if (h + u < rem) v[u] = *reinterpret_cast<const ulonglong2*>(s_lane + cell[h + u] * 128u);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (h + u < rem) { a0 = fadd2(a0, v[u].x); a1 = fadd2(a1, v[u].y); }
                 }
-#pragma unroll
-                for (int u = 0; u < 7; ++u)
-                    if (u < rem) { a0 = fadd2(a0, v[u].x); a1 = fadd2(a1, v[u].y); }
             }
         };
         const int warp = tid >> 5, g = lane >> 3;
@@ -398,7 +408,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
             const unsigned long long ri = s_info[h];
             const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
             if (r >= rows) continue;
-            const int qlen = (((cnt + 3) >> 2) + 3) & ~3;
+            const int qlen = (((cnt + 3) >> 2) + 7) & ~7;
             unsigned long long p0 = 0ull, p1 = 0ull;
             sum_range(s_lists + 2 * off, min(cnt, g * qlen), min(cnt, (g + 1) * qlen), p0, p1);
             p0 = fadd2(p0, __shfl_xor_sync(0xffffffffu, p0, 8));
@@ -441,11 +451,12 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
             unsigned long long ri_n;
             ulonglong2 prev_n;
             fetch(base_n, ri_n, prev_n);
-            if (ri != ~0ull) {
-                const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
+            {
+                const bool have = ri != ~0ull;
+                const int r = (int)(ri >> 32), off = have ? (int)((ri >> 16) & 0xffffu) : 0, cnt = have ? (int)(ri & 0xffffu) : 0;
                 unsigned long long a0 = prev.x, a1 = prev.y;
                 sum_range(s_lists + 2 * off, 0, cnt, a0, a1);
-                __stcg(reinterpret_cast<ulonglong2*>(grad + (size_t)(row0 + r) * F + col), make_ulonglong2(a0, a1));
+                if (have) __stcg(reinterpret_cast<ulonglong2*>(grad + (size_t)(row0 + r) * F + col), make_ulonglong2(a0, a1));
             }
             base = base_n; ri = ri_n; prev = prev_n;
         }
