@@ -808,7 +808,8 @@ int launch_tail_simple(cudaStream_t s, const float* l1_pre, const float* score, 
 // (dense_mm_bucket.rs:112-161; native_kernels.cu:2591-2744 use register accumulators + atomics.)
 // ------------------------------------------------------------------------------------------------
 #define SW_CMAX 5
-#define SW_SPLIT_LS 64  // blocks per bucket segment (LayerStack); the Simple net splits its one segment in 128
+#define SW_SPLIT_LS 59  // blocks per bucket segment (LayerStack): 10 segments x 59 = 590 blocks, two full waves of 1024-thread
+                        // blocks on 148 SMs; the Simple net splits its one segment in 128
 __global__ void __launch_bounds__(1024) k_small_wgrad(const int* __restrict__ order, const int* __restrict__ seg_start,
                                                        const float* __restrict__ U, int dimU, const float* __restrict__ V,
                                                        int dimV, const float* __restrict__ Bsrc, const float* __restrict__ l2_acted,
@@ -1050,9 +1051,9 @@ __global__ void __launch_bounds__(256) k_l1_wgrad_shared(const float* __restrict
 // rows are staged once, then the x rows arrive through a private ring of asynchronous copies (a thread copies the 16
 // bytes it reads itself), WG_STAGES rounds of four positions ahead of the arithmetic.
 #define WG_POS (TB_UNIT_TILES * TB_TILE_M)
-#define WG_STAGES 3
-template <int OPT>
-__global__ void __launch_bounds__(256) k_l1_wgrad_stream(const float* __restrict__ x, int K, const float* __restrict__ dl1,
+#define WG_STAGES 2
+template <int OPT, int THREADS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(THREADS, MIN_BLOCKS) k_l1_wgrad_stream(const float* __restrict__ x, int K, const float* __restrict__ dl1,
                                                           const int* __restrict__ order, const TileDesc* __restrict__ tiles,
                                                           const TileDesc* __restrict__ units, const int* __restrict__ n_units, int l1,
                                                           float* __restrict__ partials) {
@@ -1139,12 +1140,16 @@ int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, con
         const int threads = l1 == 32 ? 256 : 128;
         const size_t smem = (size_t)WG_POS * l1 * sizeof(float) + (size_t)WG_STAGES * 4 * threads * 16;
         const dim3 grid(ceil_div(K / 4, 128), max_units);
+        // 128-thread blocks at six per SM: with K = 1536 the 3 x 265 blocks of the benchmark then run as one wave
         if (l1 == 8) {
-            cudaFuncSetAttribute(k_l1_wgrad_stream<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-            k_l1_wgrad_stream<8><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+            cudaFuncSetAttribute(k_l1_wgrad_stream<8, 128, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            k_l1_wgrad_stream<8, 128, 6><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+        } else if (l1 == 16) {
+            cudaFuncSetAttribute(k_l1_wgrad_stream<16, 128, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            k_l1_wgrad_stream<16, 128, 6><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
         } else {
-            cudaFuncSetAttribute(k_l1_wgrad_stream<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-            k_l1_wgrad_stream<16><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
+            cudaFuncSetAttribute(k_l1_wgrad_stream<16, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+            k_l1_wgrad_stream<16, 256, 2><<<grid, threads, smem, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
         }
     } else
         k_l1_wgrad<<<dim3(K / 128, max_units), 256, 0, s>>>(x, K, dl1, order, tiles, units, n_units, l1, partials);
