@@ -102,6 +102,11 @@ int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* 
 int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,
                      int rows_per_slice, int n_persp, int* items, int* hist, int* seg);
 int sort_max_units(int max_tiles);
+// launch_bucket_sort and launch_item_sort in four launches instead of seven; hist: scratch of
+// (nb + 1) * ceil(B / 1024) + (slices + 1) * ceil(n_persp * B / 1024) ints
+int launch_step_sorts(cudaStream_t s, const int* bucket /*may be NULL*/, int B, int nb, int* order, TileDesc* tiles, int* n_tiles,
+                      int* seg_start, int max_tiles, const int* idx_stm, const int* idx_nstm, const int* nnz, int A, int N,
+                      int rows_per_slice, int n_persp, int* items, int* item_seg, int* hist);
 int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F);
 int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F);
 

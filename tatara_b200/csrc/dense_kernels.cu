@@ -808,8 +808,8 @@ int launch_tail_simple(cudaStream_t s, const float* l1_pre, const float* score, 
 // (dense_mm_bucket.rs:112-161; native_kernels.cu:2591-2744 use register accumulators + atomics.)
 // ------------------------------------------------------------------------------------------------
 #define SW_CMAX 5
-#define SW_SPLIT_LS 59  // blocks per bucket segment (LayerStack): 10 segments x 59 = 590 blocks, two full waves of 1024-thread
-                        // blocks on 148 SMs; the Simple net splits its one segment in 128
+#define SW_SPLIT_LS 64  // blocks per bucket segment (LayerStack; 59, two exact waves, measured slower); the Simple net splits
+                        // its one segment in 128
 __global__ void __launch_bounds__(1024) k_small_wgrad(const int* __restrict__ order, const int* __restrict__ seg_start,
                                                        const float* __restrict__ U, int dimU, const float* __restrict__ V,
                                                        int dimV, const float* __restrict__ Bsrc, const float* __restrict__ l2_acted,

@@ -35,19 +35,32 @@ struct ItemKey {
 };
 
 template <class KeyFn>
-__global__ void __launch_bounds__(SORT_BLOCK) k_sort_hist(KeyFn fn, int n, int K, int G, int* __restrict__ hist) {
-    __shared__ int s_h[SORT_MAX_KEYS];
+static __device__ __forceinline__ void sort_hist_body(KeyFn fn, int n, int K, int G, int* __restrict__ hist, int* s_h, int block) {
     if (threadIdx.x < SORT_MAX_KEYS) s_h[threadIdx.x] = 0;
     __syncthreads();
-    const int i = blockIdx.x * SORT_BLOCK + threadIdx.x;
+    const int i = block * SORT_BLOCK + threadIdx.x;
     if (i < n) atomicAdd(&s_h[fn(i)], 1);
     __syncthreads();
-    if ((int)threadIdx.x < K) hist[threadIdx.x * G + blockIdx.x] = s_h[threadIdx.x];
+    if ((int)threadIdx.x < K) hist[threadIdx.x * G + block] = s_h[threadIdx.x];
+}
+
+template <class KeyFn>
+__global__ void __launch_bounds__(SORT_BLOCK) k_sort_hist(KeyFn fn, int n, int K, int G, int* __restrict__ hist) {
+    __shared__ int s_h[SORT_MAX_KEYS];
+    sort_hist_body(fn, n, K, G, hist, s_h, blockIdx.x);
+}
+
+// two independent sorts in one launch: blockIdx.y selects the sort
+template <class Fn0, class Fn1>
+__global__ void __launch_bounds__(SORT_BLOCK) k_sort_hist2(Fn0 f0, int n0, int K0, int G0, int* __restrict__ h0, Fn1 f1, int n1, int K1,
+                                                            int G1, int* __restrict__ h1) {
+    __shared__ int s_h[SORT_MAX_KEYS];
+    if (blockIdx.y == 0) { if ((int)blockIdx.x < G0) sort_hist_body(f0, n0, K0, G0, h0, s_h, blockIdx.x); }
+    else if ((int)blockIdx.x < G1) sort_hist_body(f1, n1, K1, G1, h1, s_h, blockIdx.x);
 }
 
 // exclusive scan of hist[K][G] in key-major order (in place); seg_start[k] = first output slot of key k
-__global__ void __launch_bounds__(1024) k_sort_scan(int* __restrict__ hist, int K, int G, int n, int* __restrict__ seg_start) {
-    __shared__ int s_warp[32];
+static __device__ __forceinline__ void sort_scan_body(int* __restrict__ hist, int K, int G, int n, int* __restrict__ seg_start, int* s_warp) {
     const int total = K * G;
     const int per = (total + 1023) / 1024;
     const int beg = min((int)threadIdx.x * per, total), end = min(beg + per, total);
@@ -83,13 +96,24 @@ __global__ void __launch_bounds__(1024) k_sort_scan(int* __restrict__ hist, int 
     if (threadIdx.x == 0) seg_start[K] = n;
 }
 
+__global__ void __launch_bounds__(1024) k_sort_scan(int* __restrict__ hist, int K, int G, int n, int* __restrict__ seg_start) {
+    __shared__ int s_warp[32];
+    sort_scan_body(hist, K, G, n, seg_start, s_warp);
+}
+
+__global__ void __launch_bounds__(1024) k_sort_scan2(int* __restrict__ h0, int K0, int G0, int n0, int* __restrict__ seg0,
+                                                      int* __restrict__ h1, int K1, int G1, int n1, int* __restrict__ seg1) {
+    __shared__ int s_warp[32];
+    if (blockIdx.x == 0) sort_scan_body(h0, K0, G0, n0, seg0, s_warp);
+    else sort_scan_body(h1, K1, G1, n1, seg1, s_warp);
+}
+
 template <class KeyFn>
-__global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, int K, int G, const int* __restrict__ base,
-                                                             int* __restrict__ out) {
-    __shared__ int s_cnt[32][SORT_MAX_KEYS];
+static __device__ __forceinline__ void sort_scatter_body(KeyFn fn, int n, int K, int G, const int* __restrict__ base, int* __restrict__ out,
+                                                         int (*s_cnt)[SORT_MAX_KEYS], int block) {
     for (int e = threadIdx.x; e < 32 * SORT_MAX_KEYS; e += SORT_BLOCK) (&s_cnt[0][0])[e] = 0;
     __syncthreads();
-    const int i = blockIdx.x * SORT_BLOCK + threadIdx.x;
+    const int i = block * SORT_BLOCK + threadIdx.x;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int key = i < n ? fn(i) : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, key);
@@ -105,7 +129,22 @@ __global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, in
         }
     }
     __syncthreads();
-    if (key >= 0) out[base[key * G + blockIdx.x] + s_cnt[w][key] + rank] = i;
+    if (key >= 0) out[base[key * G + block] + s_cnt[w][key] + rank] = i;
+}
+
+template <class KeyFn>
+__global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, int K, int G, const int* __restrict__ base,
+                                                             int* __restrict__ out) {
+    __shared__ int s_cnt[32][SORT_MAX_KEYS];
+    sort_scatter_body(fn, n, K, G, base, out, s_cnt, blockIdx.x);
+}
+
+template <class Fn0, class Fn1>
+__global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter2(Fn0 f0, int n0, int K0, int G0, const int* __restrict__ b0, int* __restrict__ o0,
+                                                              Fn1 f1, int n1, int K1, int G1, const int* __restrict__ b1, int* __restrict__ o1) {
+    __shared__ int s_cnt[32][SORT_MAX_KEYS];
+    if (blockIdx.y == 0) { if ((int)blockIdx.x < G0) sort_scatter_body(f0, n0, K0, G0, b0, o0, s_cnt, blockIdx.x); }
+    else if ((int)blockIdx.x < G1) sort_scatter_body(f1, n1, K1, G1, b1, o1, s_cnt, blockIdx.x);
 }
 
 // tiles: runs of <= TB_TILE_M positions of one bucket; units: runs of <= TB_UNIT_TILES tiles of one bucket
@@ -179,4 +218,28 @@ int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, co
     k_sort_scan<<<1, 1024, 0, s>>>(hist, K, G, n, seg);
     k_sort_scatter<<<G, SORT_BLOCK, 0, s>>>(fn, n, K, G, hist, items);
     return 3;
+}
+
+// Both sorts of a step in four launches: positions by bucket (order, tiles, units) and items by table slice.
+// hist: scratch of (nb + 1) * ceil(B / 1024) + (slices + 1) * ceil(n_persp * B / 1024) ints.
+int launch_step_sorts(cudaStream_t s, const int* bucket, int B, int nb, int* order, TileDesc* tiles, int* n_tiles, int* seg_start,
+                      int max_tiles, const int* idx_stm, const int* idx_nstm, const int* nnz, int A, int N, int rows_per_slice,
+                      int n_persp, int* items, int* item_seg, int* hist) {
+    int n_slices = ceil_div(N, rows_per_slice);
+    if (n_slices + 1 > SORT_MAX_KEYS) {
+        rows_per_slice = ceil_div(N, SORT_MAX_KEYS - 1);
+        n_slices = ceil_div(N, rows_per_slice);
+    }
+    const int K0 = nb + 1, G0 = ceil_div(B, SORT_BLOCK);
+    const int n1 = n_persp * B, K1 = n_slices + 1, G1 = ceil_div(n1, SORT_BLOCK);
+    int* h0 = hist;
+    int* h1 = hist + (size_t)K0 * G0;
+    BucketKey f0{bucket, nb};
+    ItemKey f1{idx_stm, idx_nstm, nnz, B, A, N, rows_per_slice, n_slices};
+    const dim3 grid(G0 > G1 ? G0 : G1, 2);
+    k_sort_hist2<<<grid, SORT_BLOCK, 0, s>>>(f0, B, K0, G0, h0, f1, n1, K1, G1, h1);
+    k_sort_scan2<<<2, 1024, 0, s>>>(h0, K0, G0, B, seg_start, h1, K1, G1, n1, item_seg);
+    k_sort_scatter2<<<grid, SORT_BLOCK, 0, s>>>(f0, B, K0, G0, h0, order, f1, n1, K1, G1, h1, items);
+    k_make_tiles<<<1, 256, 0, s>>>(seg_start, K0, tiles, n_tiles, tiles + max_tiles, n_tiles + 1);
+    return 4;
 }

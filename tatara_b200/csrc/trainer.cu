@@ -308,11 +308,10 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     const float* table = c.ft_factorize ? t->comb : t->groups[0].w;
     t->last_n = B;
     { PhaseScope p(t, PH_SORT);
-      int n = launch_bucket_sort(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
-                                 t->seg_start, t->max_tiles, t->sort_hist);
-      // items of both perspectives ordered by the king-bucket slice of the FT table they read
-      n += launch_item_sort(t->stream, d.stm, d.nstm, d.nnz, B, A, N, c.piece_inputs > 0 ? c.piece_inputs : N, 2, t->items,
-                            t->sort_hist, t->item_seg);
+      // positions by bucket (order, tiles, units) and items of both perspectives by the king-bucket slice of the FT table
+      int n = launch_step_sorts(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
+                                t->seg_start, t->max_tiles, d.stm, d.nstm, d.nnz, A, N, c.piece_inputs > 0 ? c.piece_inputs : N, 2,
+                                t->items, t->item_seg, t->sort_hist);
       p.done(n); }
     { PhaseScope p(t, PH_FT_FWD);
       const int mode = ls ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
@@ -674,7 +673,9 @@ int create_impl(tb_trainer* t) {
     t->dgrad_rows = DGRAD_CTAS > 2 * t->max_units ? DGRAD_CTAS : 2 * t->max_units;  // partial FT bias rows: one per block
     CU(t, dalloc(&t->bias_partials, (size_t)t->dgrad_rows * 2 * F));
     CU(t, dalloc(&t->feat_counts, inverse_index_counts_len((int)N))); CU(t, dalloc(&t->feat_offsets, (size_t)2 * (N + 1)));
-    CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2))); CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
+    // histograms of the item sort and of the bucket sort
+    CU(t, dalloc(&t->sort_hist, (size_t)128 * (2 * B / 1024 + 2) + (size_t)(TB_MAX_BUCKETS + 1) * (B / 1024 + 2)));
+    CU(t, dalloc(&t->items, 2 * B)); CU(t, dalloc(&t->item_seg, 130));
     CU(t, dalloc(&t->fwd_work, ft_forward_slice_work_ints((int)(2 * B), 129, A)));
     {
         const int rps = c.piece_inputs > 0 ? c.piece_inputs : (int)N;
