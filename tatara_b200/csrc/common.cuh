@@ -157,5 +157,11 @@ int launch_radam(cudaStream_t s, float* w, float* m, float* v, const float* g, f
 int launch_radam_small(cudaStream_t s, const SmallGroups& groups, int max_n, OptScalars sc);
 // factorised FT table: per virtual row v, updates the real rows kb*pi+v, reduces their gradients into the
 // virtual row, updates it and writes the folded forward table.
+// the same in pieces: the real rows of the king buckets [kb0, kb1) (call with ascending ranges), then the virtual rows
+// and the folded table
+int launch_radam_factorized_rows(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, int N, int pi, int F, int kb0,
+                                 int kb1, OptScalars sc);
+int launch_radam_factorized_fold(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb, int N, int pi,
+                                 int F, OptScalars sc);
 int launch_radam_factorized(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb,
                             int N, int pi, int F, OptScalars sc);

@@ -151,6 +151,79 @@ __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) k_radam_factorized(fl
     }
 }
 
+// The same work in two kinds of launches, for the data-parallel pipeline in which the gradient rows arrive king bucket
+// range by king bucket range: k_radam_factorized_rows updates the real rows of the buckets [kb0, kb1) and carries the
+// running gradient sum of every virtual row through that row's gradient cell (ranges must be given in ascending
+// order, so the sum is added up in the order of the fused kernel), k_radam_factorized_fold then updates the virtual
+// rows and writes the folded table.  Results are bit-identical to the fused kernel.
+__global__ void __launch_bounds__(1024) k_radam_factorized_rows(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v,
+                                                                 float4* __restrict__ g, float4* __restrict__ slow, int N, int pi,
+                                                                 int row4, int kb0, int kb1, OptScalars sc) {
+    const int vr = blockIdx.x;
+    const int c = threadIdx.x;
+    const float rate = sc.lr * sc.step_size;
+    const float decay_mul = 1.0f - sc.decay * rate;
+    const size_t iv = (size_t)(N + vr) * row4 + c;
+    float4 gsum = kb0 == 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : g[iv];
+#pragma unroll 4
+    for (int kb = kb0; kb < kb1; ++kb) {
+        const size_t i = (size_t)(kb * pi + vr) * row4 + c;
+        const float4 gi = __ldcs(g + i);
+        float4 mi = __ldcs(m + i), vi = __ldcs(v + i);
+        float4 p = radam_four(w[i], mi, vi, gi, sc, rate, decay_mul);
+        __stcs(m + i, mi);
+        __stcs(v + i, vi);
+        if (sc.lerp) {
+            p = lerp_four(p, __ldcs(slow + i), sc.alpha);
+            __stcs(slow + i, p);
+        }
+        w[i] = p;
+        gsum.x += gi.x; gsum.y += gi.y; gsum.z += gi.z; gsum.w += gi.w;
+    }
+    g[iv] = gsum;
+}
+
+__global__ void __launch_bounds__(1024) k_radam_factorized_fold(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v,
+                                                                 float4* __restrict__ g, float4* __restrict__ slow,
+                                                                 float4* __restrict__ comb, int N, int pi, int row4, OptScalars sc) {
+    const int vr = blockIdx.x;
+    const int c = threadIdx.x;
+    const float rate = sc.lr * sc.step_size;
+    const float decay_mul = 1.0f - sc.decay * rate;
+    const int KB = N / pi;
+    const size_t iv = (size_t)(N + vr) * row4 + c;
+    float4 mv = m[iv], vv = v[iv];
+    float4 pv = radam_four(w[iv], mv, vv, g[iv], sc, rate, decay_mul);
+    m[iv] = mv;
+    v[iv] = vv;
+    if (sc.lerp) {
+        pv = lerp_four(pv, slow[iv], sc.alpha);
+        slow[iv] = pv;
+    }
+    w[iv] = pv;
+#pragma unroll 4
+    for (int kb = 0; kb < KB; ++kb) {
+        const size_t i = (size_t)(kb * pi + vr) * row4 + c;
+        const float4 p = __ldcs(w + i);
+        __stcs(comb + i, make_float4(p.x + pv.x, p.y + pv.y, p.z + pv.z, p.w + pv.w));
+    }
+}
+
+int launch_radam_factorized_rows(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, int N, int pi, int F, int kb0,
+                                 int kb1, OptScalars sc) {
+    k_radam_factorized_rows<<<pi, F / 4, 0, s>>>(reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v),
+                                                 reinterpret_cast<float4*>(g), reinterpret_cast<float4*>(slow), N, pi, F / 4, kb0, kb1, sc);
+    return 1;
+}
+
+int launch_radam_factorized_fold(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb, int N, int pi,
+                                 int F, OptScalars sc) {
+    k_radam_factorized_fold<<<pi, F / 4, 0, s>>>(reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v),
+                                                 reinterpret_cast<float4*>(g), reinterpret_cast<float4*>(slow),
+                                                 reinterpret_cast<float4*>(comb), N, pi, F / 4, sc);
+    return 1;
+}
+
 int launch_radam_factorized(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb, int N,
                             int pi, int F, OptScalars sc) {
     float4 *w4 = reinterpret_cast<float4*>(w), *m4 = reinterpret_cast<float4*>(m), *v4 = reinterpret_cast<float4*>(v);

@@ -123,8 +123,11 @@ struct tb_trainer {
     int *sort_hist = nullptr, *items = nullptr, *item_seg = nullptr, *bwd_plan = nullptr, *fwd_work = nullptr, *bwd_slice = nullptr;
     int dgrad_rows = 0;
     cudaStream_t comm_stream = nullptr;  // data parallel: all-reduces behind the FT weight gradient
-    cudaEvent_t ev_part[AR_PARTS] = {}, ev_comm_done = nullptr;
+    cudaStream_t opt_stream = nullptr;   // data parallel: FT row updates behind their all-reduces
+    cudaEvent_t ev_part[AR_PARTS] = {}, ev_reduced[AR_PARTS] = {}, ev_comm_done = nullptr, ev_opt_done = nullptr;
     bool ar_pipelined = false;
+    bool opt_begun = false;        // this step's optimizer scalars are out (step_count already incremented)
+    bool ft_rows_updated = false;  // this step's real FT rows were updated behind their all-reduces
     bool slice_fwd = false;  // this step's forward ran slice-resident (its row codes are in fwd_work)
     float* bwd_partial = nullptr;
     int last_n = 0;
@@ -307,6 +310,7 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     const bool ls = c.arch == TB_ARCH_LAYERSTACK;
     const float* table = c.ft_factorize ? t->comb : t->groups[0].w;
     t->last_n = B;
+    if (backward) { t->opt_begun = false; t->ft_rows_updated = false; }  // a step that failed half way leaves no state behind
     { PhaseScope p(t, PH_SORT);
       // positions by bucket (order, tiles, units) and items of both perspectives by the king-bucket slice of the FT table
       int n = launch_step_sorts(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
@@ -345,7 +349,11 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     return TB_OK;
 }
 
-int run_backward(tb_trainer* t, const DevBatch& d) {
+static OptScalars ft_scalars(tb_trainer* t, float lr);
+
+// lr >= 0: a full training step (the data-parallel pipeline may then update FT rows behind their all-reduces);
+// lr < 0: gradients only
+int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
     const tb_config& c = t->cfg;
     const int B = d.n_pos, F = c.ft_out, N = c.ft_in, A = c.max_active;
     const bool ls = c.arch == TB_ARCH_LAYERSTACK;
@@ -415,9 +423,30 @@ int run_backward(tb_trainer* t, const DevBatch& d) {
               if (rc == 0 && part == parts - 1) rc = g_nccl.AllReduce(t->loss_acc, t->loss_acc, 1, /*ncclDouble*/ 8, 0, t->comm, t->comm_stream);
               const int rc2 = g_nccl.GroupEnd();
               if (rc == 0) rc = rc2;
+              if (rc == 0 && lr >= 0.0f) {
+                  // consumer side of the pipeline: the optimizer of this part's real rows follows its all-reduce on the
+                  // same stream, next to the gradient launch of the next part (and alone on the GPU behind the last)
+                  // (a third stream: the next part's all-reduce does not wait for this part's optimizer)
+                  const OptScalars sc = ft_scalars(t, lr);
+                  Group& g = t->groups[0];
+                  const int r0 = k0 * rps, r1 = k1 * rps < N ? k1 * rps : N;
+                  CU(t, cudaEventRecord(t->ev_reduced[part], t->comm_stream));
+                  CU(t, cudaStreamWaitEvent(t->opt_stream, t->ev_reduced[part], 0));
+                  if (c.ft_factorize)
+                      n += launch_radam_factorized_rows(t->opt_stream, g.w, g.m, g.v, g.grad, g.slow, N, c.piece_inputs, F, k0, k1, sc);
+                  else
+                      n += launch_radam(t->opt_stream, g.w + (size_t)r0 * F, g.m + (size_t)r0 * F, g.v + (size_t)r0 * F,
+                                        g.grad + (size_t)r0 * F, c.optimizer == TB_OPT_RANGER ? g.slow + (size_t)r0 * F : g.slow,
+                                        (int64_t)(r1 - r0) * F, sc);
+                  t->ft_rows_updated = true;
+              }
           }
           if (pipeline) {
               if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString(rc));
+              if (t->ft_rows_updated) {  // the optimizer stream joins the communication stream
+                  CU(t, cudaEventRecord(t->ev_opt_done, t->opt_stream));
+                  CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_opt_done, 0));
+              }
               CU(t, cudaEventRecord(t->ev_comm_done, t->comm_stream));
               t->ar_pipelined = true;
           }
@@ -446,17 +475,38 @@ int run_allreduce(tb_trainer* t) {
     return TB_OK;
 }
 
-int run_optimizer(tb_trainer* t, float lr) {
+// The step's optimizer scalars; the first call of a step increments step_count (before the scalars are computed,
+// trainer_layerstack.rs:4078-4081), run_optimizer ends the step.
+static OptScalars optimizer_step_scalars(tb_trainer* t) {
     const tb_config& c = t->cfg;
-    const bool ls = c.arch == TB_ARCH_LAYERSTACK;
-    // step_count increments before the scalars are computed (trainer_layerstack.rs:4078-4081)
-    t->step_count += 1;
+    if (!t->opt_begun) {
+        t->step_count += 1;
+        t->opt_begun = true;
+    }
     OptScalars sc;
     optimizer_scalars(c.optimizer, t->step_count, &sc.step_size, &sc.denom, &sc.beta1);
     sc.beta2 = BETA2;
     sc.eps = EPS;
     sc.alpha = RANGER_ALPHA;
     sc.lerp = (c.optimizer == TB_OPT_RANGER && t->step_count % RANGER_K == 0) ? 1 : 0;
+    return sc;
+}
+
+static OptScalars ft_scalars(tb_trainer* t, float lr) {
+    OptScalars sc = optimizer_step_scalars(t);
+    const Group& g = t->groups[0];
+    sc.lr = lr * t->cfg.lr_mult_ft;
+    sc.decay = t->cfg.wd_ft;
+    sc.min_w = -g.clamp;
+    sc.max_w = g.clamp;
+    return sc;
+}
+
+int run_optimizer(tb_trainer* t, float lr) {
+    const tb_config& c = t->cfg;
+    const bool ls = c.arch == TB_ARCH_LAYERSTACK;
+    OptScalars sc = optimizer_step_scalars(t);
+    t->opt_begun = false;
     const float wd[3] = {c.wd_ft, ls ? c.wd_dense : c.wd_ft, ls ? c.wd_bias : c.wd_ft};
     const float lm[3] = {c.lr_mult_ft, ls ? c.lr_mult_dense : c.lr_mult_ft, ls ? c.lr_mult_bias : c.lr_mult_ft};
     {
@@ -466,7 +516,15 @@ int run_optimizer(tb_trainer* t, float lr) {
         sc.decay = wd[0];
         sc.min_w = -g.clamp;
         sc.max_w = g.clamp;
-        if (c.ft_factorize)
+        if (t->ft_rows_updated) {
+            // data parallel: the real rows were updated part by part behind their all-reduces; what is left are the
+            // virtual rows and the folded table
+            t->ft_rows_updated = false;
+            if (c.ft_factorize)
+                p.done(launch_radam_factorized_fold(t->stream, g.w, g.m, g.v, g.grad, g.slow, t->comb, c.ft_in, c.piece_inputs, c.ft_out, sc));
+            else
+                p.done(0);
+        } else if (c.ft_factorize)
             p.done(launch_radam_factorized(t->stream, g.w, g.m, g.v, g.grad, g.slow, t->comb, c.ft_in, c.piece_inputs, c.ft_out, sc));
         else
             p.done(launch_radam(t->stream, g.w, g.m, g.v, g.grad, g.slow, g.len, sc));
@@ -512,7 +570,7 @@ int loss_ring_next(tb_trainer* t, double* out) {
 
 int step_on(tb_trainer* t, const DevBatch& d, float lr, float lambda, const tb_loss* loss, double* loss_prev) {
     int rc = run_forward(t, d, loss, lambda, 1);
-    if (rc == TB_OK) rc = run_backward(t, d);
+    if (rc == TB_OK) rc = run_backward(t, d, lr);
     if (rc == TB_OK) rc = run_allreduce(t);
     if (rc == TB_OK) rc = run_optimizer(t, lr);
     if (rc != TB_OK) return rc;
@@ -574,7 +632,10 @@ void free_all(tb_trainer* t) {
         if (t->ph_stop[i]) cudaEventDestroy(t->ph_stop[i]);
     }
     if (t->comm_stream) cudaStreamDestroy(t->comm_stream);
+    if (t->opt_stream) cudaStreamDestroy(t->opt_stream);
     for (auto& e : t->ev_part) if (e) cudaEventDestroy(e);
+    for (auto& e : t->ev_reduced) if (e) cudaEventDestroy(e);
+    if (t->ev_opt_done) cudaEventDestroy(t->ev_opt_done);
     if (t->ev_comm_done) cudaEventDestroy(t->ev_comm_done);
     if (t->copy_stream) cudaStreamDestroy(t->copy_stream);
     if (t->stream) cudaStreamDestroy(t->stream);
@@ -704,7 +765,10 @@ int create_impl(tb_trainer* t) {
             CU(t, cudaDeviceGetStreamPriorityRange(&lo, &hi));
             CU(t, cudaStreamCreateWithPriority(&t->comm_stream, cudaStreamNonBlocking, hi));
         }
+        CU(t, cudaStreamCreateWithFlags(&t->opt_stream, cudaStreamNonBlocking));
         for (auto& e : t->ev_part) CU(t, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        for (auto& e : t->ev_reduced) CU(t, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        CU(t, cudaEventCreateWithFlags(&t->ev_opt_done, cudaEventDisableTiming));
         CU(t, cudaEventCreateWithFlags(&t->ev_comm_done, cudaEventDisableTiming));
     }
     CU(t, cudaDeviceSynchronize());
@@ -915,7 +979,7 @@ int tb_forward_backward(tb_trainer* t, const tb_batch* batch, float wdl_lambda, 
     DevBatch& d = t->slots[TB_NUM_SLOTS - 1];
     rc = upload_batch(t, batch, &d, nullptr, t->stream);
     if (rc == TB_OK) rc = run_forward(t, d, loss, wdl_lambda, 1);
-    if (rc == TB_OK) rc = run_backward(t, d);
+    if (rc == TB_OK) rc = run_backward(t, d, -1.0f);
     if (rc == TB_OK) rc = run_allreduce(t);
     if (rc != TB_OK) return rc;
     if (t->cfg.ft_factorize)
