@@ -878,32 +878,40 @@ __global__ void __launch_bounds__(1024) k_small_wgrad(const int* __restrict__ or
     }
 }
 
-// n_seg segments (the last one holds positions with an out-of-range bucket when has_invalid).
-__global__ void k_small_wgrad_final(const float* __restrict__ partials, int n_seg, int has_invalid, int SW_SPLIT, int n_cells, int nW,
-                                    int l2, int l1, float* __restrict__ gw2, float* __restrict__ gb2, float* __restrict__ gw3,
-                                    float* __restrict__ gb3, float* __restrict__ gb1, float* __restrict__ gb1_shared) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// n_seg segments (the last one holds positions with an out-of-range bucket when has_invalid).  A warp per output
+// cell: the lanes add the SW_SPLIT partials of the cell (lane l takes l, l + 32, ...), then a shuffle tree; a fixed order.
+static __device__ __forceinline__ float sw_cell_sum(const float* __restrict__ partials, int g, int SW_SPLIT, int n_cells, int cell,
+                                                    int lane) {
+    float sum = 0.f;
+    for (int sp = lane; sp < SW_SPLIT; sp += 32) sum += partials[((size_t)g * SW_SPLIT + sp) * n_cells + cell];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    return sum;
+}
+
+__global__ void __launch_bounds__(256) k_small_wgrad_final(const float* __restrict__ partials, int n_seg, int has_invalid, int SW_SPLIT,
+                                                            int n_cells, int nW, int l2, int l1, float* __restrict__ gw2,
+                                                            float* __restrict__ gb2, float* __restrict__ gw3, float* __restrict__ gb3,
+                                                            float* __restrict__ gb1, float* __restrict__ gb1_shared) {
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // warp index
     const int n_real = has_invalid ? n_seg - 1 : n_seg;
     if (i < n_real * n_cells) {
         const int g = i / n_cells, cell = i - g * n_cells;
-        float sum = 0.f;
-        for (int sp = 0; sp < SW_SPLIT; ++sp) sum += partials[((size_t)g * SW_SPLIT + sp) * n_cells + cell];
-        if (cell < nW) gw2[(size_t)g * nW + cell] = sum;
-        else if (cell < nW + l2) gb2[g * l2 + (cell - nW)] = sum;
-        else if (cell < nW + 2 * l2) gw3[g * l2 + (cell - nW - l2)] = sum;
-        else if (cell == nW + 2 * l2) gb3[g] = sum;
-        else gb1[g * l1 + (cell - nW - 2 * l2 - 1)] = sum;
-    }
-    if (gb1_shared && i < l1) {
-        // shared L1 bias: every position contributes, also those with an out-of-range bucket
-        float tot = 0.f;
-        const int cell = nW + 2 * l2 + 1 + i;
-        for (int g = 0; g < n_seg; ++g) {
-            float sum = 0.f;
-            for (int sp = 0; sp < SW_SPLIT; ++sp) sum += partials[((size_t)g * SW_SPLIT + sp) * n_cells + cell];
-            tot += sum;
+        const float sum = sw_cell_sum(partials, g, SW_SPLIT, n_cells, cell, lane);
+        if (lane == 0) {
+            if (cell < nW) gw2[(size_t)g * nW + cell] = sum;
+            else if (cell < nW + l2) gb2[g * l2 + (cell - nW)] = sum;
+            else if (cell < nW + 2 * l2) gw3[g * l2 + (cell - nW - l2)] = sum;
+            else if (cell == nW + 2 * l2) gb3[g] = sum;
+            else gb1[g * l1 + (cell - nW - 2 * l2 - 1)] = sum;
         }
-        gb1_shared[i] = tot;
+    } else if (gb1_shared && i < n_real * n_cells + l1) {
+        // shared L1 bias: every position contributes, also those with an out-of-range bucket
+        const int cell = nW + 2 * l2 + 1 + (i - n_real * n_cells);
+        float tot = 0.f;
+        for (int g = 0; g < n_seg; ++g) tot += sw_cell_sum(partials, g, SW_SPLIT, n_cells, cell, lane);
+        if (lane == 0) gb1_shared[i - n_real * n_cells] = tot;
     }
 }
 
@@ -917,8 +925,8 @@ static int small_wgrad(cudaStream_t s, const int* order, const int* seg_start, i
     cudaFuncSetAttribute(k_small_wgrad, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     k_small_wgrad<<<dim3(n_seg, split), 1024, smem, s>>>(order, seg_start, U, dimU, V, dimV, Bsrc, l2_acted, l2, dy, dl1,
                                                           l1, partials, n_cells);
-    const int n = n_seg * n_cells;
-    k_small_wgrad_final<<<ceil_div(n > l1 ? n : l1, 256), 256, 0, s>>>(partials, n_seg, has_invalid, split, n_cells, nW, l2, l1, gw2,
+    const int n = n_seg * n_cells + l1;  // warps
+    k_small_wgrad_final<<<ceil_div(n, 8), 256, 0, s>>>(partials, n_seg, has_invalid, split, n_cells, nW, l2, l1, gw2,
                                                                       gb2, gw3, gb3, gb1, gb1_shared);
     return 2;
 }

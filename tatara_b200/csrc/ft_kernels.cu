@@ -167,7 +167,7 @@ __global__ void k_fwd_plan(const int* __restrict__ item_seg, int n_keys, int ipc
     }
     __syncthreads();
     for (int k = 0; k < n_keys; ++k) {
-        const int b0 = item_seg[k], e0 = item_seg[k + 1];
+        const int b0 = s_seg[k], e0 = s_seg[k + 1];
         const int n = s_base[k + 1] - s_base[k];
         // equal runs, a multiple of the 128 items a block handles per round (<= ipc, itself such a multiple)
         const int size = n > 0 ? ((e0 - b0 + n - 1) / n + 127) & ~127 : 0;

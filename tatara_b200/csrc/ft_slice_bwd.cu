@@ -88,7 +88,7 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
     __syncthreads();
     for (int k = threadIdx.x; k <= n_keys; k += blockDim.x) first[k] = s_base[k];
     for (int k = 0; k < n_keys; ++k) {
-        const int b0 = item_seg[k], e0 = item_seg[k + 1];
+        const int b0 = s_seg[k], e0 = s_seg[k + 1];
         const int n = s_base[k + 1] - s_base[k];
         const int size = n > 0 ? ((e0 - b0 + n - 1) / n + 7) & ~7 : 0;  // equal chunks (<= ipc: ipc is a multiple of 8)
         for (int i = threadIdx.x; i < n; i += blockDim.x) {

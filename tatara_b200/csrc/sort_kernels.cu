@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_
     }
     __syncthreads();
     for (int k = 0; k < K; ++k) {
-        const int s0 = seg_start[k], c = seg_start[k + 1] - s0;
+        const int s0 = s_seg[k], c = s_seg[k + 1] - s0;
         const int nt = (c + TB_TILE_M - 1) / TB_TILE_M;
         for (int t = threadIdx.x; t < nt; t += blockDim.x) {
             TileDesc d;
