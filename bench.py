@@ -46,8 +46,8 @@ FALLBACK_HBM_GBS = 6650.0
 # (bytes at the benchmark's full size; None = not captured yet)
 NCU_TRAFFIC_BYTES = {
     # profiles/step_cfg3_launch_list.md: full-size launches of the dominant kernel of each phase (the metrics take one pass)
-    ("cfg3", "ft_backward"): 1621.8e6, ("cfg3", "ft_forward"): 1748.1e6, ("cfg3", "opt_ft"): 3943.4e6,
-    ("cfg3", "l1_dgrad_ftgrad"): 1583.0e6, ("cfg3", "l1_forward"): 404.6e6, ("cfg3", "l1_wgrad"): 425.6e6,
+    ("cfg3", "ft_backward"): 1635.0e6, ("cfg3", "ft_forward"): 1750.2e6, ("cfg3", "opt_ft"): 4232.5e6,
+    ("cfg3", "l1_dgrad_ftgrad"): 1583.3e6, ("cfg3", "l1_forward"): 404.8e6, ("cfg3", "l1_wgrad"): 411.2e6,
 }
 
 
