@@ -4,8 +4,8 @@
 // feature sets by construction; k_fwd_codes checks it for the batch at hand), a feature row of slice k is touched
 // only by the items sorted into slice k.  The slice's items are cut into chunks of <= CH consecutive slots; for
 // each chunk one block builds the inverse index locally (k_inv_chunk: for every row of the slice the ascending
-// list of chunk-local slots that hold it, by a stable counting sort in shared memory, no atomics, no per-list
-// sort), and the gradient kernel keeps a 32-column strip of the chunk's dft rows in shared memory together with
+// list of chunk-local slots that hold it, by a counting sort in shared memory whose integer atomics only hand out
+// ranks inside one slot, so the lists come out ascending without a per-list sort), and the gradient kernel keeps a 32-column strip of the chunk's dft rows in shared memory together with
 // all of the chunk's lists, so that every row read of the sum comes from shared memory.
 // A block owns (slice, column strip), walks the slice's chunks in order and carries the running sums through the
 // gradient rows themselves, so a row's terms are added one by one in ascending item order: the result is
@@ -20,7 +20,7 @@
 #include "ft_slice.cuh"
 
 #define INV_SORT_N 2048  // rows per slice limit (bitonic sort size)
-#define BWD_HOT 256      // list length from which a list is summed by a warp of its own
+#define BWD_HOT 256      // list length from which a list is summed as four quarters by the four groups of one warp
 #define BWD_DESC 64      // chunk descriptors a block stages in shared memory
 
 struct BwdLayout {
@@ -103,8 +103,8 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
 }
 
 // Inverse index of one chunk.  Shared memory: hist [32 warps][rps_h] 16-bit cells, rowoff [rps] ints, sort keys
-// [INV_SORT_N] ints, the chunk's lists [region] 16-bit cells (copied out at the end in 16-byte pieces).  Warp w owns a contiguous range of the chunk's slots, so "warp, then step, then lane" is
-// ascending slot order and the ranked scatter is stable.
+// [INV_SORT_N] ints, the chunk's lists [region] 16-bit cells (copied out at the end in 16-byte pieces).  Warp w owns
+// a contiguous range of the chunk's slots and walks it slot by slot, so "warp, then slot" is ascending slot order.
 // rowinfo (sorted by descending list length, so that the eight-lane groups of a warp get lists of similar length
 // and the long lists start first): row << 32 | list offset << 16 | list length; lists are padded to a multiple of
 // eight cells with the index of the chunk's row of zeros (CH).
