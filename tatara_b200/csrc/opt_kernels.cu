@@ -143,8 +143,9 @@ __global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) k_radam_factorized(fl
         slow[iv] = pv;
     }
     w[iv] = pv;
+    // newest rows first: they are the ones most likely still in L2
 #pragma unroll 4
-    for (int kb = 0; kb < KB; ++kb) {
+    for (int kb = KB - 1; kb >= 0; --kb) {
         const size_t i = (size_t)(kb * pi + vr) * row4 + c;
         const float4 p = w[i];
         __stcs(comb + i, make_float4(p.x + pv.x, p.y + pv.y, p.z + pv.z, p.w + pv.w));
