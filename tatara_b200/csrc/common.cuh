@@ -57,12 +57,12 @@ static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b;
 
 // ft_kernels.cu
 // mode: 0 raw gather-sum, 1 LayerStack pairwise (+bias, CReLU, product, scale), 2 Simple CReLU, 3 Simple SCReLU
-// items: the (position, perspective) processing order from launch_item_sort, or NULL for natural order
+// items: the (position, perspective) processing order from launch_step_sorts, or NULL for natural order
 int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
                       const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
                       const int* items, int B, int F, int N, int A, float scale, int n_persp);
 // slice-resident forward: every item's rows come from a 32-column strip of its king-bucket slice held in shared
-// memory.  Needs items / item_seg from launch_item_sort with the same rows_per_slice; work: scratch of
+// memory.  Needs items / item_seg from launch_step_sorts with the same rows_per_slice; work: scratch of
 // ft_forward_slice_work_ints(n_items, slices + 1, A) ints.
 bool ft_forward_slice_supported(int F, int N, int A, int rows_per_slice);
 size_t ft_forward_slice_work_ints(int n_items, int n_keys, int A);
@@ -97,12 +97,10 @@ int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int
 // the rows of slices [slice_begin, slice_begin + slice_count)
 int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
                              int A, int N, int F, int rows_per_slice, int n_persp, int slice_begin, int slice_count, float* grad);
-// items of both perspectives sorted by the table slice of their features; hist: [(slices + 1) * ceil(n_persp*B/1024)],
-// seg: [slices + 2]
-int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,
-                     int rows_per_slice, int n_persp, int* items, int* hist, int* seg);
 int sort_max_units(int max_tiles);
-// launch_bucket_sort and launch_item_sort in four launches instead of seven; hist: scratch of
+// The two sorts of a step: positions by bucket -> order, bucket segments seg_start [nb + 2], tiles (room for max_tiles
+// tiles followed by the work units; n_tiles is {tile count, unit count}); items (position, perspective) of both
+// perspectives by the table slice of their features -> items, item_seg [slices + 2].  hist: scratch of
 // (nb + 1) * ceil(B / 1024) + (slices + 1) * ceil(n_persp * B / 1024) ints
 int launch_step_sorts(cudaStream_t s, const int* bucket /*may be NULL*/, int B, int nb, int* order, TileDesc* tiles, int* n_tiles,
                       int* seg_start, int max_tiles, const int* idx_stm, const int* idx_nstm, const int* nnz, int A, int N,
@@ -111,10 +109,6 @@ int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F);
 int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F);
 
 // dense_kernels.cu
-// tiles has room for max_tiles tiles followed by the work units; n_tiles is {tile count, unit count}
-// hist: scratch of (nb + 1) * ceil(B / 1024) ints
-int launch_bucket_sort(cudaStream_t s, const int* bucket /*may be NULL*/, int B, int nb, int* order,
-                       TileDesc* tiles, int* n_tiles, int* seg_start /*[nb+2]*/, int max_tiles, int* hist);
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb /*[nb][l1][K] or NULL*/,
                       const float* bb, const float* ws /*[K][l1]*/, const float* bs, float* y /*[B][l1]*/,

@@ -3,8 +3,9 @@
 //    (replaces count_buckets / exclusive_scan_aligned / scatter_bucket_perm, native_kernels.cu:1858-1925)
 //  - (position, perspective) items by the king bucket of their feature rows -> `items`, so that blocks that
 //    run at the same time gather from the same slice of the FT table and the slice stays in L2.
-// Three launches each: per-block histogram, one-block scan of the [key][block] matrix, stable scatter
-// (rank inside a block = warp match + prefix over the block's warps).  Results do not depend on timing.
+// Both sorts share three launches (blockIdx.y / blockIdx.x selects the sort): per-block histogram, one-block scan of the
+// [key][block] matrix, stable scatter (rank inside a block = warp match + prefix over the block's warps); a fourth
+// launch cuts the bucket segments into tiles and work units.  Results do not depend on timing.
 #include "common.cuh"
 
 #define SORT_BLOCK 1024
@@ -42,12 +43,6 @@ static __device__ __forceinline__ void sort_hist_body(KeyFn fn, int n, int K, in
     if (i < n) atomicAdd(&s_h[fn(i)], 1);
     __syncthreads();
     if ((int)threadIdx.x < K) hist[threadIdx.x * G + block] = s_h[threadIdx.x];
-}
-
-template <class KeyFn>
-__global__ void __launch_bounds__(SORT_BLOCK) k_sort_hist(KeyFn fn, int n, int K, int G, int* __restrict__ hist) {
-    __shared__ int s_h[SORT_MAX_KEYS];
-    sort_hist_body(fn, n, K, G, hist, s_h, blockIdx.x);
 }
 
 // two independent sorts in one launch: blockIdx.y selects the sort
@@ -96,11 +91,6 @@ static __device__ __forceinline__ void sort_scan_body(int* __restrict__ hist, in
     if (threadIdx.x == 0) seg_start[K] = n;
 }
 
-__global__ void __launch_bounds__(1024) k_sort_scan(int* __restrict__ hist, int K, int G, int n, int* __restrict__ seg_start) {
-    __shared__ int s_warp[32];
-    sort_scan_body(hist, K, G, n, seg_start, s_warp);
-}
-
 __global__ void __launch_bounds__(1024) k_sort_scan2(int* __restrict__ h0, int K0, int G0, int n0, int* __restrict__ seg0,
                                                       int* __restrict__ h1, int K1, int G1, int n1, int* __restrict__ seg1) {
     __shared__ int s_warp[32];
@@ -130,13 +120,6 @@ static __device__ __forceinline__ void sort_scatter_body(KeyFn fn, int n, int K,
     }
     __syncthreads();
     if (key >= 0) out[base[key * G + block] + s_cnt[w][key] + rank] = i;
-}
-
-template <class KeyFn>
-__global__ void __launch_bounds__(SORT_BLOCK) k_sort_scatter(KeyFn fn, int n, int K, int G, const int* __restrict__ base,
-                                                             int* __restrict__ out) {
-    __shared__ int s_cnt[32][SORT_MAX_KEYS];
-    sort_scatter_body(fn, n, K, G, base, out, s_cnt, blockIdx.x);
 }
 
 template <class Fn0, class Fn1>
@@ -191,34 +174,6 @@ __global__ void __launch_bounds__(256) k_make_tiles(const int* __restrict__ seg_
 }
 
 int sort_max_units(int max_tiles) { return max_tiles / TB_UNIT_TILES + TB_MAX_BUCKETS + 2; }
-
-// hist: scratch of (nb + 1) * ceil(B / 1024) ints
-int launch_bucket_sort(cudaStream_t s, const int* bucket, int B, int nb, int* order, TileDesc* tiles, int* n_tiles,
-                       int* seg_start, int max_tiles, int* hist) {
-    const int K = nb + 1, G = ceil_div(B, SORT_BLOCK);
-    BucketKey fn{bucket, nb};
-    k_sort_hist<<<G, SORT_BLOCK, 0, s>>>(fn, B, K, G, hist);
-    k_sort_scan<<<1, 1024, 0, s>>>(hist, K, G, B, seg_start);
-    k_sort_scatter<<<G, SORT_BLOCK, 0, s>>>(fn, B, K, G, hist, order);
-    k_make_tiles<<<1, 256, 0, s>>>(seg_start, K, tiles, n_tiles, tiles + max_tiles, n_tiles + 1);
-    return 4;
-}
-
-// items[2B] sorted by table slice; hist: scratch of (n_slices + 1) * ceil(2B / 1024) ints; seg: [n_slices + 2]
-int launch_item_sort(cudaStream_t s, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A, int N,
-                     int rows_per_slice, int n_persp, int* items, int* hist, int* seg) {
-    int n_slices = ceil_div(N, rows_per_slice);
-    if (n_slices + 1 > SORT_MAX_KEYS) {  // too many slices for the small-key sort: coarser slices keep most of the locality
-        rows_per_slice = ceil_div(N, SORT_MAX_KEYS - 1);
-        n_slices = ceil_div(N, rows_per_slice);
-    }
-    const int n = n_persp * B, K = n_slices + 1, G = ceil_div(n, SORT_BLOCK);
-    ItemKey fn{idx_stm, idx_nstm, nnz, B, A, N, rows_per_slice, n_slices};
-    k_sort_hist<<<G, SORT_BLOCK, 0, s>>>(fn, n, K, G, hist);
-    k_sort_scan<<<1, 1024, 0, s>>>(hist, K, G, n, seg);
-    k_sort_scatter<<<G, SORT_BLOCK, 0, s>>>(fn, n, K, G, hist, items);
-    return 3;
-}
 
 // Both sorts of a step in four launches: positions by bucket (order, tiles, units) and items by table slice.
 // hist: scratch of (nb + 1) * ceil(B / 1024) + (slices + 1) * ceil(n_persp * B / 1024) ints.
