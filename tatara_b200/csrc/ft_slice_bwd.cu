@@ -137,9 +137,13 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
     // pass 1: per-warp histogram (two 16-bit cells per shared-memory word, bumped by 32-bit atomics; a cell never
     // reaches 65536, so no carry crosses into its neighbour)
     unsigned* my_hist32 = reinterpret_cast<unsigned*>(my_hist);
-    for (int e = lane; e < n_e; e += 32) {
-        const unsigned code = cw[e];
-        if (code < (unsigned)rps) atomicAdd(my_hist32 + (code >> 1), 1u << ((code & 1u) * 16u));
+    for (int e0 = lane; e0 < n_e; e0 += 8 * 32) {  // eight loads in flight, then their atomics
+        unsigned code[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) code[u] = e0 + 32 * u < n_e ? cw[e0 + 32 * u] : 0xFFFFu;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (code[u] < (unsigned)rps) atomicAdd(my_hist32 + (code[u] >> 1), 1u << ((code[u] & 1u) * 16u));
     }
     __syncthreads();
 
