@@ -187,13 +187,15 @@ int tb_adam_clamp_bench(int device, float* w, float* m, float* v, const float* g
  * No counterpart in the reference (its trainers allocate their workspace in the constructor).
  * For hosts that must not allocate device memory once they run — a framework whose allocator owns the
  * whole GPU, a process with a fixed memory plan — this variant of the FT backward keeps the working
- * memory of the inverse index in a static device array inside the library (about 14.7 MB per GPU, held
- * until exit) and calls no cudaMalloc / cudaFree.  ALL pointers are DEVICE memory owned by the caller;
+ * memory of the inverse index and of the long-list partial sums in a static device array inside the
+ * library (about 21.5 MB per GPU, held until exit) and calls no cudaMalloc / cudaFree.  ALL pointers are DEVICE memory owned by the caller;
  * the work is enqueued on `stream` (a cudaStream_t, NULL = default stream) and not synchronised.
  * Limits: ft_in <= TB_STATIC_SCRATCH_MAX_FT_IN and batch * max_active <= TB_STATIC_SCRATCH_MAX_PAIRS;
  * beyond them the call fails and writes the reason to err (may be NULL).  Calls share the one array:
  * never let two of them overlap on a GPU.  The first call on a device resolves the array's address;
- * issue it before any stream capture.  Same result as tb_ft_backward_bench. */
+ * issue it before any stream capture.  d_dft and d_grad must be 16-byte aligned (rows move as 128-bit
+ * vectors).  Same kernels and same summation order as tb_ft_backward_bench (lists of more than 4096 entries are
+ * summed in parts of 4096), so the two agree bit for bit. */
 #define TB_STATIC_SCRATCH_MAX_FT_IN 131072
 #define TB_STATIC_SCRATCH_MAX_PAIRS 655360
 int tb_ft_backward_static_scratch(const float* d_dft, const int32_t* d_indices, const int32_t* d_nnz, int batch,

@@ -76,9 +76,6 @@ static inline size_t inverse_index_counts_len(int N) { return 4 * (size_t)N + 1 
 // run_if (here and below): NULL, or a device flag; the launched kernels return at once while it is 0
 int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, const int* idx_nstm, const int* nnz, int B, int A,
                          int N, int n_persp, int* counts, int* offsets, int* cursor, int* lists);
-// one block per feature row, whatever the length of its list
-int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
-                       const int* lists, int B, int A, int N, int F, int n_persp, float* grad);
 // long lists are cut into parts summed by separate blocks; plan: [2 + 2 * max_work + 3 * N] ints,
 // partial: [max_work][F] floats with max_work = ft_backward_max_work(B, A, n_persp)
 int ft_backward_max_work(int B, int A, int n_persp);

@@ -648,59 +648,16 @@ int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, 
     k_lists_sort_short<<<(int)(run_if && (warps * 32 + 255) / 256 > 148 * 32 ? 148 * 32 : (warps * 32 + 255) / 256), 256, 0, s>>>(offsets, N, n_persp, B, A, lists, long_queue, long_count, run_if);
     int words = (B + 31) / 32;
     if ((size_t)words * 4 > 160 * 1024) words = 0;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(k_lists_sort_long, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        attr_set = true;
-    }
+    // per device and cheap: set before every launch (a process may drive several GPUs)
+    cudaFuncSetAttribute(k_lists_sort_long, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     k_lists_sort_long<<<148 * 4, 256, (size_t)words * 4, s>>>(offsets, N, B, A, lists, scratch, long_queue, long_count, words, run_if);
     return 6;
 }
 
 // ------------------------------------------------------------------------------------------------
-// backward: one block per feature row, one thread per float4 column.  The row of the gradient is
-// written exactly once per step (stm list first, then nstm list, each in ascending position order —
-// the accumulation order of sparse_ft_backward_cpu called for stm then nstm).
-// ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(512) k_ft_backward(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
-                                                       const int* __restrict__ offsets, const int* __restrict__ lists,
-                                                       int B, int A, int N, int F, int n_persp, float* __restrict__ grad) {
-    const int f = blockIdx.x;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
-    const int row4 = F >> 2;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < n_persp; ++p) {
-        const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
-        const int* __restrict__ L = lists + (size_t)p * B * A;
-        const float4* __restrict__ d = reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm);
-        for (int j = beg; j < end; j += 8) {
-            // unconditional loads (a slot past the end re-reads the last row and is dropped below), so that all
-            // eight row loads are in flight together
-            int bi[8];
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) bi[u] = __ldg(L + min(j + u, end - 1));
-#pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldg(d + (size_t)bi[u] * row4 + c);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (j + u < end) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
-            }
-        }
-    }
-    reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
-}
-
-int launch_ft_backward(cudaStream_t s, const float* dft_stm, const float* dft_nstm, const int* offsets,
-                       const int* lists, int B, int A, int N, int F, int n_persp, float* grad) {
-    const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
-    // a gated launch (run_if) normally returns at once: a small grid of row-striding blocks keeps that cheap
-    k_ft_backward<<<dim3(N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad);
-    return 1;
-}
-
-// ------------------------------------------------------------------------------------------------
-// backward with list splitting.  A feature that is active in very many positions (the king square of a
+// backward: a block per feature row, a thread per float4 column.  The row of the gradient is written exactly once per
+// step (stm list first, then nstm list, each in ascending position order: the accumulation order of
+// sparse_ft_backward_cpu called for stm then nstm), with list splitting: a feature that is active in very many positions (the king square of a
 // king bucket, a pawn in hand) makes one block walk a list of thousands of rows; with real, skewed data such
 // lists reach tens of thousands of entries and would set the kernel's run time on their own.  Features whose
 // lists (stm + nstm) exceed BWD_PART entries are cut into parts of BWD_PART entries; every part is summed

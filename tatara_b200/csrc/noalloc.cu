@@ -9,7 +9,7 @@
 //
 // tb_ft_backward_static_scratch therefore keeps that working memory in a file-scope __device__ array of a
 // fixed size.  It calls no cudaMalloc / cudaFree and no allocating library routine.  The price:
-//   - every GPU on which this library's device code is used holds the array (about 14.7 MB) from that first
+//   - every GPU on which this library's device code is used holds the array (about 21.5 MB) from that first
 //     use until the process exits;
 //   - sizes are capped: ft_in <= TB_STATIC_SCRATCH_MAX_FT_IN rows, batch * max_active <=
 //     TB_STATIC_SCRATCH_MAX_PAIRS index slots; larger problems are refused with an error text;
@@ -27,10 +27,14 @@
 
 #define MAX_FT_IN TB_STATIC_SCRATCH_MAX_FT_IN
 #define MAX_PAIRS TB_STATIC_SCRATCH_MAX_PAIRS
+#define MAX_FT_OUT 4096
 // layout expected by launch_inverse_index: histogram + long-list queue + scan sums, offsets [2(N + 1)],
-// cursors [2N], lists + sort scratch [4P]
+// cursors [2N], lists + sort scratch [4P]; then what launch_ft_backward_split needs to cut long lists into parts:
+// its plan [2 + 2 * max_work + 3N] and the partial rows [max_work][F]
 #define COUNTS_INTS (4 * MAX_FT_IN + 1 + 2 * (MAX_FT_IN / 2048 + 2))
-#define SCRATCH_INTS (COUNTS_INTS + 4 * MAX_FT_IN + 2 + 4 * MAX_PAIRS + 64)
+#define MAX_WORK (2 * (MAX_PAIRS / 4096) + 2)   /* ft_backward_max_work at the slot limit */
+#define PLAN_INTS (2 + 2 * MAX_WORK + 3 * MAX_FT_IN)
+#define SCRATCH_INTS (COUNTS_INTS + 4 * MAX_FT_IN + 2 + 4 * MAX_PAIRS + PLAN_INTS + MAX_WORK * MAX_FT_OUT + 64)
 
 // In host code this name is only a handle for the runtime, not a device address: it must never be passed
 // to a kernel.  The address comes from cudaGetSymbolAddress below.
@@ -54,8 +58,10 @@ extern "C" int tb_ft_backward_static_scratch(const float* d_dft, const int32_t* 
         return report(err, err_len, TB_ERR_INVALID_ARGUMENT, "a device pointer is NULL");
     if (batch < 1 || max_active < 1 || ft_in < 1)
         return report(err, err_len, TB_ERR_INVALID_ARGUMENT, "batch, max_active and ft_in must be positive");
-    if (ft_out < 128 || ft_out % 128 != 0 || ft_out > 4096)
+    if (ft_out < 128 || ft_out % 128 != 0 || ft_out > MAX_FT_OUT)
         return report(err, err_len, TB_ERR_INVALID_ARGUMENT, "ft_out must be a multiple of 128 in [128, 4096] (got %lld)", ft_out);
+    if (((uintptr_t)d_dft | (uintptr_t)d_grad) & 15)
+        return report(err, err_len, TB_ERR_INVALID_ARGUMENT, "d_dft and d_grad must be 16-byte aligned (rows are moved as 128-bit vectors)");
     if (ft_in > MAX_FT_IN)
         return report(err, err_len, TB_ERR_INVALID_ARGUMENT,
                       "ft_in %lld exceeds the static scratch limit of %lld rows (use the allocating entry points)", ft_in, MAX_FT_IN);
@@ -86,12 +92,16 @@ extern "C" int tb_ft_backward_static_scratch(const float* d_dft, const int32_t* 
     int* offsets = counts + inverse_index_counts_len(ft_in);    // [2(N + 1)]
     int* cursor = offsets + 2 * (N + 1);      // [2N]
     int* lists = cursor + 2 * N;              // [4P]
-    (void)P;
+    int* plan = lists + 4 * P;                // [2 + 2 * max_work + 3N]
+    const size_t max_work = (size_t)ft_backward_max_work(batch, max_active, 1);  // <= MAX_WORK by the slot limit
+    // the partial rows start on a 16-byte boundary (they are read and written as float4)
+    float* partial = reinterpret_cast<float*>(plan + (2 + 2 * max_work + 3 * N + 3) / 4 * 4);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // launch_inverse_index clears the histogram and the long-list counter itself; offsets, cursors and lists are
-    // fully rewritten for the rows and slots this call uses
+    // launch_inverse_index clears the histogram and the long-list counter itself, launch_ft_backward_split its two
+    // counters; offsets, cursors, lists, plan and partial rows are rewritten for the rows and slots this call uses
     launch_inverse_index(s, nullptr, d_indices, d_indices, d_nnz, batch, max_active, ft_in, 1, counts, offsets, cursor, lists);
-    launch_ft_backward(s, d_dft, d_dft, offsets, lists, batch, max_active, ft_in, ft_out, 1, d_grad);
+    // the same launcher as tb_ft_backward_bench: lists of more than 4096 entries are summed in parts of 4096
+    launch_ft_backward_split(s, nullptr, d_dft, d_dft, offsets, lists, batch, max_active, ft_in, ft_out, 1, plan, partial, d_grad);
     e = cudaGetLastError();
     if (e != cudaSuccess) {
         if (err && err_len) snprintf(err, err_len, "kernel launch: %s", cudaGetErrorString(e));

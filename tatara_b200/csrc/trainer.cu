@@ -30,8 +30,6 @@
 // slots wins, a shorter last part (whose communication nothing hides) breaking near ties.  Measured on two B200s at
 // 45 slices x 48 strips: 5 parts 4.81 ms per step, 3 parts 4.97, 4 parts 4.99, 6 parts 4.95, 8 parts 5.05.
 static int ar_parts_for(int n_slices, int strips, int n_sm) {
-    static const int forced = getenv("TATARA_DP_PARTS") ? atoi(getenv("TATARA_DP_PARTS")) : 0;  // tuning aid
-    if (forced >= 1 && forced <= AR_PARTS_MAX && n_slices >= forced) return forced;
     int best = 1;
     double best_cost = 1e30;
     for (int parts = 3; parts <= AR_PARTS_MAX; ++parts) {
@@ -156,6 +154,7 @@ struct tb_trainer {
     bool opt_begun = false;        // this step's optimizer scalars are out (step_count already incremented)
     bool ft_rows_updated = false;  // this step's real FT rows were updated behind their all-reduces
     bool slice_fwd = false;  // this step's forward ran slice-resident (its row codes are in fwd_work)
+    bool poisoned = false;   // a step failed after its optimizer had begun: parameters are part old, part new
     float* bwd_partial = nullptr;
     int last_n = 0;
     // loss ring (AsyncLossRing, trainer_common.rs:909-1000)
@@ -337,7 +336,7 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     const bool ls = c.arch == TB_ARCH_LAYERSTACK;
     const float* table = c.ft_factorize ? t->comb : t->groups[0].w;
     t->last_n = B;
-    if (backward) { t->opt_begun = false; t->ft_rows_updated = false; }  // a step that failed half way leaves no state behind
+    if (backward) { t->opt_begun = false; t->ft_rows_updated = false; }
     { PhaseScope p(t, PH_SORT);
       // positions by bucket (order, tiles, units) and items of both perspectives by the king-bucket slice of the FT table
       int n = launch_step_sorts(t->stream, ls ? d.bucket : nullptr, B, ls ? c.num_buckets : 0, t->order, t->tiles, t->n_tiles,
@@ -596,12 +595,22 @@ int loss_ring_next(tb_trainer* t, double* out) {
 }
 
 int step_on(tb_trainer* t, const DevBatch& d, float lr, float lambda, const tb_loss* loss, double* loss_prev) {
+    if (t->poisoned)
+        return fail(t, TB_ERR_CUDA, "an earlier step failed after its optimizer had begun; the parameters are inconsistent: "
+                                    "destroy the handle and restore a checkpoint");
     int rc = run_forward(t, d, loss, lambda, 1);
     if (rc == TB_OK) rc = run_backward(t, d, lr);
     if (rc == TB_OK) rc = run_allreduce(t);
-    if (rc == TB_OK) rc = run_optimizer(t, lr);
+    // Up to here a failed step leaves the parameters and step_count untouched, unless the data-parallel pipeline had
+    // already sent the optimizer behind the first gradient parts (opt_begun): then some FT rows carry this step's update
+    // and a retry would apply it twice, so the handle refuses further steps.
+    if (rc != TB_OK && t->opt_begun) t->poisoned = true;
+    if (rc == TB_OK) {
+        rc = run_optimizer(t, lr);
+        if (rc == TB_OK && cudaGetLastError() != cudaSuccess) rc = fail(t, TB_ERR_CUDA, "a kernel launch of the step failed");
+        if (rc != TB_OK) t->poisoned = true;
+    }
     if (rc != TB_OK) return rc;
-    CU(t, cudaGetLastError());
     rc = loss_ring_next(t, loss_prev);
     profile_collect(t);
     return rc;

@@ -66,6 +66,39 @@ def test_static_scratch_matches_allocating_entry_point_twice():
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), "call %d differs" % call
 
 
+def test_static_scratch_long_list_is_summed_like_the_allocating_entry_point():
+    """A feature held by every position: its list (16 384 entries) is cut into parts of 4096 by both entry points,
+    so they agree bit for bit; against the one-by-one sum of the CPU oracle the row agrees to rounding."""
+    torch = pytest.importorskip("torch")
+    import oracle_lib as O
+    from helpers import assert_close_scaled
+    lib = tb.load_library()
+    torch.cuda.set_device(0)
+    B, F, N, A = 16384, 256, 64, 4
+    rng = np.random.default_rng(5)
+    dft = (rng.standard_normal((B, F)) * 1e-3).astype(np.float32)
+    idx = np.stack([np.full(B, 7), rng.integers(8, N, B), rng.integers(8, N, B), np.full(B, -1)], 1).astype(np.int32)
+    nnz = np.full(B, 3, np.int32)
+    want = _reference(dft, idx, nnz, N, F, A)
+    d_dft, d_idx, d_nnz = torch.from_numpy(dft).cuda(), torch.from_numpy(idx).cuda(), torch.from_numpy(nnz).cuda()
+    d_grad = torch.full((N, F), 7.0, dtype=torch.float32, device="cuda")
+    err = C.create_string_buffer(256)
+    rc = lib.tb_ft_backward_static_scratch(d_dft.data_ptr(), d_idx.data_ptr(), d_nnz.data_ptr(), B, F, N, A,
+                                           d_grad.data_ptr(), None, err, 256)
+    assert rc == 0, err.value
+    torch.cuda.synchronize()
+    got = d_grad.cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    seq = np.zeros((N, F), np.float32)
+    O.lib().ora_sparse_ft_backward(dft.reshape(-1), idx.reshape(-1), seq.reshape(-1), B, F, N, A)
+    assert_close_scaled(got, seq, 1e-5, "long list against the sequential sum")
+    assert np.array_equal(got[8:].view(np.uint32), seq[8:].view(np.uint32))      # short lists: the sequential sum itself
+    # a misaligned buffer is refused before anything is launched
+    rc = lib.tb_ft_backward_static_scratch(d_dft.data_ptr() + 4, d_idx.data_ptr(), d_nnz.data_ptr(), B - 16, F, N, A,
+                                           d_grad.data_ptr(), None, err, 256)
+    assert rc == -1 and b"16-byte aligned" in err.value
+
+
 def test_static_scratch_rejects_sizes_beyond_its_array():
     lib = tb.load_library()
     err = C.create_string_buffer(256)
