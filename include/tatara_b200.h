@@ -126,6 +126,15 @@ int tb_set_step_count(tb_trainer* t, uint64_t step_count);
  * (trainer_simple.rs:742).  n_pos == 0 returns loss 0 without work. */
 int tb_train_step(tb_trainer* t, const tb_batch* batch, float lr, float wdl_lambda, const tb_loss* loss,
                   double* loss_prev);
+/* train_step fed with PackedSfenValue records instead of extracted indices: `psv` is n_pos 40-byte records in HOST
+ * memory (crates/shogi-format/src/packed_sfen.rs:251-271); 40 bytes per position cross the bus and the work of the
+ * reference's dataloader workers (decode, feature extraction of both perspectives, kingrank9 bucket, score and wdl:
+ * crates/nnue-train/src/dataloader.rs:444-500, 1303-1407) runs on the device on the copy stream, overlapped with the
+ * previous step.  feature_set as in tb_psv_extract; it must be the set the trainer was created for.  The step is
+ * bit-identical to tb_train_step on the batch tb_psv_extract returns for the same records.  per_pos_norm is the
+ * reference's 1 / (n_pos * world_size). */
+int tb_train_step_psv(tb_trainer* t, int feature_set, const uint8_t* psv, int n_pos, float lr, float wdl_lambda,
+                      const tb_loss* loss, double* loss_prev);
 /* flush_pending_loss: the lagged loss of the last step, then re-arms the ring */
 int tb_flush_pending_loss(tb_trainer* t, double* loss);
 /* validate_step -> GpuTrainer::validate (trainer_layerstack.rs:1963): forward + loss only, no state
@@ -182,6 +191,22 @@ int tb_ft_backward_bench(int device, const float* dft, const int32_t* indices, c
                          int batch, int ft_out, int ft_in, int max_active, int iters, float* grad, float* ms_per_iter);
 int tb_adam_clamp_bench(int device, float* w, float* m, float* v, const float* grad, int64_t n, float lr,
                         float decay, float min_w, float max_w, int iters, float* ms_per_iter);
+
+/* The three FT kernels on DEVICE-resident data, one perspective (the reference's microbenchmark protocol:
+ * a fixed in-memory batch, warm-up, timed launches, bins/nnue_train/src/native_bench.rs:550-576,
+ * docs/native-cuda-benchmark.md:11-33).  Only the index lists come from the host; table, incoming gradient rows and
+ * moments are filled on the device.  Every launch group is timed with its own pair of CUDA events; with flush_l2 a
+ * 256 MB buffer is written before each one.  fwd / bwd / adam: the generic kernels (L2 gather; global inverse index +
+ * per-row sums; AdamW with the +-32767/127 clamp).  With rows_per_slice > 0 and king-sliced lists (every row of a
+ * position inside one slice of rows_per_slice table rows) the slice-resident kernels of the training step are timed
+ * too, sorts and plans included; otherwise those two fields are negative. */
+typedef struct tb_ft_microbench_result {
+    float fwd_ms, bwd_ms, adam_ms;
+    float fwd_slice_ms, bwd_slice_ms;
+    int32_t iters;
+} tb_ft_microbench_result;
+int tb_ft_microbench(int device, const int32_t* indices, const int32_t* nnz, int batch, int ft_out, int ft_in,
+                     int rows_per_slice, int max_active, int iters, int flush_l2, tb_ft_microbench_result* out);
 
 /* ---- FT weight gradient without any allocation -------------------------------------------
  * No counterpart in the reference (its trainers allocate their workspace in the constructor).

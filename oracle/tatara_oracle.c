@@ -685,6 +685,128 @@ int ora_extract_active_features(int feature_set, const ora_board* b, int32_t* st
     return count;
 }
 
+/* ---- synthetic PackedSfenValue records --------------------------------------------------------------------------
+ * The reference has no encoder and no generator (its benchmark data is a private teacher file).  The benchmark's
+ * stand-in is a seeded generator whose draw order is part of its definition; it is restated here so that the CPU arm
+ * of the benchmark and the tests can produce the very same records without the CUDA library.  The bit stream is the
+ * inverse of the decoder above (packed_sfen.rs:387-448).
+ * Per record, from one SplitMix64 stream: side to move (low bit of a draw), black king square (uniform of 81), white
+ * king square (uniform of the other 80); then each of the 38 other pieces in the order 18 pawns, 4 lances, 4 knights,
+ * 4 silvers, 4 golds, 2 bishops, 2 rooks: on the board with p = 0.85 (uniform empty square in square order, uniform
+ * owner, promoted with p = 0.1 unless gold), else in the hand of a uniform side; score = round-to-even(400 * N(0,1))
+ * by Box-Muller, clipped to +-3000; result: draw with p = 0.05, else win with p = sigmoid(score / 600), else loss;
+ * ply uniform in 1..256. */
+typedef struct { uint64_t s; } sm64;
+static uint64_t sm64_next(sm64* r) {
+    uint64_t z = (r->s += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+static double sm64_unit(sm64* r) { return (double)(sm64_next(r) >> 11) * (1.0 / 9007199254740992.0); }
+static uint32_t sm64_below(sm64* r, uint32_t n) { return (uint32_t)(((sm64_next(r) >> 32) * (uint64_t)n) >> 32); }
+
+static void put_bits(uint8_t* data, int* cur, uint32_t v, int n) {
+    for (int i = 0; i < n; ++i, ++*cur)
+        if ((v >> i) & 1u) data[*cur >> 3] |= (uint8_t)(1u << (*cur & 7));
+}
+static int huff_id_for(uint8_t base_pt) {
+    for (int id = 1; id < 8; ++id)
+        if (HUFF_PT[id] == base_pt) return id;
+    return 0;
+}
+static uint8_t unpromote_pt(uint8_t pt, int* promoted) {
+    static const uint8_t base_of[6] = {PT_PAWN, PT_LANCE, PT_KNIGHT, PT_SILVER, PT_BISHOP, PT_ROOK};
+    static const uint8_t pro_of[6] = {PT_PRO_PAWN, PT_PRO_LANCE, PT_PRO_KNIGHT, PT_PRO_SILVER, PT_HORSE, PT_DRAGON};
+    *promoted = 0;
+    for (int i = 0; i < 6; ++i)
+        if (pt == pro_of[i]) { *promoted = 1; return base_of[i]; }
+    return pt;
+}
+
+int ora_psv_encode(const ora_board* b, uint8_t* out) {
+    memset(out, 0, 40);
+    int cur = 0;
+    put_bits(out, &cur, b->side_to_move & 1u, 1);
+    put_bits(out, &cur, b->black_king_sq, 7);
+    put_bits(out, &cur, b->white_king_sq, 7);
+    for (int sq = 0; sq < 81; ++sq) {
+        if (sq == b->black_king_sq || sq == b->white_king_sq) continue;
+        if (b->board_pt[sq] == PT_NONE) { put_bits(out, &cur, 0, 1); continue; }
+        int promoted;
+        int id = huff_id_for(unpromote_pt(b->board_pt[sq], &promoted));
+        if (id == 0) return -1;
+        put_bits(out, &cur, HUFF_PATTERN[id], HUFF_BITS[id]);
+        if (id != HUFF_GOLD) put_bits(out, &cur, (uint32_t)promoted, 1);
+        put_bits(out, &cur, b->board_color[sq] & 1u, 1);
+        if (cur > 256) return -1;
+    }
+    static const uint8_t slot_pt[7] = {PT_PAWN, PT_LANCE, PT_KNIGHT, PT_SILVER, PT_GOLD, PT_BISHOP, PT_ROOK};
+    for (int color = 0; color < 2; ++color)
+        for (int slot = 0; slot < 7; ++slot)
+            for (int k = 0; k < b->hand[color][slot]; ++k) {
+                int id = huff_id_for(slot_pt[slot]);
+                put_bits(out, &cur, (uint32_t)HUFF_PATTERN[id] >> 1, HUFF_BITS[id] - 1);
+                if (id != HUFF_GOLD) put_bits(out, &cur, 0, 1); /* piece-box flag */
+                put_bits(out, &cur, (uint32_t)color, 1);
+                if (cur > 256) return -1;
+            }
+    out[32] = (uint8_t)(b->score & 0xff);
+    out[33] = (uint8_t)(((uint16_t)b->score >> 8) & 0xff);
+    out[36] = (uint8_t)(b->ply & 0xff);
+    out[37] = (uint8_t)((b->ply >> 8) & 0xff);
+    out[38] = (uint8_t)b->result;
+    return 0;
+}
+
+int ora_psv_synthesize(uint64_t seed, size_t n_records, uint8_t* out) {
+    static const uint8_t kinds[7] = {PT_PAWN, PT_LANCE, PT_KNIGHT, PT_SILVER, PT_GOLD, PT_BISHOP, PT_ROOK};
+    static const int copies[7] = {18, 4, 4, 4, 4, 2, 2};
+    sm64 rng = {seed};
+    for (size_t r = 0; r < n_records; ++r) {
+        ora_board b;
+        memset(&b, 0, sizeof b);
+        b.side_to_move = (uint8_t)(sm64_next(&rng) & 1u);
+        b.black_king_sq = (uint8_t)sm64_below(&rng, 81);
+        int wk = (int)sm64_below(&rng, 80);
+        if (wk >= b.black_king_sq) ++wk;
+        b.white_king_sq = (uint8_t)wk;
+        b.board_pt[b.black_king_sq] = PT_KING; b.board_color[b.black_king_sq] = 0;
+        b.board_pt[wk] = PT_KING; b.board_color[wk] = 1;
+        int empties = 79;
+        for (int t = 0; t < 7; ++t)
+            for (int k = 0; k < copies[t]; ++k) {
+                if (sm64_unit(&rng) < 0.85) {
+                    int pick = (int)sm64_below(&rng, (uint32_t)empties), sq = 0;
+                    for (;; ++sq)
+                        if (b.board_pt[sq] == PT_NONE && pick-- == 0) break;
+                    int owner = (int)(sm64_next(&rng) & 1u);
+                    uint8_t placed = kinds[t];
+                    if (kinds[t] != PT_GOLD && sm64_unit(&rng) < 0.1) placed = promote_pt(kinds[t]);
+                    b.board_pt[sq] = placed;
+                    b.board_color[sq] = (uint8_t)owner;
+                    --empties;
+                } else {
+                    int owner = (int)(sm64_next(&rng) & 1u);
+                    b.hand[owner][hand_slot(kinds[t])]++;
+                }
+            }
+        double u1 = sm64_unit(&rng);
+        if (u1 < 1e-300) u1 = 1e-300;
+        double u2 = sm64_unit(&rng);
+        double z = sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2);
+        long sc = lrint(z * 400.0);
+        if (sc > 3000) sc = 3000;
+        if (sc < -3000) sc = -3000;
+        b.score = (int16_t)sc;
+        if (sm64_unit(&rng) < 0.05) b.result = 0;
+        else b.result = sm64_unit(&rng) < 1.0 / (1.0 + exp(-(double)sc / 600.0)) ? 1 : -1;
+        b.ply = (uint16_t)(1 + sm64_below(&rng, 256));
+        if (ora_psv_encode(&b, out + 40 * r)) return -1;
+    }
+    return 0;
+}
+
 /* crates/shogi-features/src/kingrank9.rs:11-24 */
 int ora_kingrank9_bucket(const ora_board* b) {
     int friendly, enemy;

@@ -106,6 +106,9 @@ typedef struct {
 } ora_board;
 
 void ora_psv_decode(const uint8_t* psv40, ora_board* out);
+/* inverse of the decoder, and the benchmark's seeded synthetic record generator (see the .c file for its draw order) */
+int ora_psv_encode(const ora_board* b, uint8_t* psv40_out);
+int ora_psv_synthesize(uint64_t seed, size_t n_records, uint8_t* out);
 /* feature_set: 0 halfkp, 1 halfka-split, 2 halfka-merged, 3 halfka-hm-split, 4 halfka-hm-merged */
 int ora_feature_dims(int feature_set, int* king_buckets, int* piece_inputs, int* ft_in, int* max_active);
 int ora_extract_active_features(int feature_set, const ora_board* board, int32_t* stm_out,

@@ -41,6 +41,10 @@ class Loss(C.Structure):
     ]
 
 
+class MicrobenchResult(C.Structure):
+    _fields_ = [("fwd_ms", f), ("bwd_ms", f), ("adam_ms", f), ("fwd_slice_ms", f), ("bwd_slice_ms", f), ("iters", i32)]
+
+
 class Batch(C.Structure):
     _fields_ = [
         ("n_pos", i32), ("stm_indices", vp), ("nstm_indices", vp), ("nnz", vp), ("bucket_idx", vp), ("score", vp),
@@ -61,6 +65,7 @@ SIGNATURES = {
     "tb_get_step_count": (C.c_int, [vp, C.POINTER(C.c_uint64)]),
     "tb_set_step_count": (C.c_int, [vp, C.c_uint64]),
     "tb_train_step": (C.c_int, [vp, C.POINTER(Batch), f, f, C.POINTER(Loss), C.POINTER(C.c_double)]),
+    "tb_train_step_psv": (C.c_int, [vp, C.c_int, vp, C.c_int, f, f, C.POINTER(Loss), C.POINTER(C.c_double)]),
     "tb_flush_pending_loss": (C.c_int, [vp, C.POINTER(C.c_double)]),
     "tb_validate_step": (C.c_int, [vp, C.POINTER(Batch), f, C.POINTER(Loss), C.POINTER(C.c_double), vp]),
     "tb_read_fp16_clamp_count": (C.c_int, [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
@@ -81,6 +86,8 @@ SIGNATURES = {
     "tb_ft_forward_bench": (C.c_int, [C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, C.POINTER(f)]),
     "tb_ft_backward_bench": (C.c_int, [C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, C.POINTER(f)]),
     "tb_adam_clamp_bench": (C.c_int, [C.c_int, vp, vp, vp, vp, i64, f, f, f, f, C.c_int, C.POINTER(f)]),
+    "tb_ft_microbench": (C.c_int, [C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                   C.POINTER(MicrobenchResult)]),
     "tb_psv_extract": (C.c_int, [C.c_int, C.c_int, vp, i64, vp, vp, vp, vp, vp, vp]),
     "tb_psv_synthesize": (C.c_int, [C.c_uint64, i64, vp]),
     "tb_psv_encode": (C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),

@@ -105,6 +105,11 @@ int launch_step_sorts(cudaStream_t s, const int* bucket /*may be NULL*/, int B, 
 int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F);
 int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F);
 
+// psv.cu
+int launch_psv_extract(cudaStream_t s, int feature_set, const void* d_psv, long long n, int* stm, int* nstm, int* nnz,
+                       int* bucket, float* score, float* wdl);
+bool psv_feature_set_dims(int feature_set, int* ft_in, int* max_active);
+
 // dense_kernels.cu
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb /*[nb][l1][K] or NULL*/,

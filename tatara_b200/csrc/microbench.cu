@@ -1,0 +1,145 @@
+// FT kernels alone on device-resident data: the per-kernel microbenchmark of the reference's protocol
+// (bins/nnue_train/src/native_bench.rs:550-576: a fixed in-memory batch, warm-up, then timed launches), one
+// perspective: forward gather-sum, backward (inverse index + per-row sums), fused AdamW + clamp.
+// Only the index lists come from the host (their distribution is the benchmark's definition); table, gradient rows and
+// moments are filled on the device with a fixed pattern, since the kernels' timing does not depend on the values.
+#include "common.cuh"
+#include "ft_slice.cuh"
+#include "../../include/tatara_b200.h"
+
+#include <stdio.h>
+
+namespace {
+
+__global__ void k_fill_pattern(float* __restrict__ p, size_t n, float scale, unsigned salt) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        unsigned h = (unsigned)i * 2654435761u + salt;
+        h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+        p[i] = ((float)(h & 0xffffu) / 32768.0f - 1.0f) * scale;
+    }
+}
+
+__global__ void k_flush(float4* __restrict__ p, size_t n4) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
+        p[i] = make_float4(1.f, 2.f, 3.f, 4.f);
+}
+
+struct Timer {
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    float* flush = nullptr;
+    size_t flush_floats = 0;
+    double total = 0.0;
+    // one timed launch group: optional L2 flush before it (a write of a buffer larger than the L2), events around it
+    template <class Fn>
+    cudaError_t run(int iters, Fn fn) {
+        total = 0.0;
+        for (int i = -1; i < iters; ++i) {  // iteration -1 is the warm-up
+            if (flush) k_flush<<<148 * 8, 256>>>(reinterpret_cast<float4*>(flush), flush_floats / 4);
+            cudaEventRecord(e0, 0);
+            fn();
+            cudaEventRecord(e1, 0);
+            cudaError_t e = cudaEventSynchronize(e1);
+            if (e != cudaSuccess) return e;
+            float ms = 0.f;
+            cudaEventElapsedTime(&ms, e0, e1);
+            if (i >= 0) total += ms;
+        }
+        return cudaGetLastError();
+    }
+};
+
+}  // namespace
+
+extern "C" int tb_ft_microbench(int device, const int32_t* indices, const int32_t* nnz, int batch, int ft_out, int ft_in,
+                                int rows_per_slice, int max_active, int iters, int flush_l2, tb_ft_microbench_result* out) {
+    if (!indices || !nnz || !out || batch < 1 || ft_in < 1 || max_active < 1 || max_active > 256 || ft_out < 128 || ft_out % 128 != 0 ||
+        ft_out > 4096 || iters < 1 || batch > (1 << 20))
+        return TB_ERR_INVALID_ARGUMENT;
+    const size_t B = batch, F = ft_out, N = ft_in, A = max_active;
+    const int rps = rows_per_slice > 0 ? rows_per_slice : ft_in;
+    float *d_table = nullptr, *d_x = nullptr, *d_grad = nullptr, *d_m = nullptr, *d_v = nullptr, *d_part = nullptr;
+    int *d_idx = nullptr, *d_nnz = nullptr, *d_cnt = nullptr, *d_off = nullptr, *d_cur = nullptr, *d_lists = nullptr, *d_plan = nullptr;
+    int *d_order = nullptr, *d_ntiles = nullptr, *d_seg = nullptr, *d_hist = nullptr, *d_items = nullptr, *d_itemseg = nullptr;
+    int *d_fwd_work = nullptr, *d_bwd_work = nullptr;
+    TileDesc* d_tiles = nullptr;
+    Timer tm;
+    int rc = TB_OK;
+    const size_t max_work = (size_t)ft_backward_max_work(batch, max_active, 1);
+    const int max_tiles = (int)(B / TB_TILE_M) + TB_MAX_BUCKETS + 2;
+    const bool sliced = rows_per_slice > 0 && ft_forward_slice_supported(ft_out, ft_in, max_active, rps) &&
+                        ft_backward_slice_supported(ft_out, ft_in, max_active, rps);
+    OptScalars sc;
+    sc.lr = 1e-3f; sc.step_size = 1.f; sc.decay = 0.01f; sc.beta1 = 0.9f; sc.beta2 = 0.999f; sc.eps = 1e-8f;
+    sc.min_w = -32767.0f / 127.0f; sc.max_w = 32767.0f / 127.0f;  // the i16 range at QA = 127 (bins/nnue_train/src/arch.rs:122-131)
+    sc.alpha = 0.5f; sc.denom = 1; sc.lerp = 0;
+#define MB(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fprintf(stderr, "tb_ft_microbench: %s: %s\n", #call, cudaGetErrorString(e_)); rc = e_ == cudaErrorMemoryAllocation ? TB_ERR_OUT_OF_MEMORY : TB_ERR_CUDA; goto done; } } while (0)
+    MB(cudaSetDevice(device));
+    MB(cudaMalloc(&d_table, N * F * 4)); MB(cudaMalloc(&d_x, B * F * 4)); MB(cudaMalloc(&d_grad, N * F * 4));
+    MB(cudaMalloc(&d_m, N * F * 4)); MB(cudaMalloc(&d_v, N * F * 4));
+    MB(cudaMalloc(&d_idx, B * A * 4)); MB(cudaMalloc(&d_nnz, B * 4));
+    MB(cudaMalloc(&d_cnt, inverse_index_counts_len(ft_in) * 4)); MB(cudaMalloc(&d_off, 2 * (N + 1) * 4)); MB(cudaMalloc(&d_cur, 2 * N * 4));
+    MB(cudaMalloc(&d_lists, 4 * B * A * 4)); MB(cudaMalloc(&d_plan, (2 + 2 * max_work + 3 * N) * 4)); MB(cudaMalloc(&d_part, max_work * F * 4));
+    MB(cudaMemcpy(d_idx, indices, B * A * 4, cudaMemcpyHostToDevice));
+    MB(cudaMemcpy(d_nnz, nnz, B * 4, cudaMemcpyHostToDevice));
+    k_fill_pattern<<<148 * 8, 256>>>(d_table, N * F, 0.05f, 1u);
+    k_fill_pattern<<<148 * 8, 256>>>(d_m, N * F, 1e-4f, 2u);
+    MB(cudaMemset(d_v, 0, N * F * 4));
+    if (flush_l2) {
+        tm.flush_floats = (size_t)64 << 20;  // 256 MB, twice the L2
+        MB(cudaMalloc(&tm.flush, tm.flush_floats * 4));
+    }
+    MB(cudaEventCreate(&tm.e0)); MB(cudaEventCreate(&tm.e1));
+    out->iters = iters;
+    out->fwd_slice_ms = out->bwd_slice_ms = -1.0f;
+
+    // generic path: L2-gather forward, global inverse index + per-row sums
+    MB(tm.run(iters, [&] { launch_ft_forward(0, 0, d_table, d_idx, d_idx, d_nnz, nullptr, d_x, d_x, nullptr, nullptr, batch, ft_out, ft_in, max_active, 1.f, 1); }));
+    out->fwd_ms = (float)(tm.total / iters);
+    k_fill_pattern<<<148 * 8, 256>>>(d_x, B * F, 1e-3f, 3u);  // the incoming gradient rows
+    MB(tm.run(iters, [&] {
+        launch_inverse_index(0, nullptr, d_idx, d_idx, d_nnz, batch, max_active, ft_in, 1, d_cnt, d_off, d_cur, d_lists);
+        launch_ft_backward_split(0, nullptr, d_x, d_x, d_off, d_lists, batch, max_active, ft_in, ft_out, 1, d_plan, d_part, d_grad);
+    }));
+    out->bwd_ms = (float)(tm.total / iters);
+    MB(tm.run(iters, [&] { launch_radam(0, d_table, d_m, d_v, d_grad, nullptr, (int64_t)(N * F), sc); }));
+    out->adam_ms = (float)(tm.total / iters);
+
+    if (sliced) {
+        // king-sliced index lists: the slice-resident kernels of the training step, with everything they need from the
+        // raw lists (item sort, run plan, row codes; chunk inverse index for the backward)
+        const int n_keys = ceil_div(ft_in, rps) + 1;
+        MB(cudaMalloc(&d_order, B * 4)); MB(cudaMalloc(&d_ntiles, 2 * 4)); MB(cudaMalloc(&d_seg, (TB_MAX_BUCKETS + 3) * 4));
+        MB(cudaMalloc(&d_tiles, ((size_t)max_tiles + sort_max_units(max_tiles)) * sizeof(TileDesc)));
+        MB(cudaMalloc(&d_hist, ((size_t)128 * (B / 1024 + 2) + (size_t)(TB_MAX_BUCKETS + 1) * (B / 1024 + 2)) * 4));
+        MB(cudaMalloc(&d_items, B * 4)); MB(cudaMalloc(&d_itemseg, 130 * 4));
+        MB(cudaMalloc(&d_fwd_work, ft_forward_slice_work_ints(batch, n_keys, max_active) * 4));
+        MB(cudaMalloc(&d_bwd_work, ft_backward_slice_ints(batch, max_active, rps) * 4));
+        k_fill_pattern<<<148 * 8, 256>>>(d_table, N * F, 0.05f, 1u);
+        MB(tm.run(iters, [&] {
+            launch_step_sorts(0, nullptr, batch, 0, d_order, d_tiles, d_ntiles, d_seg, max_tiles, d_idx, d_idx, d_nnz, max_active, ft_in, rps, 1,
+                              d_items, d_itemseg, d_hist);
+            launch_ft_forward_slice(0, 0, d_table, d_idx, d_idx, d_nnz, nullptr, d_x, d_x, nullptr, d_items, d_itemseg, d_fwd_work, batch,
+                                    ft_out, ft_in, max_active, rps, 1.f, 1);
+        }));
+        int outside = 0;
+        MB(cudaMemcpy(&outside, ft_slice_outside_flag(d_fwd_work, batch, ft_in, rps), 4, cudaMemcpyDeviceToHost));
+        if (!outside) {
+            out->fwd_slice_ms = (float)(tm.total / iters);
+            k_fill_pattern<<<148 * 8, 256>>>(d_x, B * F, 1e-3f, 3u);
+            MB(tm.run(iters, [&] {
+                launch_inverse_slice(0, d_itemseg, d_fwd_work, d_bwd_work, batch, max_active, ft_in, rps, 1);
+                launch_ft_backward_slice(0, d_x, d_x, d_fwd_work, d_bwd_work, batch, max_active, ft_in, ft_out, rps, 1, 0, ceil_div(ft_in, rps), d_grad);
+            }));
+            out->bwd_slice_ms = (float)(tm.total / iters);
+        }
+    }
+done:
+    cudaFree(d_table); cudaFree(d_x); cudaFree(d_grad); cudaFree(d_m); cudaFree(d_v); cudaFree(d_part); cudaFree(d_idx); cudaFree(d_nnz);
+    cudaFree(d_cnt); cudaFree(d_off); cudaFree(d_cur); cudaFree(d_lists); cudaFree(d_plan); cudaFree(d_order); cudaFree(d_ntiles);
+    cudaFree(d_seg); cudaFree(d_hist); cudaFree(d_items); cudaFree(d_itemseg); cudaFree(d_fwd_work); cudaFree(d_bwd_work); cudaFree(d_tiles);
+    cudaFree(tm.flush);
+    if (tm.e0) cudaEventDestroy(tm.e0);
+    if (tm.e1) cudaEventDestroy(tm.e1);
+    return rc;
+#undef MB
+}

@@ -385,6 +385,26 @@ extern "C" int tb_psv_synthesize(uint64_t seed, int64_t n_records, uint8_t* out)
     return TB_OK;
 }
 
+// Device-to-device form for the trainer: records already in device memory -> step inputs in device memory, on `s`.
+// Returns the number of kernels launched, or -1 for an unknown feature set.
+int launch_psv_extract(cudaStream_t s, int feature_set, const void* d_psv, long long n, int* stm, int* nstm, int* nnz,
+                       int* bucket, float* score, float* wdl) {
+    FsSpec spec;
+    if (!fs_spec(feature_set, &spec)) return -1;
+    if (n <= 0) return 0;
+    k_psv_extract<<<(unsigned)((n + 127) / 128), 128, 0, s>>>(static_cast<const unsigned*>(d_psv), n, spec, stm, nstm, nnz, bucket, score, wdl);
+    return 1;
+}
+
+// dimensions of a feature set id: rows of the FT table and slots per perspective (feature_set.rs:1031-1038)
+bool psv_feature_set_dims(int feature_set, int* ft_in, int* max_active) {
+    FsSpec spec;
+    if (!fs_spec(feature_set, &spec)) return false;
+    *ft_in = (spec.mirror ? 45 : 81) * spec.piece_inputs;
+    *max_active = spec.max_active;
+    return true;
+}
+
 extern "C" int tb_psv_extract(int device, int feature_set, const uint8_t* psv, int64_t n, int32_t* stm_indices,
                               int32_t* nstm_indices, int32_t* nnz, int32_t* bucket, float* score, float* wdl) {
     FsSpec spec;

@@ -132,6 +132,8 @@ struct tb_trainer {
     // inputs
     DevBatch ring[2], slots[TB_NUM_SLOTS];
     HostStage stage[2];
+    unsigned char* ring_psv[2] = {nullptr, nullptr};   // device: the 40-byte records of a batch fed as PackedSfenValue
+    unsigned char* stage_psv[2] = {nullptr, nullptr};  // pinned staging for pageable record buffers
     cudaEvent_t ev_upload[2] = {nullptr, nullptr}, ev_consumed[2] = {nullptr, nullptr};
     bool upload_pending[2] = {false, false}, consumed_pending[2] = {false, false};
     uint64_t ring_step = 0;
@@ -636,6 +638,35 @@ int ring_upload(tb_trainer* t, const tb_batch* b, int* slot_out) {
     return TB_OK;
 }
 
+// The same for a batch given as PackedSfenValue records: 40 bytes per position cross the bus, the indices, buckets and
+// targets are produced on the device by k_psv_extract, on the copy stream, so that decode and extraction of batch k + 1
+// overlap the compute of batch k (the work of the reference's dataloader workers,
+// crates/nnue-train/src/dataloader.rs:1303-1407).
+int ring_upload_psv(tb_trainer* t, int feature_set, const uint8_t* psv, int n_pos, int* slot_out) {
+    const int s = (int)(t->ring_step % 2);
+    if (t->upload_pending[s]) { CU(t, cudaEventSynchronize(t->ev_upload[s])); t->upload_pending[s] = false; }
+    if (t->consumed_pending[s]) { CU(t, cudaStreamWaitEvent(t->copy_stream, t->ev_consumed[s], 0)); }
+    const void* src = psv;
+    const size_t bytes = (size_t)n_pos * 40;
+    if (!is_pinned(psv)) { memcpy(t->stage_psv[s], psv, bytes); src = t->stage_psv[s]; }
+    CU(t, cudaMemcpyAsync(t->ring_psv[s], src, bytes, cudaMemcpyHostToDevice, t->copy_stream));
+    DevBatch& d = t->ring[s];
+    const int n = launch_psv_extract(t->copy_stream, feature_set, t->ring_psv[s], n_pos, d.stm, d.nstm, d.nnz,
+                                     t->cfg.arch == TB_ARCH_LAYERSTACK ? d.bucket : nullptr, d.score, d.wdl);
+    if (n < 0) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown feature set id %d", feature_set);
+    t->launches += n;
+    d.n_pos = n_pos;
+    d.norm = 1.0f / ((float)n_pos * (float)t->cfg.world_size);
+    CU(t, cudaEventRecord(t->ev_upload[s], t->copy_stream));
+    t->upload_pending[s] = true;
+    CU(t, cudaStreamWaitEvent(t->stream, t->ev_upload[s], 0));
+    const int o = s ^ 1;
+    if (t->upload_pending[o]) { CU(t, cudaEventSynchronize(t->ev_upload[o])); t->upload_pending[o] = false; }
+    t->ring_step += 1;
+    *slot_out = s;
+    return TB_OK;
+}
+
 void free_all(tb_trainer* t) {
     if (!t) return;
     if (t->stream) cudaStreamSynchronize(t->stream);
@@ -647,6 +678,7 @@ void free_all(tb_trainer* t) {
     auto free_batch = [](DevBatch& d) { cudaFree(d.stm); cudaFree(d.nstm); cudaFree(d.nnz); cudaFree(d.bucket); cudaFree(d.score); cudaFree(d.wdl); };
     for (auto& d : t->ring) free_batch(d);
     for (auto& d : t->slots) free_batch(d);
+    for (int i = 0; i < 2; ++i) { cudaFree(t->ring_psv[i]); cudaFreeHost(t->stage_psv[i]); }
     for (auto& s : t->stage) { cudaFreeHost(s.stm); cudaFreeHost(s.nstm); cudaFreeHost(s.nnz); cudaFreeHost(s.bucket); cudaFreeHost(s.score); cudaFreeHost(s.wdl); }
     for (int i = 0; i < 2; ++i) {
         cudaFree(t->pre[i]); cudaFree(t->dft[i]);
@@ -746,6 +778,8 @@ int create_impl(tb_trainer* t) {
         CU(t, cudaHostAlloc((void**)&s.score, B * 4, cudaHostAllocDefault)); CU(t, cudaHostAlloc((void**)&s.wdl, B * 4, cudaHostAllocDefault));
     }
     for (int i = 0; i < 2; ++i) {
+        CU(t, dalloc(&t->ring_psv[i], B * 40));
+        CU(t, cudaHostAlloc((void**)&t->stage_psv[i], B * 40, cudaHostAllocDefault));
         CU(t, cudaEventCreateWithFlags(&t->ev_upload[i], cudaEventDisableTiming));
         CU(t, cudaEventCreateWithFlags(&t->ev_consumed[i], cudaEventDisableTiming));
         CU(t, cudaEventCreateWithFlags(&t->ev_loss[i], cudaEventDisableTiming));
@@ -929,6 +963,35 @@ int tb_train_step(tb_trainer* t, const tb_batch* batch, float lr, float wdl_lamb
     CU(t, cudaSetDevice(t->cfg.device));
     int s = 0;
     rc = ring_upload(t, batch, &s);
+    if (rc != TB_OK) return rc;
+    rc = step_on(t, t->ring[s], lr, wdl_lambda, loss, loss_prev);
+    if (rc != TB_OK) return rc;
+    CU(t, cudaEventRecord(t->ev_consumed[s], t->stream));
+    t->consumed_pending[s] = true;
+    return TB_OK;
+}
+
+int tb_train_step_psv(tb_trainer* t, int feature_set, const uint8_t* psv, int n_pos, float lr, float wdl_lambda,
+                      const tb_loss* loss, double* loss_prev) {
+    if (!t) return TB_ERR_INVALID_ARGUMENT;
+    int rc = check_loss(t, loss);
+    if (rc != TB_OK) return rc;
+    if (n_pos < 0) return fail(t, TB_ERR_INVALID_ARGUMENT, "n_pos is negative (%d)", n_pos);
+    if (n_pos == 0) { if (loss_prev) *loss_prev = 0.0; return TB_OK; }
+    if (!psv) return fail(t, TB_ERR_INVALID_ARGUMENT, "psv is NULL");
+    if (n_pos % 16 != 0) return fail(t, TB_ERR_INVALID_ARGUMENT, "n_pos must be a multiple of 16 (got %d)", n_pos);
+    if (n_pos > t->cfg.batch_capacity)
+        return fail(t, TB_ERR_INVALID_ARGUMENT, "batch %d exceeds workspace capacity %d (the workspace is allocated once at creation)",
+                    n_pos, t->cfg.batch_capacity);
+    int fs_in = 0, fs_active = 0;
+    if (!psv_feature_set_dims(feature_set, &fs_in, &fs_active)) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown feature set id %d", feature_set);
+    // the batch's feature set must be the trainer's (bins/nnue_train/src/trainer_common.rs:301-307)
+    if (fs_in != t->cfg.ft_in || fs_active != t->cfg.max_active)
+        return fail(t, TB_ERR_INVALID_ARGUMENT, "feature set %d has ft_in %d / max_active %d, the trainer was created with %d / %d",
+                    feature_set, fs_in, fs_active, t->cfg.ft_in, t->cfg.max_active);
+    CU(t, cudaSetDevice(t->cfg.device));
+    int s = 0;
+    rc = ring_upload_psv(t, feature_set, psv, n_pos, &s);
     if (rc != TB_OK) return rc;
     rc = step_on(t, t->ring[s], lr, wdl_lambda, loss, loss_prev);
     if (rc != TB_OK) return rc;

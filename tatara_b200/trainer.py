@@ -262,6 +262,16 @@ class _Trainer:
 
     step = train_step
 
+    def train_step_psv(self, psv: np.ndarray, lr: float, wdl_lambda: float, loss: LossKind) -> float:
+        """train_step on 40-byte PackedSfenValue records (uint8 [n, 40]); decode and feature extraction run on the GPU."""
+        psv = np.ascontiguousarray(psv, np.uint8).reshape(-1, 40)
+        out = C.c_double()
+        cl = loss.to_c()
+        self._check(self._lib.tb_train_step_psv(self._h, self.feature_set.index, psv.ctypes.data, psv.shape[0], lr, wdl_lambda,
+                                                C.byref(cl), C.byref(out)), "tb_train_step_psv")
+        self._last_batch = psv
+        return out.value
+
     def flush_pending_loss(self) -> float:
         out = C.c_double()
         self._check(self._lib.tb_flush_pending_loss(self._h, C.byref(out)), "tb_flush_pending_loss")

@@ -117,11 +117,14 @@ def lib():
         "ora_kingrank9_bucket": [C.POINTER(Board)],
         "ora_psv_to_batch": [C.c_int, u8p, sz, i32p, i32p, i32p, C.c_void_p, f32p, f32p],
         "ora_loader_digest_bytes": [i32p, i32p, C.c_int32, f, f, u8p],
+        "ora_psv_synthesize": [C.c_uint64, sz, u8p],
+        "ora_psv_encode": [C.POINTER(Board), u8p],
     }
     for name, args in sig.items():
         getattr(L, name).argtypes = args
         getattr(L, name).restype = None
-    for name in ("ora_feature_dims", "ora_extract_active_features", "ora_kingrank9_bucket", "ora_psv_to_batch"):
+    for name in ("ora_feature_dims", "ora_extract_active_features", "ora_kingrank9_bucket", "ora_psv_to_batch",
+                 "ora_psv_synthesize", "ora_psv_encode"):
         getattr(L, name).restype = C.c_int
     L.ora_loader_digest_bytes.restype = sz
     # trainer
@@ -164,6 +167,13 @@ def feature_dims(name):
     kb, pi, n, a = C.c_int(), C.c_int(), C.c_int(), C.c_int()
     assert lib().ora_feature_dims(FEATURE_SETS[name], kb, pi, n, a) == 0
     return dict(king_buckets=kb.value, piece_inputs=pi.value, ft_in=n.value, max_active=a.value)
+
+
+def synthesize_psv(seed, n_records):
+    """The benchmark's seeded synthetic records (uint8 [n, 40]), from the oracle's own generator."""
+    out = np.zeros((n_records, 40), np.uint8)
+    assert lib().ora_psv_synthesize(seed, n_records, out.reshape(-1)) == 0
+    return out
 
 
 def psv_to_batch(feature_set, psv_bytes, with_bucket=True):

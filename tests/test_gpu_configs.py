@@ -1,0 +1,236 @@
+"""The benchmark configurations at their stated sizes, loss curves over superbatches, the PackedSfenValue-fed step and
+the raw checkpoint round trip — CUDA path (through the C ABI) against the CPU oracle.
+
+Tolerances as in test_gpu_parity.py: FT forward sums bit-exact, forward values and loss 1e-5, gradients 1e-4 (against
+the tensor's scale), superbatch loss means 1e-3 relative (the reference's form |g - c| <= tol (1 + |c|),
+bins/nnue_train/src/tests/gpu_cpu_equivalence_tests.rs:155-172).
+"""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+import tatara_b200 as tb
+from helpers import assert_close, assert_close_scaled
+
+pytestmark = pytest.mark.gpu
+
+TOL_FWD = 1e-5
+TOL_GRAD = 1e-4
+LS_FS = tb.FeatureSetSpec("halfka-hm-merged", 4, 45, 1629, 40, True)
+KP_FS = tb.FeatureSetSpec("halfkp", 0, 81, 1548, 38, True)
+LR = 8.75e-4  # bins/nnue_train/src/cli.rs:260
+WRM290_T = tb.LossKind.wrm(nnue2score=290.0, in_scaling=290.0, in_offset=0.0, target_offset=0.0, target_scaling=290.0)
+WRM290_O = O.wrm_loss(290.0, 290.0, 0.0, 0.0, 290.0)
+
+
+def _batch_dict(b):
+    d = dict(stm=b.stm_indices, nstm=b.nstm_indices, nnz=b.nnz, score=b.score, wdl=b.wdl)
+    if b.bucket_idx is not None:
+        d["bucket"] = b.bucket_idx
+    return d
+
+
+def _oracle(arch, fs, F, l1, l2, nb, optimizer, wd, cap, init):
+    ot = O.OracleTrainer(arch=arch, ft_in=fs.ft_in, piece_inputs=fs.piece_inputs, factorize=fs.ft_factorize,
+                         max_active=fs.max_active, ft_out=F, l1=l1, l2=l2, num_buckets=nb, optimizer=optimizer, wd=wd,
+                         capacity=cap)
+    ot.set_threads(os.cpu_count() or 1)
+    for name in ot.names:
+        ot.group(name)[:] = init[name]
+    return ot
+
+
+def _one_step_against_oracle(tr, ot, batch, lt, lo, B, F, bit_exact_ft):
+    l_gpu = tr.forward_backward(batch, 0.0, lt)
+    l_cpu = ot.step(_batch_dict(batch), LR, 0.0, lo, do_optimizer=False)
+    for name in ("ft_stm", "ft_nstm"):
+        got, want = tr.read_buffer(name, B * F), ot.buffer(name)
+        if bit_exact_ft:
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+        else:
+            assert_close(got, want, 1e-6, name + " (+bias)")
+    assert_close(tr.read_buffer("net_output", B), ot.buffer("net_output"), TOL_FWD, "net_output")
+    assert abs(l_gpu - l_cpu) <= TOL_FWD * (1 + abs(l_cpu)), (l_gpu, l_cpu)
+    assert_close_scaled(tr.read_buffer("dy", B), ot.buffer("dy"), TOL_GRAD, "dy")
+    assert_close_scaled(tr.read_buffer("dft_stm", B * F), ot.buffer("dft_stm"), TOL_GRAD, "dft_stm")
+    for name in ot.names:
+        assert_close_scaled(tr.download_grad(name), ot.group(name, "grad"), TOL_GRAD, "grad " + name)
+    tr.apply_optimizer(LR); ot.apply_optimizer(LR)
+    for name in ot.names:
+        got = tr.download_group(name, ("w", "m", "v"))
+        assert_close(got["w"], ot.group(name, "w"), TOL_FWD, "w " + name)
+        assert_close_scaled(got["m"], ot.group(name, "m"), TOL_GRAD, "m " + name)
+        assert_close_scaled(got["v"], ot.group(name, "v"), TOL_GRAD, "v " + name)
+
+
+def _simple_init(fs, F, l1, l2, rng):
+    init = tb.simple_default_init(fs, F, l1, l2)
+    init["ft_w"][:fs.ft_in * F] *= 4.0          # pre-activations on both sides of the CReLU edges
+    for k in ("l1_w", "l2_w", "l3_w"):
+        init[k] *= 8.0
+    init["ft_w"][fs.ft_in * F:] = (rng.standard_normal(fs.piece_inputs * F) * 0.02).astype(np.float32)
+    return init
+
+
+def _layerstack_init(fs, F, l1, l2, nb, rng):
+    init = tb.layerstack_default_init(fs, F, l1, l2, nb)
+    for n in ("ft_b", "l1_b", "l1_shared_bias", "l2_b", "l3_b"):
+        init[n] = (rng.standard_normal(init[n].size) * 0.05).astype(np.float32)
+    init["ft_w"][:fs.ft_in * F] *= 30.0
+    init["ft_w"][fs.ft_in * F:] = (rng.standard_normal(fs.piece_inputs * F) * 0.02).astype(np.float32)
+    return init
+
+
+@pytest.mark.parametrize("config,B", [(0, 16384), (1, 65536)])
+def test_config0_config1_full_size_step_matches_oracle(config, B):
+    """Simple halfkp 256x2-32-32 CReLU, WRM with every scale 290 (a plain sigmoid), AdamW, factorizer on: one
+    forward/backward/optimizer step at the configuration's own batch size."""
+    F, l1, l2 = 256, 32, 32
+    fs = KP_FS
+    rng = np.random.default_rng(B)
+    init = _simple_init(fs, F, l1, l2, rng)
+    tr = tb.SimpleGpuTrainer(B, F, l1, l2, fs, activation="crelu", optimizer="adamw", weight_decay=0.0, init=init)
+    ot = _oracle("simple", fs, F, l1, l2, 0, "adamw", (0.0, 0.0, 0.0), B, init)
+    batch = tb.synthetic_batch(tb.SYNTH_SEED + config, B, fs, with_bucket=False)
+    _one_step_against_oracle(tr, ot, batch, WRM290_T, WRM290_O, B, F, bit_exact_ft=False)
+    tr.close()
+
+
+def test_config2_full_size_step_matches_oracle():
+    """LayerStack F=768, l1=8, l2=32, halfka-hm-merged, kingrank9, B = 65 536, Ranger, factorizer on."""
+    F, l1, l2, B, nb = 768, 8, 32, 65536, 9
+    fs = LS_FS
+    rng = np.random.default_rng(2)
+    init = _layerstack_init(fs, F, l1, l2, nb, rng)
+    tr = tb.GpuTrainer(B, F, l1, l2, nb, fs, optimizer="ranger", init=init)
+    ot = _oracle("layerstack", fs, F, l1, l2, nb, "ranger", (0.01, 0.01, 0.01), B, init)
+    batch = tb.synthetic_batch(tb.SYNTH_SEED + 2, B, fs)
+    _one_step_against_oracle(tr, ot, batch, tb.LossKind.sigmoid(1.0 / 290.0), O.sigmoid_loss(1.0 / 290.0), B, F, bit_exact_ft=True)
+    tr.close()
+
+
+SUPERBATCHES, CURVE_B = 8, 8192
+
+
+def _scale_outputs(make_oracle, init, dense, batch, lo, target_std):
+    """The reference's initial weights give a network output of ~1e-3: the loss is then the variance of the targets and
+    blind to the network.  Scales the dense layers (equally) so that the output's spread is `target_std`, which makes
+    the loss depend on every layer and lets it fall as training pulls the outputs back."""
+    ot = make_oracle(init)
+    _, out = ot.validate(_batch_dict(batch), 0.0, lo)
+    ot.close()
+    k = (target_std / float(out.std())) ** (1.0 / 3.0)
+    for name in dense:
+        init[name] = init[name] * np.float32(k)
+        assert np.abs(init[name]).max() < 1.9, "scaled weights would sit on the clamp"
+    return init
+
+
+def _loss_curve(tr, ot, fs, lt, lo, with_bucket, seed0, batches_per_superbatch):
+    """8 superbatches of `batches_per_superbatch` batches of 8192 positions (the reference's superbatch is 6104 batches
+    of 65 536: shortened so that the CPU oracle finishes in a minute or two; the network's shapes are the config's)."""
+    gpu, cpu = [], []
+    for sb in range(SUPERBATCHES):
+        g_sum = c_sum = 0.0
+        for k in range(batches_per_superbatch):
+            batch = tb.synthetic_batch(seed0 + 1000 * sb + k, CURVE_B, fs, with_bucket=with_bucket)
+            g_sum += tr.train_step(batch, LR, 0.0, lt)              # lagged by one step: flushed below
+            c_sum += ot.step(_batch_dict(batch), LR, 0.0, lo)
+        g_sum += tr.flush_pending_loss()                              # superbatch end drains the ring (trainer.rs:1087)
+        gpu.append(g_sum / (batches_per_superbatch * CURVE_B))
+        cpu.append(c_sum / (batches_per_superbatch * CURVE_B))
+    return np.array(gpu), np.array(cpu)
+
+
+def test_loss_curve_8_superbatches_config3_shape():
+    """Config 3's network, Ranger, 8 superbatches x 8 batches x 8192 positions (64 steps; ten look-ahead steps)."""
+    F, l1, l2, nb, k = 1536, 16, 32, 9, 8
+    fs = LS_FS
+    lt, lo = tb.LossKind.sigmoid(1.0 / 290.0), O.sigmoid_loss(1.0 / 290.0)
+    init = _layerstack_init(fs, F, l1, l2, nb, np.random.default_rng(33))
+    mk = lambda ini: _oracle("layerstack", fs, F, l1, l2, nb, "ranger", (0.01, 0.01, 0.01), CURVE_B, ini)
+    probe = tb.synthetic_batch(2999, CURVE_B, fs)
+    init = _scale_outputs(mk, init, ("l1_w", "l1_shared_weight", "l2_w", "l3_w"), probe, lo, 1.5 * 290.0)
+    tr = tb.GpuTrainer(CURVE_B, F, l1, l2, nb, fs, optimizer="ranger", init=init)
+    ot = mk(init)
+    gpu, cpu = _loss_curve(tr, ot, fs, lt, lo, True, 3000, k)
+    assert tr.step_count == SUPERBATCHES * k == ot.step_count
+    assert np.all(np.abs(gpu - cpu) <= 1e-3 * np.abs(cpu)), (gpu, cpu)
+    assert cpu[-1] < 0.9 * cpu[0], cpu                          # the curve is not flat: it trains
+    tr.close()
+
+
+def test_loss_curve_8_superbatches_config1_shape():
+    """Config 1's network, AdamW, WRM(290), 8 superbatches x 16 batches x 8192 positions (128 steps)."""
+    F, l1, l2, k = 256, 32, 32, 16
+    fs = KP_FS
+    init = _simple_init(fs, F, l1, l2, np.random.default_rng(11))
+    mk = lambda ini: _oracle("simple", fs, F, l1, l2, 0, "adamw", (0.0, 0.0, 0.0), CURVE_B, ini)
+    probe = tb.synthetic_batch(999, CURVE_B, fs, with_bucket=False)
+    init = _scale_outputs(mk, init, ("l1_w", "l2_w", "l3_w"), probe, WRM290_O, 1.5)
+    tr = tb.SimpleGpuTrainer(CURVE_B, F, l1, l2, fs, activation="crelu", optimizer="adamw", weight_decay=0.0, init=init)
+    ot = mk(init)
+    gpu, cpu = _loss_curve(tr, ot, fs, WRM290_T, WRM290_O, False, 1000, k)
+    assert np.all(np.abs(gpu - cpu) <= 1e-3 * np.abs(cpu)), (gpu, cpu)
+    assert cpu[-1] < 0.9 * cpu[0], cpu
+    tr.close()
+
+
+def test_train_step_psv_is_bit_identical_to_host_index_feed():
+    """Three steps fed with 40-byte records (decode + extraction on the device) against three steps fed with the host
+    index arrays of the same records: identical losses and weights, bit for bit."""
+    F, l1, l2, B, nb = 256, 16, 32, 1024, 9
+    fs = LS_FS
+    init = tb.layerstack_default_init(fs, F, l1, l2, nb)
+    a = tb.GpuTrainer(B, F, l1, l2, nb, fs, init=init)
+    b = tb.GpuTrainer(B, F, l1, l2, nb, fs, init=init)
+    la, lb = [], []
+    for s in range(3):
+        n = B if s != 1 else B - 112                  # a ragged middle batch (still a multiple of 16)
+        psv = tb.synthesize_psv(500 + s, n)
+        la.append(a.train_step(tb.extract_batch(psv, fs), 1e-3, 0.0, tb.LossKind.sigmoid()))
+        lb.append(b.train_step_psv(psv, 1e-3, 0.0, tb.LossKind.sigmoid()))
+    assert la == lb and a.flush_pending_loss() == b.flush_pending_loss()
+    for name in a.group_names:
+        assert np.array_equal(a.download_group(name)["w"].view(np.uint32), b.download_group(name)["w"].view(np.uint32)), name
+    with pytest.raises(tb.TrainerError, match="feature set"):
+        wrong = tb.GpuTrainer(B, F, l1, l2, nb, fs, init=init)
+        wrong.feature_set = KP_FS
+        wrong.train_step_psv(psv, 1e-3, 0.0, tb.LossKind.sigmoid())
+    with pytest.raises(tb.TrainerError, match="multiple of 16"):
+        b.train_step_psv(psv[:24], 1e-3, 0.0, tb.LossKind.sigmoid())
+    a.close(); b.close()
+
+
+def test_raw_checkpoint_round_trip_crosses_the_lookahead_step(tmp_path):
+    """Five Ranger steps, save RNRC v8, restore into a fresh handle, step 6 (the look-ahead step) on both: bit-identical
+    weights, moments and slow weights; a file of another shape is refused."""
+    F, l1, l2, B, nb = 256, 16, 32, 512, 9
+    fs = LS_FS
+    init = tb.layerstack_default_init(fs, F, l1, l2, nb)
+    a = tb.GpuTrainer(B, F, l1, l2, nb, fs, optimizer="ranger", init=init)
+    batches = [tb.synthetic_batch(700 + s, B, fs) for s in range(6)]
+    for s in range(5):
+        a.train_step(batches[s], 1e-3, 0.0, tb.LossKind.sigmoid())
+    a.flush_pending_loss()
+    path = str(tmp_path / "net-3.ckpt")
+    tb.save_raw_checkpoint(a, path, superbatch=3, run_id="net-20250101-1", lr_horizon=8)
+    b = tb.GpuTrainer(B, F, l1, l2, nb, fs, optimizer="ranger", init=None)
+    h = tb.load_raw_checkpoint(b, path)
+    assert (h.superbatch, h.step_count, h.lr_horizon, h.run_id) == (3, 5, 8, "net-20250101-1") and b.step_count == 5
+    assert (h.arch_kind, h.bucket_mode, h.topology) == ("layerstack", "kingrank9", (F, l1, l2, nb))
+    a.train_step(batches[5], 1e-3, 0.0, tb.LossKind.sigmoid())
+    b.train_step(batches[5], 1e-3, 0.0, tb.LossKind.sigmoid())
+    assert a.flush_pending_loss() == b.flush_pending_loss()
+    assert a.step_count == b.step_count == 6
+    for name in a.group_names:
+        ga, gb = a.download_group(name, ("w", "m", "v", "slow")), b.download_group(name, ("w", "m", "v", "slow"))
+        for k in ga:
+            assert np.array_equal(ga[k].view(np.uint32), gb[k].view(np.uint32)), (name, k)
+        assert np.abs(ga["slow"]).max() > 0          # the look-ahead ran
+    other = tb.GpuTrainer(B, F, 8, l2, nb, fs, optimizer="ranger", init=None)
+    with pytest.raises(tb.TrainerError, match="topology"):
+        tb.load_raw_checkpoint(other, path)
+    a.close(); b.close(); other.close()

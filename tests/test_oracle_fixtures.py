@@ -70,3 +70,19 @@ def test_all_five_feature_sets_respect_their_dimensions():
         for key in ("stm", "nstm"):
             valid = b[key][b[key] >= 0]
             assert valid.max() < d["ft_in"]
+
+
+def test_synthetic_generator_of_the_oracle_equals_the_library_generator():
+    """Both generators follow the same documented draw order: byte-identical records; decode(encode(x)) == x."""
+    import tatara_b200 as tb
+    for seed, n in ((tb.SYNTH_SEED + 3, 4096), (1, 333)):
+        a = tb.synthesize_psv(seed, n)
+        b = O.synthesize_psv(seed, n)
+        assert np.array_equal(a, b)
+    rec = O.synthesize_psv(5, 64)
+    for r in rec:
+        board = O.Board()
+        O.lib().ora_psv_decode(np.ascontiguousarray(r), board)
+        again = np.zeros(40, np.uint8)
+        assert O.lib().ora_psv_encode(board, again) == 0
+        assert np.array_equal(again, r)
