@@ -92,10 +92,15 @@ extern "C" int tb_ft_backward_static_scratch(const float* d_dft, const int32_t* 
     int* offsets = counts + inverse_index_counts_len(ft_in);    // [2(N + 1)]
     int* cursor = offsets + 2 * (N + 1);      // [2N]
     int* lists = cursor + 2 * N;              // [4P]
-    int* plan = lists + 4 * P;                // [2 + 2 * max_work + 3N]
+    // The plan holds 8-byte records and the partial rows are moved as float4: both start on a 16-byte boundary of the
+    // array itself (offsets from its 256-byte aligned base rounded up to a multiple of four ints).
     const size_t max_work = (size_t)ft_backward_max_work(batch, max_active, 1);  // <= MAX_WORK by the slot limit
-    // the partial rows start on a 16-byte boundary (they are read and written as float4)
-    float* partial = reinterpret_cast<float*>(plan + (2 + 2 * max_work + 3 * N + 3) / 4 * 4);
+    const size_t plan_off = ((size_t)(lists - base) + 4 * P + 3) / 4 * 4;
+    const size_t partial_off = (plan_off + 2 + 2 * max_work + 3 * N + 3) / 4 * 4;
+    int* plan = base + plan_off;              // [2 + 2 * max_work + 3N]
+    float* partial = reinterpret_cast<float*>(base + partial_off);
+    if (partial_off + max_work * (size_t)ft_out > (size_t)SCRATCH_INTS)   // cannot happen inside the limits checked above
+        return report(err, err_len, TB_ERR_INVALID_ARGUMENT, "static scratch layout overflow");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // launch_inverse_index clears the histogram and the long-list counter itself, launch_ft_backward_split its two
     // counters; offsets, cursors, lists, plan and partial rows are rewritten for the rows and slots this call uses

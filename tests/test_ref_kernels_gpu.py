@@ -74,6 +74,7 @@ def test_ft_backward_vs_reference_inverse_index_pipeline(ref, F, B, A, N):
     rng = np.random.default_rng(F * 3 + B)
     dft = (rng.standard_normal((B, F)) * 1e-3).astype(np.float32)
     d = random_index_batch(rng, B, A, N, max(0, A - 8), A, with_bucket=0)
+    d["stm"][d["stm"] >= N - 40] = 6   # the last 40 rows are held by nobody
     d["stm"][::9, 0] = -1
     d["stm"][::13, 1] = N + 1
     d["stm"][::3, 2] = 5            # a list of several hundred entries
