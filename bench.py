@@ -72,15 +72,28 @@ def peak_hbm():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def algorithmic_bytes(w, n_pos):
+def algorithmic_bytes(w, n_pos, all_optim=False):
     """Algorithmic bytes per launch of each kernel phase: every large tensor crosses HBM once per producer and
-    once per consumer; index arrays, [B, <=32] tensors and the small parameter groups are left out."""
+    once per consumer; index arrays, [B, <=32] tensors and the small parameter groups are left out.
+    Under --all-optim the FT table read by the forward, the pre-activations, the dft rows and the FT moments are fp16."""
     kb, pi, _ = FS_DIMS[w["fs"]]
     F = w["F"]
     W = kb * pi * F * 4.0
     Wt = (kb + 1) * pi * F * 4.0
     X = n_pos * F * 4.0
     comb = X if w["arch"] == "layerstack" else 2 * X      # the L1 input [B, F] or [B, 2F]
+    if all_optim:
+        Wh, Xh = W / 2, X / 2
+        d = {
+            "ft_forward": Wh + 2 * Xh + comb,      # fp16 table in, fp16 pre-activations and the fp32 L1 input out
+            "l1_forward": comb,
+            "l1_wgrad": comb,
+            "l1_dgrad_ftgrad": 4 * Xh,             # fp16 pre-activations in, fp16 dft out
+            "ft_backward": 2 * Xh + W,             # fp16 dft in, fp32 gradient rows out
+            "opt_ft": 5 * Wt + Wh,                 # w, g in (fp32), m, v in and out (fp16), w out; fp16 folded table out
+        }
+        d["step"] = sum(d.values())                # = 2W + 5Wt + 7X
+        return d
     return {
         "ft_forward": W + 2 * X + comb,        # read the table once, write both pre-activations and the L1 input
         "l1_forward": comb,                    # read the L1 input
@@ -394,6 +407,8 @@ def main():
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--repeats", type=int, default=5)
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "all-optim"],
+                    help="all-optim: --tf32 --ft-fp16 --ft-fp16-out --fp16-opt-state of the reference's CLI")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
@@ -447,7 +462,9 @@ def main():
             if rank == 0:
                 print(json.dumps({"error": "data-parallel self check failed", "dp_parity": dp_ok, "replicas_identical": dp_same_small}), flush=True)
             sys.exit(1)
-    tr, loss, fs = make_trainer(tb, w, device, world, rank, nccl_id, capacity=B)
+    all_optim = args.precision == "all-optim"
+    prec = tb.PrecisionFlags(tf32=True, ft_fp16=True, ft_fp16_out=True, fp16_opt_state=True) if all_optim else None
+    tr, loss, fs = make_trainer(tb, w, device, world, rank, nccl_id, capacity=B, precision=prec)
     n_batches = 3
     seed0 = SYNTH_SEED + CONFIG_INDEX[args.workload] + 7919 * rank
     psvs = [tb.synthesize_psv(seed0 + 104729 * i, B) for i in range(n_batches)]
@@ -539,12 +556,12 @@ def main():
 
     if rank == 0:
         peak, peak_kind = peak_hbm()
-        alg = algorithmic_bytes(w, B)
+        alg = algorithmic_bytes(w, B, all_optim)
         phases = {k: v[0] / n_prof for k, v in prof.items() if v[1] > 0}
         dominant = max((k for k in phases if k in alg), key=lambda k: phases[k])
         ach = alg[dominant] / (phases[dominant] * 1e-3) / 1e9
         step_ach = alg["step"] / (ms / K * 1e-3) / 1e9
-        lookup = 2.0 * B * fs.max_active * w["F"] * 4.0     # row bytes both slice-resident FT kernels read from shared memory
+        lookup = 2.0 * B * fs.max_active * w["F"] * (2.0 if all_optim else 4.0)   # row bytes each slice-resident FT kernel reads from shared memory
         smem_peak = None
         if clocks and clocks.get("sm_mhz"):
             smem_peak = 148 * SMEM_BYTES_PER_CLK_PER_SM * clocks["sm_mhz"] * 1e6 / 1e9     # GB/s at the sampled clock
@@ -553,12 +570,13 @@ def main():
             if k in phases and smem_peak:
                 a = lookup / (phases[k] * 1e-3) / 1e9
                 smem[k] = {"achieved": a, "peak": smem_peak, "unit": "GB/s", "frac": a / smem_peak}
-        exact_case = args.workload == "cfg3" and B == BATCH and world == 1
+        exact_case = args.workload == "cfg3" and B == BATCH and world == 1 and not all_optim
         line = {
             "metric": "train_positions_per_second", "value": value, "unit": "pos/s", "n_gpus": world, "steps": K, "warmup": Wm,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": w["name"], "positions_per_step_per_gpu": B, "global_batch": B * world,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16/tf32" if all_optim else "f32", "data": "synthetic",
+            "config": {"workload": w["name"].replace("fp32", "all-optim (fp16 FT table/activations/moments, tf32 L1)") if all_optim else w["name"],
+                       "positions_per_step_per_gpu": B, "global_batch": B * world,
                        "parallelism": "dp%d" % world, "l2": "inputs larger than L2 (tables and activations >> 126 MB), 3 rotating batches",
                        "loss_per_position": last_loss / (B * world)},
             "repeats": {"n": len(rep_ms), "steps_each": K, "ms_per_step_median": ms / K, "ms_per_step_min": min(rep_ms) / K,

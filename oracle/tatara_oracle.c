@@ -418,6 +418,57 @@ void ora_radam_step(float* weights, float* m, float* v, float* grad, float lr, f
     }
 }
 
+/* ---- reduced precision (--ft-fp16, --ft-fp16-out, --fp16-opt-state, --tf32) ------------------------------------------
+ * The reference has no CPU twin for these modes; the functions below restate its CUDA kernels
+ * (crates/cuda-native-runtime/kernels/native_kernels.cu) with their rounding points.  fp16 values are kept in float
+ * arrays holding exactly representable fp16 values. */
+float ora_round_half(float x) { return (float)(_Float16)x; } /* __float2half_rn followed by __half2float */
+
+/* TF32 operand: cuBLAS in CUBLAS_TF32_TENSOR_OP_MATH (bins/nnue_train/src/trainer_common.rs:691-727) feeds fp32 data to
+ * the tensor cores, which read the sign, the exponent and the upper 10 mantissa bits.  Modelled as truncation. */
+float ora_tf32(float x) {
+    uint32_t u;
+    memcpy(&u, &x, 4);
+    u &= 0xFFFFE000u;
+    memcpy(&x, &u, 4);
+    return x;
+}
+
+/* native_clamp_half, native_kernels.cu:636-646 */
+static float clamp_half_count(float v, uint64_t* clamps) {
+    if (v > 65504.0f) { ++*clamps; return 65504.0f; }
+    if (v < -65504.0f) { ++*clamps; return -65504.0f; }
+    return v;
+}
+
+/* native_radam_step_fp16<HalfState = true>, native_kernels.cu:1127-1181.  m and v hold the stored fp16 values divided by
+ * their scale (what MomentBuf::to_host_f32 returns, bins/nnue_train/src/trainer_common.rs:89-105). */
+void ora_radam_step_f16state(float* weights, float* m, float* v, float* grad, float lr, float step_size, int32_t denom,
+                             float decay, float beta1, float beta2, float eps, float min_w, float max_w, float m_scale,
+                             float v_scale, size_t n) {
+    float rate = lr * step_size;
+    PAR_FOR
+    for (size_t i = 0; i < n; ++i) {
+        float g = grad[i];
+        float p = weights[i] * (1.0f - decay * rate);
+        float prev_m = m[i], prev_v = v[i]; /* = half2float(stored) / scale */
+        float mi = beta1 * prev_m + (1.0f - beta1) * g;
+        float vi = beta2 * prev_v + (1.0f - beta2) * g * g;
+        float sm = mi * m_scale;
+        sm = sm > 65504.0f ? 65504.0f : (sm < -65504.0f ? -65504.0f : sm);
+        float sv = vi * v_scale;
+        sv = sv > 65504.0f ? 65504.0f : sv;
+        m[i] = ora_round_half(sm) / m_scale;
+        v[i] = ora_round_half(sv) / v_scale;
+        float val = mi;
+        if (denom != 0) val /= sqrtf(vi) + eps;
+        p -= rate * val;
+        p = p < min_w ? min_w : (p > max_w ? max_w : p);
+        weights[i] = p;
+        grad[i] = 0.0f;
+    }
+}
+
 /* crates/gpu-kernels/src/pointwise/ranger_step.rs:52-59 */
 void ora_ranger_lookahead_lerp(float* weights, float* slow, float alpha, size_t n) {
     float oma = 1.0f - alpha;
@@ -887,6 +938,10 @@ struct ora_trainer {
     float *l1_pre, *l1_acted, *dl1_acted, *dl1_pre;
     int32_t* idx_tmp;
     int last_n;
+    /* reduced precision: bit 1 tf32, 2 ft_fp16, 4 ft_fp16_out, 8 fp16_opt_state (cli.rs:623-638) */
+    int precision;
+    float *table_h, *gtmp, *x_t, *w_t, *ws_t, *dl1_t; /* fp16 forward table; FT gradient of one perspective; tf32 operands */
+    uint64_t clamp_count, clamp_elems;
 };
 
 static float* falloc(size_t n) { return (float*)calloc(n ? n : 1, sizeof(float)); }
@@ -955,9 +1010,15 @@ void ora_trainer_destroy(ora_trainer* t) {
                      t->l1_pre, t->l1_acted, t->dl1_acted, t->dl1_pre};
     for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); ++i) free(bufs[i]);
     free(t->idx_tmp);
+    free(t->table_h); free(t->gtmp); free(t->x_t); free(t->w_t); free(t->ws_t); free(t->dl1_t);
     free(t);
 }
 
+void ora_trainer_set_precision(ora_trainer* t, int flags) { t->precision = flags; }
+void ora_trainer_clamp_count(const ora_trainer* t, uint64_t* clamps, uint64_t* elems) {
+    if (clamps) *clamps = t->clamp_count;
+    if (elems) *elems = t->clamp_elems;
+}
 int ora_trainer_num_groups(const ora_trainer* t) { return t->n_groups; }
 const char* ora_trainer_group_name(const ora_trainer* t, int g) { return t->g[g].name; }
 size_t ora_trainer_group_len(const ora_trainer* t, int g) { return t->g[g].len; }
@@ -1022,11 +1083,23 @@ const float* ora_trainer_buffer(const ora_trainer* t, const char* name, size_t* 
 
 static const float* forward_table(ora_trainer* t) {
     const ora_config* c = &t->cfg;
-    if (!c->factorize) return t->g[0].w;
-    /* the reference keeps comb in sync after every optimizer step / upload (trainer_layerstack.rs
-     * launch_ft_fold); recomputing it from the current master weights here is the same thing. */
-    ora_ft_fold_virtual(t->g[0].w, t->comb, (size_t)c->ft_in, (size_t)c->ft_out, (size_t)c->piece_inputs);
-    return t->comb;
+    size_t NF = (size_t)c->ft_in * (size_t)c->ft_out;
+    const float* table = t->g[0].w;
+    if (c->factorize) {
+        /* the reference keeps comb in sync after every optimizer step / upload (trainer_layerstack.rs
+         * launch_ft_fold); recomputing it from the current master weights here is the same thing. */
+        ora_ft_fold_virtual(t->g[0].w, t->comb, (size_t)c->ft_in, (size_t)c->ft_out, (size_t)c->piece_inputs);
+        table = t->comb;
+    }
+    if (t->precision & 2) {
+        /* --ft-fp16: the forward reads an fp16 table: ft_fold_virtual_f16 (native_kernels.cu:262-318) with the factorizer,
+         * else the mirror the optimizer kernels write (radam_step_*_mirror, ranger_lookahead_lerp_fp16_mirror) */
+        if (!t->table_h) t->table_h = falloc(NF);
+        PAR_FOR
+        for (size_t i = 0; i < NF; ++i) t->table_h[i] = ora_round_half(table[i]);
+        table = t->table_h;
+    }
+    return table;
 }
 
 static double run_loss(ora_trainer* t, const float* score, const float* wdl, int n, float lambda, const ora_loss* L) {
@@ -1050,11 +1123,24 @@ static double ls_forward(ora_trainer* t, const int32_t* stm_idx, const int32_t* 
     size_t B = (size_t)n, F = (size_t)c->ft_out, N = (size_t)c->ft_in, A = (size_t)c->max_active;
     size_t l1 = (size_t)c->l1, l2 = (size_t)c->l2, nb = (size_t)c->num_buckets, l1e = l1 - 1, l2in = 2 * l1e;
     const float* table = forward_table(t);
-    ora_sparse_ft_forward(table, stm_idx, nnz, t->ft_stm, B, F, N, A);
+    ora_sparse_ft_forward(table, stm_idx, nnz, t->ft_stm, B, F, N, A);   /* fp16 rows are summed in fp32 (:743-801) */
     ora_sparse_ft_forward(table, nstm_idx, nnz, t->ft_nstm, B, F, N, A);
+    if (t->precision & 4) { /* sparse_ft_forward_fp16_out: the sums are stored as fp16; ft_post_perspective_fwd_fp16 reads them */
+        PAR_FOR
+        for (size_t i = 0; i < B * F; ++i) { t->ft_stm[i] = ora_round_half(t->ft_stm[i]); t->ft_nstm[i] = ora_round_half(t->ft_nstm[i]); }
+    }
     ora_ft_post_perspective_fwd(t->ft_stm, t->ft_nstm, t->g[1].w, t->combined, B, F, FT_POST_SCALE);
-    ora_dense_mm_fwd_bucket(t->combined, t->g[2].w, t->g[3].w, bucket, t->l1_bucket, B, F, l1, nb);
-    ora_dense_mm_fwd(t->combined, t->g[4].w, t->g[5].w, t->l1_shared, B, F, l1);
+    const float *x1 = t->combined, *w1 = t->g[2].w, *ws1 = t->g[4].w;
+    if (t->precision & 1) { /* --tf32: every L1 product runs on TF32 operands (trainer_layerstack.rs:2388-2420, 2498-2506) */
+        if (!t->x_t) { t->x_t = falloc((size_t)t->cap * F); t->w_t = falloc(nb * l1 * F); t->ws_t = falloc(F * l1); t->dl1_t = falloc((size_t)t->cap * l1); }
+        PAR_FOR
+        for (size_t i = 0; i < B * F; ++i) t->x_t[i] = ora_tf32(t->combined[i]);
+        for (size_t i = 0; i < nb * l1 * F; ++i) t->w_t[i] = ora_tf32(t->g[2].w[i]);
+        for (size_t i = 0; i < F * l1; ++i) t->ws_t[i] = ora_tf32(t->g[4].w[i]);
+        x1 = t->x_t; w1 = t->w_t; ws1 = t->ws_t;
+    }
+    ora_dense_mm_fwd_bucket(x1, w1, t->g[3].w, bucket, t->l1_bucket, B, F, l1, nb);
+    ora_dense_mm_fwd(x1, ws1, t->g[5].w, t->l1_shared, B, F, l1);
     ora_elementwise_add(t->l1_bucket, t->l1_shared, t->l1_total, B * l1);
     ora_slice_extract_2d(t->l1_total, t->l1_main, B, l1, 0, l1e);
     ora_slice_extract_2d(t->l1_total, t->l1_skip, B, l1, l1e, 1);
@@ -1088,6 +1174,33 @@ static void ft_backward(ora_trainer* t, const int32_t* stm_idx, const int32_t* n
     if (c->factorize) ora_ft_reduce_virtual_grad(t->g[0].grad, N, F, (size_t)c->piece_inputs);
 }
 
+/* --ft-fp16-out: ft_post_perspective_grad_fused_fp16 (native_kernels.cu:2304-2353) stores dft * gradient_scale clamped to
+ * the fp16 range (clamps counted) and rounded, with gradient_scale = 2^14 * batch (trainer_layerstack.rs:3617-3621, the
+ * bias gradient takes the unscaled value); gather_and_sum_per_feature_{overwrite,add}_fp16 (:1081-1181) sum the fp16 rows
+ * of one perspective in fp32, multiply by 1 / gradient_scale, and the second perspective is added to the first. */
+static void ft_backward_fp16(ora_trainer* t, const int32_t* stm_idx, const int32_t* nstm_idx, const int32_t* nnz, size_t B) {
+    const ora_config* c = &t->cfg;
+    size_t F = (size_t)c->ft_out, N = (size_t)c->ft_in, A = (size_t)c->max_active;
+    size_t Nt = N + (c->factorize ? (size_t)c->piece_inputs : 0);
+    float scale = 16384.0f * (float)B, inv = 1.0f / scale;
+    if (!t->gtmp) t->gtmp = falloc(Nt * F);
+    uint64_t clamps = 0;
+    for (int p = 0; p < 2; ++p) {
+        float* d = p == 0 ? t->dft_stm : t->dft_nstm;
+        for (size_t i = 0; i < B * F; ++i) d[i] = ora_round_half(clamp_half_count(d[i] * scale, &clamps)); /* the stored fp16 rows */
+        memset(t->gtmp, 0, N * F * sizeof(float));
+        ora_sparse_ft_backward(d, masked_indices(t, p == 0 ? stm_idx : nstm_idx, nnz, B, A), t->gtmp, B, F, N, A);
+        float* g = t->g[0].grad;
+        PAR_FOR
+        for (size_t i = 0; i < N * F; ++i) g[i] = p == 0 ? t->gtmp[i] * inv : g[i] + t->gtmp[i] * inv;
+        PAR_FOR
+        for (size_t i = 0; i < B * F; ++i) d[i] *= inv; /* reported in the gradient's own scale */
+    }
+    t->clamp_count += clamps;
+    t->clamp_elems += 2 * (uint64_t)B * (uint64_t)F;
+    if (c->factorize) ora_ft_reduce_virtual_grad(t->g[0].grad, N, F, (size_t)c->piece_inputs);
+}
+
 /* backward of trainer_layerstack.rs:2849-4032 */
 static void ls_backward(ora_trainer* t, const int32_t* stm_idx, const int32_t* nstm_idx, const int32_t* nnz,
                         const int32_t* bucket, int n) {
@@ -1109,19 +1222,26 @@ static void ls_backward(ora_trainer* t, const int32_t* stm_idx, const int32_t* n
     memset(t->dl1_total, 0, B * l1 * sizeof(float));
     ora_slice_scatter_2d(t->dl1_main, t->dl1_total, B, l1e, l1, 0);
     ora_slice_scatter_2d(t->dy, t->dl1_total, B, 1, l1, l1e);
+    const float *x1 = t->combined, *w1 = t->g[2].w, *ws1 = t->g[4].w, *d1 = t->dl1_total;
+    if (t->precision & 1) { /* --tf32: the four L1 gradient products too (trainer_layerstack.rs:3340-3398, 3454-3541) */
+        PAR_FOR
+        for (size_t i = 0; i < B * l1; ++i) t->dl1_t[i] = ora_tf32(t->dl1_total[i]);
+        x1 = t->x_t; w1 = t->w_t; ws1 = t->ws_t; d1 = t->dl1_t; /* operands of the forward are unchanged */
+    }
     /* L1 shared */
-    ora_dense_mm_bwd_input(t->dl1_total, t->g[4].w, t->dcombined2, B, F, l1);
-    ora_dense_mm_bwd_weight(t->combined, t->dl1_total, t->g[4].grad, B, F, l1);
+    ora_dense_mm_bwd_input(d1, ws1, t->dcombined2, B, F, l1);
+    ora_dense_mm_bwd_weight(x1, d1, t->g[4].grad, B, F, l1);
     ora_bias_grad(t->dl1_total, t->g[5].grad, B, l1);
     /* L1 per bucket */
-    ora_dense_mm_bwd_weight_bucket(t->combined, t->dl1_total, bucket, t->g[2].grad, B, F, l1, nb);
-    ora_dense_mm_bwd_input_bucket(t->dl1_total, t->g[2].w, bucket, t->dcombined, B, F, l1, nb);
+    ora_dense_mm_bwd_weight_bucket(x1, d1, bucket, t->g[2].grad, B, F, l1, nb);
+    ora_dense_mm_bwd_input_bucket(d1, w1, bucket, t->dcombined, B, F, l1, nb);
     ora_bias_grad_bucket(t->dl1_total, bucket, t->g[3].grad, B, l1, nb);
     /* native_kernels.cu:2260 ft_post_perspective_grad_fused adds the two sources in-register */
     ora_elementwise_add(t->dcombined, t->dcombined2, t->dcombined, B * F);
     ora_ft_post_perspective_grad(t->dcombined, t->ft_stm, t->g[1].w, t->dft_stm, t->g[1].grad, B, F, 0, F, FT_POST_SCALE);
     ora_ft_post_perspective_grad(t->dcombined, t->ft_nstm, t->g[1].w, t->dft_nstm, t->g[1].grad, B, F, F / 2, F, FT_POST_SCALE);
-    ft_backward(t, stm_idx, nstm_idx, nnz, B);
+    if (t->precision & 4) ft_backward_fp16(t, stm_idx, nstm_idx, nnz, B);
+    else ft_backward(t, stm_idx, nstm_idx, nnz, B);
 }
 
 static void act_fwd(int act, const float* x, float* y, size_t n) { if (act == 0) ora_crelu_fwd(x, y, n); else ora_screlu_fwd(x, y, n); }
@@ -1212,8 +1332,12 @@ void ora_trainer_apply_optimizer(ora_trainer* t, float lr) {
     const float lm[3] = {c->lr_mult_ft, c->lr_mult_dense, c->lr_mult_bias};
     for (int i = 0; i < t->n_groups; ++i) {
         group* g = &t->g[i];
-        ora_radam_step(g->w, g->m, g->v, g->grad, lr * lm[g->kind], step_size, denom, wd[g->kind], beta1, BETA2,
-                       EPS, -g->clamp, g->clamp, g->len);
+        if (i == 0 && (t->precision & 8)) /* --fp16-opt-state: only the FT table's moments (trainer_layerstack.rs:4085-4117) */
+            ora_radam_step_f16state(g->w, g->m, g->v, g->grad, lr * lm[g->kind], step_size, denom, wd[g->kind], beta1, BETA2,
+                                    EPS, -g->clamp, g->clamp, 268435456.0f /* 2^28 */, 1099511627776.0f /* 2^40 */, g->len);
+        else
+            ora_radam_step(g->w, g->m, g->v, g->grad, lr * lm[g->kind], step_size, denom, wd[g->kind], beta1, BETA2,
+                           EPS, -g->clamp, g->clamp, g->len);
     }
     if (c->optimizer == 0 && t->step_count % RANGER_K == 0)
         for (int i = 0; i < t->n_groups; ++i) ora_ranger_lookahead_lerp(t->g[i].w, t->g[i].slow, RANGER_ALPHA, t->g[i].len);

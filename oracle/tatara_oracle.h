@@ -176,6 +176,14 @@ double ora_trainer_validate(ora_trainer* t, const int32_t* stm_idx, const int32_
 void ora_trainer_accumulate_grads(ora_trainer* dst, const ora_trainer* src);
 /* runs only the optimizer part on the gradients currently held. */
 void ora_trainer_apply_optimizer(ora_trainer* t, float lr);
+/* reduced precision of the LayerStack trainer: bit 1 tf32, 2 ft_fp16, 4 ft_fp16_out, 8 fp16_opt_state */
+void ora_trainer_set_precision(ora_trainer* t, int flags);
+void ora_trainer_clamp_count(const ora_trainer* t, uint64_t* clamps, uint64_t* elems);
+float ora_round_half(float x);
+float ora_tf32(float x);
+void ora_radam_step_f16state(float* weights, float* m, float* v, float* grad, float lr, float step_size, int32_t denom,
+                             float decay, float beta1, float beta2, float eps, float min_w, float max_w, float m_scale,
+                             float v_scale, size_t n);
 
 #ifdef __cplusplus
 }

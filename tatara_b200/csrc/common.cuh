@@ -32,7 +32,14 @@ struct OptScalars {
     float lr, step_size, decay, beta1, beta2, eps, min_w, max_w, alpha;
     int denom;
     int lerp;  // apply the Ranger look-ahead interpolation after the update
+    // Factor the stored gradient is multiplied by on load (1 unless the FT weight gradient was summed from loss-scaled
+    // fp16 rows: then the inverse of that scale).  Applies to the real FT rows only.
+    float grad_scale = 1.0f;
 };
+// fp16 optimizer state of the FT table: m is stored as m * 2^28, v as v * 2^40, clamped to the fp16 range
+// (bins/nnue_train/src/arch.rs:95-117 FT_OPT_M_SCALE / FT_OPT_V_SCALE; radam_step_f16state, native_kernels.cu:1127-1181)
+#define TB_FT_OPT_M_SCALE 268435456.0f
+#define TB_FT_OPT_V_SCALE 1099511627776.0f
 
 // One small parameter group for the batched optimizer kernel.
 struct SmallGroup {
@@ -58,18 +65,21 @@ static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b;
 // ft_kernels.cu
 // mode: 0 raw gather-sum, 1 LayerStack pairwise (+bias, CReLU, product, scale), 2 Simple CReLU, 3 Simple SCReLU
 // items: the (position, perspective) processing order from launch_step_sorts, or NULL for natural order
-int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
-                      const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
-                      const int* items, int B, int F, int N, int A, float scale, int n_persp);
+int launch_ft_forward(cudaStream_t s, int mode, const void* table, const int* idx_stm, const int* idx_nstm,
+                      const int* nnz, const float* bias, void* pre_stm, void* pre_nstm, float* combined,
+                      const int* items, int B, int F, int N, int A, float scale, int n_persp, int table_half = 0,
+                      int out_half = 0);
 // slice-resident forward: every item's rows come from a 32-column strip of its king-bucket slice held in shared
 // memory.  Needs items / item_seg from launch_step_sorts with the same rows_per_slice; work: scratch of
 // ft_forward_slice_work_ints(n_items, slices + 1, A) ints.
 bool ft_forward_slice_supported(int F, int N, int A, int rows_per_slice);
 size_t ft_forward_slice_work_ints(int n_items, int n_keys, int A);
-int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
-                            const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
+// table_half: fp16 table rows (64-column strips); out_half: fp16 pre-activations (needs table_half).  Returns -1 for a
+// combination that is not built (fp16 with the Simple activations).
+int launch_ft_forward_slice(cudaStream_t s, int mode, const void* table, const int* idx_stm, const int* idx_nstm,
+                            const int* nnz, const float* bias, void* pre_stm, void* pre_nstm, float* combined,
                             const int* items, const int* item_seg, int* work, int B, int F, int N, int A,
-                            int rows_per_slice, float scale, int n_persp);
+                            int rows_per_slice, float scale, int n_persp, int table_half = 0, int out_half = 0);
 // scratch of the inverse index, in ints: histogram [2N], a counter, a queue of long lists [2N], scan block sums
 static inline size_t inverse_index_counts_len(int N) { return 4 * (size_t)N + 1 + 2 * ((size_t)N / 2048 + 2); }
 // counts: [inverse_index_counts_len(N)], offsets: [2][N+1], cursor: [2][N], lists: [4][B*A] (lists + sort scratch)
@@ -79,9 +89,10 @@ int launch_inverse_index(cudaStream_t s, const int* run_if, const int* idx_stm, 
 // long lists are cut into parts summed by separate blocks; plan: [2 + 2 * max_work + 3 * N] ints,
 // partial: [max_work][F] floats with max_work = ft_backward_max_work(B, A, n_persp)
 int ft_backward_max_work(int B, int A, int n_persp);
-int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft_stm, const float* dft_nstm, const int* offsets,
+// dft_half: the incoming gradient rows are fp16; the sums keep the rows' loss scale
+int launch_ft_backward_split(cudaStream_t s, const int* run_if, const void* dft_stm, const void* dft_nstm, const int* offsets,
                              const int* lists, int B, int A, int N, int F, int n_persp, int* plan, float* partial,
-                             float* grad);
+                             float* grad, int dft_half = 0);
 // slice-resident weight gradient (ft_slice_bwd.cu).  Needs the slice-resident forward of the same step (its row codes
 // in fwd_work) and items / item_seg of the same rows_per_slice; bwd_work: ft_backward_slice_ints(...) ints.  The kernels
 // do nothing when the batch has a row outside its item's slice: *ft_slice_outside_flag(...) is then 1 and the generic
@@ -92,8 +103,9 @@ const int* ft_slice_outside_flag(int* fwd_work, int n_items, int N, int rows_per
 int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int* bwd_work, int B, int A, int N,
                          int rows_per_slice, int n_persp);
 // the rows of slices [slice_begin, slice_begin + slice_count)
-int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
-                             int A, int N, int F, int rows_per_slice, int n_persp, int slice_begin, int slice_count, float* grad);
+int launch_ft_backward_slice(cudaStream_t s, const void* dft_stm, const void* dft_nstm, int* fwd_work, int* bwd_work, int B,
+                             int A, int N, int F, int rows_per_slice, int n_persp, int slice_begin, int slice_count, float* grad,
+                             int dft_half = 0);
 int sort_max_units(int max_tiles);
 // The two sorts of a step: positions by bucket -> order, bucket segments seg_start [nb + 2], tiles (room for max_tiles
 // tiles followed by the work units; n_tiles is {tile count, unit count}); items (position, perspective) of both
@@ -103,7 +115,9 @@ int launch_step_sorts(cudaStream_t s, const int* bucket /*may be NULL*/, int B, 
                       int* seg_start, int max_tiles, const int* idx_stm, const int* idx_nstm, const int* nnz, int A, int N,
                       int rows_per_slice, int n_persp, int* items, int* item_seg, int* hist);
 int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F);
-int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F);
+int launch_ft_fold(cudaStream_t s, const float* w, void* comb, int N, int pi, int F, int half_comb = 0);
+// dst[i] = fp16(src[i]) (cast_f32_to_f16, native_kernels.cu:648), n a multiple of 4
+int launch_cast_half(cudaStream_t s, const float* src, void* dst, int64_t n);
 
 // psv.cu
 int launch_psv_extract(cudaStream_t s, int feature_set, const void* d_psv, long long n, int* stm, int* nstm, int* nnz,
@@ -141,23 +155,28 @@ int launch_l1_wgrad(cudaStream_t s, const float* x, int K, const float* dl1, con
                     float* gw_bucket, float* gw_shared);
 // L1 input gradient fused with the FT activation gradient; writes dft of both perspectives and the
 // FT bias gradient.
+// half_act: pre-activations and dft are fp16; dft is written as round(clamp(g * grad_scale)) and the clamped elements
+// are added to *clamp_counter.  Returns -1 for a combination that is not built.
 int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int* order, const TileDesc* tiles,
                            const int* n_tiles, int max_tiles, const float* wb, const float* ws,
-                           const float* pre_stm, const float* pre_nstm, const float* ft_bias, float scale,
-                           int B, int F, int l1, int nb, float* dft_stm, float* dft_nstm, float* bias_partials,
-                           float* ft_b_grad, int n_ctas);
+                           const void* pre_stm, const void* pre_nstm, const float* ft_bias, float scale,
+                           int B, int F, int l1, int nb, void* dft_stm, void* dft_nstm, float* bias_partials,
+                           float* ft_b_grad, int n_ctas, int half_act = 0, float grad_scale = 1.0f,
+                           unsigned long long* clamp_counter = nullptr);
 
 // opt_kernels.cu
-int launch_radam(cudaStream_t s, float* w, float* m, float* v, const float* g, float* slow, int64_t n,
-                 OptScalars sc);
+// half_state: m and v are fp16 arrays (scaled, see above); mirror: NULL or an fp16 copy of the updated weights
+int launch_radam(cudaStream_t s, float* w, void* m, void* v, const float* g, float* slow, int64_t n,
+                 OptScalars sc, int half_state = 0, void* mirror = nullptr);
 int launch_radam_small(cudaStream_t s, const SmallGroups& groups, int max_n, OptScalars sc);
 // factorised FT table: per virtual row v, updates the real rows kb*pi+v, reduces their gradients into the
 // virtual row, updates it and writes the folded forward table.
 // the same in pieces: the real rows of the king buckets [kb0, kb1) (call with ascending ranges), then the virtual rows
 // and the folded table
-int launch_radam_factorized_rows(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, int N, int pi, int F, int kb0,
-                                 int kb1, OptScalars sc);
-int launch_radam_factorized_fold(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb, int N, int pi,
-                                 int F, OptScalars sc);
-int launch_radam_factorized(cudaStream_t s, float* w, float* m, float* v, float* g, float* slow, float* comb,
-                            int N, int pi, int F, OptScalars sc);
+// half_state: m and v are fp16 (scaled); half_comb: the folded table is fp16 (ft_fold_virtual_f16, native_kernels.cu:262)
+int launch_radam_factorized_rows(cudaStream_t s, float* w, void* m, void* v, float* g, float* slow, int N, int pi, int F, int kb0,
+                                 int kb1, OptScalars sc, int half_state = 0);
+int launch_radam_factorized_fold(cudaStream_t s, float* w, void* m, void* v, float* g, float* slow, void* comb, int N, int pi,
+                                 int F, OptScalars sc, int half_state = 0, int half_comb = 0);
+int launch_radam_factorized(cudaStream_t s, float* w, void* m, void* v, float* g, float* slow, void* comb,
+                            int N, int pi, int F, OptScalars sc, int half_state = 0, int half_comb = 0);

@@ -13,7 +13,27 @@ static __device__ __forceinline__ void dg_cp16(void* dst_shared, const void* src
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
 }
 
+// asynchronous 8-byte copy global -> shared (both 8-byte aligned)
+static __device__ __forceinline__ void dg_cp8(void* dst_shared, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(dst_shared)), "l"(src) : "memory");
+}
+
+#include <cuda_fp16.h>
 #include <stdlib.h>
+
+#include <type_traits>
+
+static __device__ __forceinline__ unsigned dk_pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&h);
+}
+static __device__ __forceinline__ float2 dk_unpack_h2(unsigned pair) { return __half22float2(*reinterpret_cast<const __half2*>(&pair)); }
+// native_clamp_half (native_kernels.cu:636-646): values beyond the fp16 range are clamped and counted
+static __device__ __forceinline__ float clamp_half_count(float v, unsigned& clamps) {
+    if (v > 65504.0f) { ++clamps; return 65504.0f; }
+    if (v < -65504.0f) { ++clamps; return -65504.0f; }
+    return v;
+}
 
 #define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
 #define L1_SQR_SCALE (127.0f / 128.0f)
@@ -1302,16 +1322,22 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad(const float* __restrict
 #define DG_POS 128     // positions per block
 #define DG_STAGES 3
 static_assert(2 * DG_POS == TB_UNIT_TILES * TB_TILE_M, "a block of the streaming kernel owns half a work unit");
-template <int MODE, int L1>
+// HALF: pre-activations and dft rows are fp16 (ft_post_perspective_grad_fused_fp16, native_kernels.cu:2304-2353): the
+// gradient is multiplied by grad_scale, clamped to the fp16 range (clamps are counted) and rounded; the bias gradient
+// takes the unscaled fp32 value.
+template <int MODE, int L1, bool HALF>
 __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __restrict__ dl1, const int* __restrict__ order,
                                                                  const TileDesc* __restrict__ tiles, const TileDesc* __restrict__ units,
                                                                  const int* __restrict__ n_units, const float* __restrict__ wb,
-                                                                 const float* __restrict__ ws, const float* __restrict__ pre_stm,
-                                                                 const float* __restrict__ pre_nstm, const float* __restrict__ ft_bias,
-                                                                 float scale, int F, int nb, int CW, float* __restrict__ dft_stm,
-                                                                 float* __restrict__ dft_nstm, float* __restrict__ bias_partials) {
-    constexpr int NP = MODE == 1 ? 2 : 1;  // 16-byte pieces per position and thread
-    extern __shared__ __align__(16) unsigned char s_dyn[];  // ring [DG_STAGES][4 positions][NP][threads] float4
+                                                                 const float* __restrict__ ws, const void* __restrict__ pre_stm,
+                                                                 const void* __restrict__ pre_nstm, const float* __restrict__ ft_bias,
+                                                                 float scale, int F, int nb, int CW, void* __restrict__ dft_stm,
+                                                                 void* __restrict__ dft_nstm, float* __restrict__ bias_partials,
+                                                                 float grad_scale, unsigned long long* __restrict__ clamp_counter) {
+    constexpr int NP = MODE == 1 ? 2 : 1;  // pieces per position and thread
+    constexpr int ESZ = HALF ? 2 : 4;      // bytes per pre-activation / dft element
+    typedef typename std::conditional<HALF, uint2, float4>::type Piece;  // a thread's four columns of one row
+    extern __shared__ __align__(16) unsigned char s_dyn[];  // ring [DG_STAGES][4 positions][NP][threads] pieces
     __shared__ __align__(16) float sdl[DG_POS][L1];
     __shared__ int s_pos[DG_POS];
     const int persp = blockIdx.y;
@@ -1320,10 +1346,11 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
     const int Kin = MODE == 1 ? F : 2 * F;                        // row length of the L1 input
     const int cbase = (MODE == 1 ? persp * half : persp * F) + chunk * CW;  // first L1 input column of this block
     const int wcol = chunk * CW + 4 * threadIdx.x;                // column inside the perspective
-    const float* __restrict__ pre = persp ? pre_nstm : pre_stm;
-    float* __restrict__ dft = persp ? dft_nstm : dft_stm;
+    const unsigned char* __restrict__ pre = static_cast<const unsigned char*>(persp ? pre_nstm : pre_stm);
+    unsigned char* __restrict__ dft = static_cast<unsigned char*>(persp ? dft_nstm : dft_stm);
     float4 bacc0 = make_float4(0.f, 0.f, 0.f, 0.f), bacc1 = bacc0;
     float* bp = bias_partials + ((size_t)blockIdx.x * 2 + persp) * F;  // one partial row per (block, perspective)
+    unsigned clamps = 0;
 
     // the block's positions: tiles [first, last) of unit blockIdx.x / 2, contiguous in the bucket order
     const int u = blockIdx.x >> 1, h = blockIdx.x & 1;
@@ -1381,9 +1408,24 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
                                                            : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     // ring slot of (stage, position q, piece k) of this thread
-    float4* ring = reinterpret_cast<float4*>(s_dyn);
+    Piece* ring = reinterpret_cast<Piece*>(s_dyn);
     const int T = blockDim.x;
     auto slot = [&](int stage, int q, int k) { return ring + ((size_t)(stage * 4 + q) * NP + k) * T + threadIdx.x; };
+    auto copy_piece = [&](Piece* dst, const unsigned char* src) { if (HALF) dg_cp8(dst, src); else dg_cp16(dst, src); };
+    auto to_f4 = [&](const Piece& pc) {
+        if constexpr (HALF) { const float2 a = dk_unpack_h2(pc.x), b = dk_unpack_h2(pc.y); return make_float4(a.x, a.y, b.x, b.y); }
+        else return pc;
+    };
+    // stores a thread's four gradient values of one row: fp32 as they are; fp16 scaled, clamped, rounded
+    auto store_dft = [&](unsigned char* dst, const float4& gv) {
+        if constexpr (HALF) {
+            const float a = clamp_half_count(gv.x * grad_scale, clamps), b = clamp_half_count(gv.y * grad_scale, clamps);
+            const float c = clamp_half_count(gv.z * grad_scale, clamps), d = clamp_half_count(gv.w * grad_scale, clamps);
+            *reinterpret_cast<uint2*>(dst) = make_uint2(dk_pack_h2(a, b), dk_pack_h2(c, d));
+        } else {
+            *reinterpret_cast<float4*>(dst) = gv;
+        }
+    };
     auto issue = [&](int round) {  // copies of positions 4 * round .. + 3 (a missing position repeats the block's first)
         if (4 * round < n) {
             const int stage = round % DG_STAGES;
@@ -1391,8 +1433,8 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
             for (int q = 0; q < 4; ++q) {
                 const int r = 4 * round + q;
                 const int pl = s_pos[r < n ? r : 0];
-                dg_cp16(slot(stage, q, 0), pre + (size_t)pl * F + wcol);
-                if (MODE == 1) dg_cp16(slot(stage, q, 1), pre + (size_t)pl * F + half + wcol);
+                copy_piece(slot(stage, q, 0), pre + ((size_t)pl * F + wcol) * ESZ);
+                if (MODE == 1) copy_piece(slot(stage, q, 1), pre + ((size_t)pl * F + half + wcol) * ESZ);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per round, empty past the end
@@ -1422,9 +1464,9 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
                     d.x += gv[uu] * ww.x; d.y += gv[uu] * ww.y; d.z += gv[uu] * ww.z; d.w += gv[uu] * ww.w;
                 }
             }
-            const float4 xa = *slot(stage, q, 0);
+            const float4 xa = to_f4(*slot(stage, q, 0));
             if (MODE == 1) {
-                const float4 xb = *slot(stage, q, 1);
+                const float4 xb = to_f4(*slot(stage, q, 1));
                 const float4 a = make_float4(xa.x + bias0.x, xa.y + bias0.y, xa.z + bias0.z, xa.w + bias0.w);
                 const float4 b = make_float4(xb.x + bias1.x, xb.y + bias1.y, xb.z + bias1.z, xb.w + bias1.w);
                 float4 ga, gb;
@@ -1436,8 +1478,8 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
                 gb.y = (b.y > 0.f && b.y < 1.f) ? d.y * crelu01(a.y) * scale : 0.f;
                 gb.z = (b.z > 0.f && b.z < 1.f) ? d.z * crelu01(a.z) * scale : 0.f;
                 gb.w = (b.w > 0.f && b.w < 1.f) ? d.w * crelu01(a.w) * scale : 0.f;
-                *reinterpret_cast<float4*>(dft + (size_t)pp * F + wcol) = ga;   // read again by the FT backward: keep in L2
-                *reinterpret_cast<float4*>(dft + (size_t)pp * F + half + wcol) = gb;
+                store_dft(dft + ((size_t)pp * F + wcol) * ESZ, ga);   // read again by the FT backward: keep in L2
+                store_dft(dft + ((size_t)pp * F + half + wcol) * ESZ, gb);
                 bacc0.x += ga.x; bacc0.y += ga.y; bacc0.z += ga.z; bacc0.w += ga.w;
                 bacc1.x += gb.x; bacc1.y += gb.y; bacc1.z += gb.z; bacc1.w += gb.w;
             } else {
@@ -1455,7 +1497,7 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
                     g.z = d.z * ((a.z > 0.f && a.z < 1.f) ? 2.0f * a.z : 0.f);
                     g.w = d.w * ((a.w > 0.f && a.w < 1.f) ? 2.0f * a.w : 0.f);
                 }
-                *reinterpret_cast<float4*>(dft + (size_t)pp * F + wcol) = g;
+                store_dft(dft + ((size_t)pp * F + wcol) * ESZ, g);
                 bacc0.x += g.x; bacc0.y += g.y; bacc0.z += g.z; bacc0.w += g.w;
             }
         }
@@ -1463,6 +1505,10 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     *reinterpret_cast<float4*>(bp + wcol) = bacc0;
     if (MODE == 1) *reinterpret_cast<float4*>(bp + half + wcol) = bacc1;
+    if (HALF) {
+        clamps = __reduce_add_sync(0xffffffffu, clamps);
+        if ((threadIdx.x & 31) == 0 && clamps) atomicAdd(clamp_counter, (unsigned long long)clamps);
+    }
 }
 
 // out[c] = sum over the perspectives (stm first) and the blocks' partial rows; 32 lanes share a column's rows and
@@ -1485,9 +1531,9 @@ __global__ void __launch_bounds__(256) k_bias_partials_reduce(const float* __res
 
 int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int* order, const TileDesc* tiles,
                            const int* n_tiles, int max_tiles, const float* wb, const float* ws,
-                           const float* pre_stm, const float* pre_nstm, const float* ft_bias, float scale,
-                           int B, int F, int l1, int nb, float* dft_stm, float* dft_nstm, float* bias_partials,
-                           float* ft_b_grad, int n_ctas) {
+                           const void* pre_stm, const void* pre_nstm, const float* ft_bias, float scale,
+                           int B, int F, int l1, int nb, void* dft_stm, void* dft_nstm, float* bias_partials,
+                           float* ft_b_grad, int n_ctas, int half_act, float grad_scale, unsigned long long* clamp_counter) {
     (void)B;
     (void)max_tiles;
     const int work_cols = mode == 1 ? F / 2 : F;
@@ -1499,19 +1545,24 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
         const int CW = work_cols / n_chunks;
         bias_rows = 2 * max_units;
         dim3 grid(bias_rows, 2, n_chunks), block(CW / 4);
-        const size_t smem = (size_t)DG_STAGES * 4 * (mode == 1 ? 2 : 1) * (CW / 4) * 16;
-#define DGRAD_REG(M, L)                                                                                                  \
+        const size_t smem = (size_t)DG_STAGES * 4 * (mode == 1 ? 2 : 1) * (CW / 4) * (half_act ? 8 : 16);
+#define DGRAD_REG(M, L, H)                                                                                               \
     do {                                                                                                                 \
-        cudaFuncSetAttribute(k_l1_dgrad_ftgrad_stream<M, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);   \
-        k_l1_dgrad_ftgrad_stream<M, L><<<grid, block, smem, s>>>(dl1, order, tiles, tiles + max_tiles, n_tiles + 1, wb, ws, pre_stm, \
-                                                                 pre_nstm, ft_bias, scale, F, nb, CW, dft_stm, dft_nstm,  \
-                                                                 bias_partials);                                         \
+        cudaFuncSetAttribute(k_l1_dgrad_ftgrad_stream<M, L, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+        k_l1_dgrad_ftgrad_stream<M, L, H><<<grid, block, smem, s>>>(dl1, order, tiles, tiles + max_tiles, n_tiles + 1, wb, ws, pre_stm, \
+                                                                    pre_nstm, ft_bias, scale, F, nb, CW, dft_stm, dft_nstm, \
+                                                                    bias_partials, grad_scale, clamp_counter);           \
     } while (0)
-        if (l1 == 32) { if (mode == 1) DGRAD_REG(1, 32); else if (mode == 2) DGRAD_REG(2, 32); else DGRAD_REG(3, 32); }
-        else if (l1 == 16) { if (mode == 1) DGRAD_REG(1, 16); else if (mode == 2) DGRAD_REG(2, 16); else DGRAD_REG(3, 16); }
-        else { if (mode == 1) DGRAD_REG(1, 8); else if (mode == 2) DGRAD_REG(2, 8); else DGRAD_REG(3, 8); }
+        if (half_act) {  // fp16 activations: LayerStack only
+            if (mode != 1) return -1;
+            if (l1 == 32) DGRAD_REG(1, 32, true); else if (l1 == 16) DGRAD_REG(1, 16, true); else DGRAD_REG(1, 8, true);
+        }
+        else if (l1 == 32) { if (mode == 1) DGRAD_REG(1, 32, false); else if (mode == 2) DGRAD_REG(2, 32, false); else DGRAD_REG(3, 32, false); }
+        else if (l1 == 16) { if (mode == 1) DGRAD_REG(1, 16, false); else if (mode == 2) DGRAD_REG(2, 16, false); else DGRAD_REG(3, 16, false); }
+        else { if (mode == 1) DGRAD_REG(1, 8, false); else if (mode == 2) DGRAD_REG(2, 8, false); else DGRAD_REG(3, 8, false); }
 #undef DGRAD_REG
     } else {
+        if (half_act) return -1;  // the fp16 activations need the streaming kernel (l1 of 8, 16 or 32)
         int n_chunks = 1;
         while ((size_t)(work_cols / n_chunks) * l1 * 4 > 64 * 1024 || work_cols / n_chunks > 1024) n_chunks *= 2;
         const int CW = work_cols / n_chunks;
@@ -1520,8 +1571,9 @@ int launch_l1_dgrad_ftgrad(cudaStream_t s, int mode, const float* dl1, const int
 #define DGRAD_LAUNCH(M)                                                                                                  \
     do {                                                                                                                 \
         cudaFuncSetAttribute(k_l1_dgrad_ftgrad<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);       \
-        k_l1_dgrad_ftgrad<M><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, pre_stm, pre_nstm, ft_bias, \
-                                                         scale, F, l1, nb, CW, dft_stm, dft_nstm, bias_partials);        \
+        k_l1_dgrad_ftgrad<M><<<grid, block, smem, s>>>(dl1, order, tiles, n_tiles, wb, ws, static_cast<const float*>(pre_stm),  \
+                                                         static_cast<const float*>(pre_nstm), ft_bias, scale, F, l1, nb, CW, \
+                                                         static_cast<float*>(dft_stm), static_cast<float*>(dft_nstm), bias_partials); \
     } while (0)
         if (mode == 1) DGRAD_LAUNCH(1);
         else if (mode == 2) DGRAD_LAUNCH(2);

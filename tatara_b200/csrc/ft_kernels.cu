@@ -15,11 +15,32 @@
 // LayerStack activation never leaves the thread.  Rows are added in slot order with plain f32 adds:
 // the sums are bit-identical to sparse_ft_forward_cpu (sparse/sparse_ft_forward.rs:54-78).
 // ------------------------------------------------------------------------------------------------
-template <int MODE>
-__global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ table, const int* __restrict__ idx_stm,
+// four consecutive table / activation values as fp32, whatever their storage type
+template <bool H>
+static __device__ __forceinline__ float4 ld4(const void* base, size_t elem) {
+    if (H) {
+        const uint2 u = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(base) + elem));
+        const float2 a = unpack_h2(u.x), b = unpack_h2(u.y);
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    return __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem));
+}
+template <bool H>
+static __device__ __forceinline__ void st4_cs(void* base, size_t elem, float4 v) {
+    if (H) __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(base) + elem), make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w)));
+    else __stcs(reinterpret_cast<float4*>(static_cast<float*>(base) + elem), v);
+}
+static __device__ __forceinline__ float4 round_h4(float4 v) {
+    const float2 a = unpack_h2(pack_h2(v.x, v.y)), b = unpack_h2(pack_h2(v.z, v.w));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// TH: fp16 table rows (summed in fp32); OH: fp16 pre-activations, the activation computed from the rounded values
+template <int MODE, bool TH, bool OH>
+__global__ void __launch_bounds__(512) k_ft_forward(const void* __restrict__ table, const int* __restrict__ idx_stm,
                                                      const int* __restrict__ idx_nstm, const int* __restrict__ nnz,
-                                                     const float* __restrict__ bias, float* __restrict__ pre_stm,
-                                                     float* __restrict__ pre_nstm, float* __restrict__ combined,
+                                                     const float* __restrict__ bias, void* __restrict__ pre_stm,
+                                                     void* __restrict__ pre_nstm, float* __restrict__ combined,
                                                      const int* __restrict__ items, int n_items, int B, int F, int N, int A,
                                                      float scale, int ipc) {
     extern __shared__ int s_idx[];  // [ipc][A] indices, then [ipc] item ids
@@ -53,7 +74,6 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
     int n = nnz[item];
     n = n < 0 ? 0 : (n > A ? A : n);
     const int* my = s_idx + il * A;
-    const float4* __restrict__ t4 = reinterpret_cast<const float4*>(table);
     const int row4 = F >> 2;
     const int c0 = lane, c1 = lane + tpi;
 
@@ -64,9 +84,8 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
         for (int u = 0; u < 8; ++u) {
             const int f = (a0 + u < n) ? my[a0 + u] : -1;
             if (f >= 0) {
-                const float4* r = t4 + (size_t)f * row4;
-                va[u] = __ldg(r + c0);
-                vb[u] = __ldg(r + c1);
+                va[u] = ld4<TH>(table, (size_t)f * F + 4 * c0);
+                vb[u] = ld4<TH>(table, (size_t)f * F + 4 * c1);
             } else {
                 va[u] = make_float4(0.f, 0.f, 0.f, 0.f);  // x + 0.0 == x: a skipped slot leaves the sum unchanged
                 vb[u] = va[u];
@@ -79,16 +98,18 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
         }
     }
 
-    float4* pre = reinterpret_cast<float4*>(persp ? pre_nstm : pre_stm) + (size_t)item * row4;
+    void* pre = persp ? pre_nstm : pre_stm;
+    const size_t e0 = (size_t)item * F + 4 * c0, e1 = (size_t)item * F + 4 * c1;
+    if (OH) { acc0 = round_h4(acc0); acc1 = round_h4(acc1); }
     // outputs are written once and read by later kernels only: streaming stores leave L2 to the table slice
     if (MODE == 0) {
-        __stcs(pre + c0, acc0);
-        __stcs(pre + c1, acc1);
+        st4_cs<OH>(pre, e0, acc0);
+        st4_cs<OH>(pre, e1, acc1);
     } else if (MODE == 1) {
         // ft_post_perspective_fwd (layerstack/ft_post_perspective.rs:57-83): the raw sums are kept for the
         // backward pass, combined[b, persp*F/2 + r] = crelu(x_r + b_r) * crelu(x_{r+F/2} + b_{r+F/2}) * scale
-        __stcs(pre + c0, acc0);
-        __stcs(pre + c1, acc1);
+        st4_cs<OH>(pre, e0, acc0);
+        st4_cs<OH>(pre, e1, acc1);
         const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias) + c0);
         const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + c1);
         float4 o;
@@ -104,8 +125,8 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
         const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias) + c1);
         float4 x0 = make_float4(acc0.x + b0.x, acc0.y + b0.y, acc0.z + b0.z, acc0.w + b0.w);
         float4 x1 = make_float4(acc1.x + b1.x, acc1.y + b1.y, acc1.z + b1.z, acc1.w + b1.w);
-        __stcs(pre + c0, x0);
-        __stcs(pre + c1, x1);
+        st4_cs<OH>(pre, e0, x0);
+        st4_cs<OH>(pre, e1, x1);
         float4 a0 = make_float4(crelu01(x0.x), crelu01(x0.y), crelu01(x0.z), crelu01(x0.w));
         float4 a1 = make_float4(crelu01(x1.x), crelu01(x1.y), crelu01(x1.z), crelu01(x1.w));
         if (MODE == 3) {
@@ -118,9 +139,9 @@ __global__ void __launch_bounds__(512) k_ft_forward(const float* __restrict__ ta
     }
 }
 
-int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
-                      const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
-                      const int* items, int B, int F, int N, int A, float scale, int n_persp) {
+int launch_ft_forward(cudaStream_t s, int mode, const void* table, const int* idx_stm, const int* idx_nstm,
+                      const int* nnz, const float* bias, void* pre_stm, void* pre_nstm, float* combined,
+                      const int* items, int B, int F, int N, int A, float scale, int n_persp, int table_half, int out_half) {
     if (B <= 0) return 0;
     const int tpi = F / 8;
     int ipc = 256 / tpi;
@@ -129,11 +150,19 @@ int launch_ft_forward(cudaStream_t s, int mode, const float* table, const int* i
     dim3 grid(ceil_div(n_items, ipc)), block(ipc * tpi);
     size_t smem = (size_t)ipc * (A + 1) * sizeof(int);
 #define FT_FWD_ARGS table, idx_stm, idx_nstm, nnz, bias, pre_stm, pre_nstm, combined, items, n_items, B, F, N, A, scale, ipc
+    if (table_half) {
+        if (mode == 0 && !out_half) k_ft_forward<0, true, false><<<grid, block, smem, s>>>(FT_FWD_ARGS);
+        else if (mode == 1 && !out_half) k_ft_forward<1, true, false><<<grid, block, smem, s>>>(FT_FWD_ARGS);
+        else if (mode == 1) k_ft_forward<1, true, true><<<grid, block, smem, s>>>(FT_FWD_ARGS);
+        else return -1;
+        return 1;
+    }
+    if (out_half) return -1;
     switch (mode) {
-        case 0: k_ft_forward<0><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
-        case 1: k_ft_forward<1><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
-        case 2: k_ft_forward<2><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
-        default: k_ft_forward<3><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        case 0: k_ft_forward<0, false, false><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        case 1: k_ft_forward<1, false, false><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        case 2: k_ft_forward<2, false, false><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
+        default: k_ft_forward<3, false, false><<<grid, block, smem, s>>>(FT_FWD_ARGS); break;
     }
 #undef FT_FWD_ARGS
     return 1;
@@ -229,15 +258,21 @@ __global__ void __launch_bounds__(256) k_fwd_codes(const int* __restrict__ idx_s
     if (outside) *outside_flag = 1;
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __restrict__ table, const float* __restrict__ bias,
-                                                               float* __restrict__ pre_stm, float* __restrict__ pre_nstm,
+// TH: the table holds fp16 rows (the strip is then 64 columns wide: a lane reads 16 bytes = eight columns of every row and
+// sums them in fp32, native_kernels.cu:743-801 sparse_ft_forward_fp16); OH: the pre-activations are stored as fp16 and the
+// activation is computed from the rounded value (sparse_ft_forward_fp16_out + ft_post_perspective_fwd_fp16, :837-863).
+template <int MODE, bool TH, bool OH>
+__global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const void* __restrict__ table_v, const float* __restrict__ bias,
+                                                               void* __restrict__ pre_stm_v, void* __restrict__ pre_nstm_v,
                                                                float* __restrict__ combined, const int* __restrict__ idx_stm,
                                                                const int* __restrict__ idx_nstm, const int* __restrict__ info,
                                                                const uint4* __restrict__ codes, const FwdWork* __restrict__ work,
                                                                const int* __restrict__ n_work, int n_items, int B, int F, int N,
                                                                int A, int A_pad, int rps, float scale) {
-    // strip [rps + 1][32] floats, then two buffers of [32 warps][4 items][A_pad] 16-bit row codes
+    constexpr int W = TH ? 8 : 4;          // columns per lane
+    constexpr int TSZ = TH ? 2 : 4;        // bytes per table element
+    constexpr int OSZ = OH ? 2 : 4;        // bytes per stored pre-activation
+    // strip [rps + 1][8 W] elements (128 bytes per row), then two buffers of [32 warps][4 items][A_pad] 16-bit row codes
     extern __shared__ __align__(16) unsigned char s_raw[];
     if ((int)blockIdx.x >= *n_work) return;
     const FwdWork wk = work[blockIdx.x];
@@ -245,15 +280,16 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
     const int row0 = wk.slice * rps;
     const int rows = max(0, min(rps, N - row0));
     const int half = F >> 1;
-    const int cA = MODE == 1 ? 16 * strip : 32 * strip;  // first column of the strip's first 16 (or all 32) columns
-    const int cB = MODE == 1 ? half + 16 * strip : cA + 16;
+    const int cA = MODE == 1 ? 4 * W * strip : 8 * W * strip;  // first column of the strip's first half (or of all its columns)
+    const int cB = MODE == 1 ? half + 4 * W * strip : cA + 4 * W;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 3, j = lane & 7;
-    const int mycol = j < 4 ? cA + 4 * j : cB + 4 * (j - 4);
+    const int mycol = j < 4 ? cA + W * j : cB + W * (j - 4);
+    const unsigned char* __restrict__ table = static_cast<const unsigned char*>(table_v);
 
     // strip fill: thread e & 7 == j copies the 16 bytes it will later read, for rows e >> 3
     for (int e = threadIdx.x; e < rows * 8; e += blockDim.x)
-        cp_async16(s_raw + (size_t)e * 16, table + (size_t)(row0 + (e >> 3)) * F + mycol, 16);
+        cp_async16(s_raw + (size_t)e * 16, table + ((size_t)(row0 + (e >> 3)) * F + mycol) * TSZ, 16);
     if (threadIdx.x < 32) reinterpret_cast<float*>(s_raw)[rps * 32 + threadIdx.x] = 0.f;  // the row of zeros
     for (int e = rows * 8 + threadIdx.x; e < rps * 8; e += blockDim.x)  // rows past the end of the table
         *reinterpret_cast<float4*>(s_raw + (size_t)e * 16) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -279,11 +315,13 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
     cp_async_wait<0>();
     __syncthreads();
 
-    const float4 mybias = bias ? *reinterpret_cast<const float4*>(bias + mycol) : make_float4(0.f, 0.f, 0.f, 0.f);
+    // fp32 lanes keep the bias of their four columns and of the pair partner's in registers; fp16 lanes (eight columns)
+    // read it in the epilogue instead (L1 hits), their registers are taken by the wider running sums
+    float4 mybias = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!TH && bias) mybias = *reinterpret_cast<const float4*>(bias + mycol);
     float4 pbias = mybias;  // the pair partner's bias (LayerStack)
     pbias.x = __shfl_xor_sync(0xffffffffu, mybias.x, 4); pbias.y = __shfl_xor_sync(0xffffffffu, mybias.y, 4);
     pbias.z = __shfl_xor_sync(0xffffffffu, mybias.z, 4); pbias.w = __shfl_xor_sync(0xffffffffu, mybias.w, 4);
-    const ulonglong2* __restrict__ t2 = reinterpret_cast<const ulonglong2*>(table);
     const unsigned char* s_lane = s_raw + 16 * j;
 
     int buf = 0;
@@ -298,7 +336,8 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
         const int it_c = inf < 0 ? -1 : (inf & ~SLICE_SLOW_BIT);
         const unsigned char* my_codes = s_codes + buf * buf_stride + g * A_pad * 2;
 
-        unsigned long long a0 = 0ull, a1 = 0ull;  // columns (0, 1) and (2, 3) of the lane
+        LaneAcc<TH> acc;
+        acc.zero();
         if (!slow) {
             // every row of the round comes from the strip: branch-free; a slot without a feature reads the row of zeros
             // (x + 0.0 == x), rows are added in slot order
@@ -313,14 +352,8 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
                 const ulonglong2 v5 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.z >> 16) * 128u);
                 const ulonglong2 v6 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.w & 0xffffu) * 128u);
                 const ulonglong2 v7 = *reinterpret_cast<const ulonglong2*>(s_lane + (c.w >> 16) * 128u);
-                a0 = fadd2(a0, v0.x); a1 = fadd2(a1, v0.y);
-                a0 = fadd2(a0, v1.x); a1 = fadd2(a1, v1.y);
-                a0 = fadd2(a0, v2.x); a1 = fadd2(a1, v2.y);
-                a0 = fadd2(a0, v3.x); a1 = fadd2(a1, v3.y);
-                a0 = fadd2(a0, v4.x); a1 = fadd2(a1, v4.y);
-                a0 = fadd2(a0, v5.x); a1 = fadd2(a1, v5.y);
-                a0 = fadd2(a0, v6.x); a1 = fadd2(a1, v6.y);
-                a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
+                acc.add(v0); acc.add(v1); acc.add(v2); acc.add(v3);
+                acc.add(v4); acc.add(v5); acc.add(v6); acc.add(v7);
             }
         } else {
             const int p = it_c >= B, bb = it_c < 0 ? 0 : it_c - p * B;
@@ -329,40 +362,80 @@ __global__ void __launch_bounds__(1024, 1) k_ft_forward_slice(const float* __res
                 const unsigned c = reinterpret_cast<const unsigned short*>(my_codes)[q];
                 ulonglong2 v;
                 if (c != SLICE_OUTSIDE || it_c < 0) v = *reinterpret_cast<const ulonglong2*>(s_lane + min(c, (unsigned)rps) * 128u);
-                else v = __ldg(t2 + (((size_t)__ldg(ip + q) * F + mycol) >> 2));
-                a0 = fadd2(a0, v.x); a1 = fadd2(a1, v.y);
+                else v = __ldg(reinterpret_cast<const ulonglong2*>(table + ((size_t)__ldg(ip + q) * F + mycol) * TSZ));
+                acc.add(v);
             }
         }
         __syncwarp();  // all lanes are done with this round's codes before the next round overwrites the other buffer's twin
-        const float4 acc = make_float4(lo_f(a0), hi_f(a0), lo_f(a1), hi_f(a1));
 
-        // ---- epilogue
+        // ---- epilogue: x[] = the lane's sums as the later kernels will read them (rounded to fp16 when stored so)
+        float x[W];
+#pragma unroll
+        for (int i = 0; i < W; ++i) x[i] = acc.get(i);
         const bool valid = it_c >= 0;
         const int persp = it_c >= B, b = valid ? it_c - persp * B : 0;
-        float* pre = (persp ? pre_nstm : pre_stm) + (size_t)b * F;
+        unsigned char* pre = static_cast<unsigned char*>(persp ? pre_nstm_v : pre_stm_v) + ((size_t)b * F + mycol) * OSZ;
+        auto store_pre = [&](const float* val) {
+            if (OH) {
+                unsigned h[W / 2];
+#pragma unroll
+                for (int i = 0; i < W / 2; ++i) h[i] = pack_h2(val[2 * i], val[2 * i + 1]);
+                if (W == 8) __stcs(reinterpret_cast<uint4*>(pre), make_uint4(h[0], h[1], h[W / 2 - 2], h[W / 2 - 1]));
+                else __stcs(reinterpret_cast<uint2*>(pre), make_uint2(h[0], h[1]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < W; i += 4) __stcs(reinterpret_cast<float4*>(pre) + i / 4, make_float4(val[i], val[i + 1], val[i + 2], val[i + 3]));
+            }
+        };
+        if (OH) {
+#pragma unroll
+            for (int i = 0; i < W; i += 2) {
+                const float2 r = unpack_h2(pack_h2(x[i], x[i + 1]));
+                x[i] = r.x; x[i + 1] = r.y;
+            }
+        }
         if (MODE == 0) {
-            if (valid) __stcs(reinterpret_cast<float4*>(pre + mycol), acc);
+            if (valid) store_pre(x);
         } else if (MODE == 1) {
-            float4 pa;
-            pa.x = __shfl_xor_sync(0xffffffffu, acc.x, 4); pa.y = __shfl_xor_sync(0xffffffffu, acc.y, 4);
-            pa.z = __shfl_xor_sync(0xffffffffu, acc.z, 4); pa.w = __shfl_xor_sync(0xffffffffu, acc.w, 4);
+            float px[W];  // the pair partner's values
+#pragma unroll
+            for (int i = 0; i < W; ++i) px[i] = __shfl_xor_sync(0xffffffffu, x[i], 4);
             if (valid) {
-                __stcs(reinterpret_cast<float4*>(pre + mycol), acc);
+                store_pre(x);
                 if (j < 4) {
-                    float4 o;
-                    o.x = crelu01(acc.x + mybias.x) * crelu01(pa.x + pbias.x) * scale;
-                    o.y = crelu01(acc.y + mybias.y) * crelu01(pa.y + pbias.y) * scale;
-                    o.z = crelu01(acc.z + mybias.z) * crelu01(pa.z + pbias.z) * scale;
-                    o.w = crelu01(acc.w + mybias.w) * crelu01(pa.w + pbias.w) * scale;
-                    __stcs(reinterpret_cast<float4*>(combined + (size_t)b * F + persp * half + cA + 4 * j), o);
+                    float o[W], bm[W], bp[W];
+                    if (TH) {
+#pragma unroll
+                        for (int i = 0; i < W; i += 4) {
+                            const float4 u = __ldg(reinterpret_cast<const float4*>(bias + mycol + i));
+                            const float4 w = __ldg(reinterpret_cast<const float4*>(bias + half + mycol + i));
+                            bm[i] = u.x; bm[i + 1] = u.y; bm[i + 2] = u.z; bm[i + 3] = u.w;
+                            bp[i] = w.x; bp[i + 1] = w.y; bp[i + 2] = w.z; bp[i + 3] = w.w;
+                        }
+                    } else {
+                        bm[0] = mybias.x; bm[1] = mybias.y; bm[2] = mybias.z; bm[3] = mybias.w;
+                        bp[0] = pbias.x; bp[1] = pbias.y; bp[2] = pbias.z; bp[3] = pbias.w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < W; ++i) o[i] = crelu01(x[i] + bm[i]) * crelu01(px[i] + bp[i]) * scale;
+                    float4* dst = reinterpret_cast<float4*>(combined + (size_t)b * F + persp * half + mycol);
+#pragma unroll
+                    for (int i = 0; i < W; i += 4) __stcs(dst + i / 4, make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]));
                 }
             }
         } else if (valid) {
-            const float4 x = make_float4(acc.x + mybias.x, acc.y + mybias.y, acc.z + mybias.z, acc.w + mybias.w);
-            __stcs(reinterpret_cast<float4*>(pre + mycol), x);
-            float4 a = make_float4(crelu01(x.x), crelu01(x.y), crelu01(x.z), crelu01(x.w));
-            if (MODE == 3) { a.x *= a.x; a.y *= a.y; a.z *= a.z; a.w *= a.w; }
-            __stcs(reinterpret_cast<float4*>(combined + (size_t)b * 2 * F + persp * F + mycol), a);
+            float y[W], a[W];
+            const float bz[4] = {mybias.x, mybias.y, mybias.z, mybias.w};
+#pragma unroll
+            for (int i = 0; i < W; ++i) {
+                y[i] = x[i] + (TH ? __ldg(bias + mycol + i) : bz[i & 3]);
+                a[i] = crelu01(y[i]);
+                if (MODE == 3) a[i] *= a[i];
+            }
+            store_pre(y);
+            float4* dst = reinterpret_cast<float4*>(combined + (size_t)b * 2 * F + persp * F + mycol);
+#pragma unroll
+            for (int i = 0; i < W; i += 4) __stcs(dst + i / 4, make_float4(a[i], a[i + 1], a[i + 2], a[i + 3]));
         }
     }
     cp_async_wait<0>();  // nothing of this block is in flight when it leaves
@@ -378,13 +451,13 @@ static inline size_t slice_smem_bytes(int rps, int A) { return ((size_t)rps + 1)
 
 bool ft_forward_slice_supported(int F, int N, int A, int rps) {
     int n_slices = ceil_div(N, rps);
-    return F % 32 == 0 && A <= 64 && rps < 0xFFFF && slice_smem_bytes(rps, A) <= 227 * 1024 && n_slices + 1 <= SORT_KEYS_MAX;
+    return F % 128 == 0 && A <= 64 && rps < 0xFFFF && slice_smem_bytes(rps, A) <= 227 * 1024 && n_slices + 1 <= SORT_KEYS_MAX;
 }
 
-int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const int* idx_stm, const int* idx_nstm,
-                            const int* nnz, const float* bias, float* pre_stm, float* pre_nstm, float* combined,
+int launch_ft_forward_slice(cudaStream_t s, int mode, const void* table, const int* idx_stm, const int* idx_nstm,
+                            const int* nnz, const float* bias, void* pre_stm, void* pre_nstm, float* combined,
                             const int* items, const int* item_seg, int* work, int B, int F, int N, int A, int rps,
-                            float scale, int n_persp) {
+                            float scale, int n_persp, int table_half, int out_half) {
     if (B <= 0) return 0;
     const int n_items = n_persp * B;
     const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
@@ -399,19 +472,27 @@ int launch_ft_forward_slice(cudaStream_t s, int mode, const float* table, const 
     k_fwd_codes<<<ceil_div(n_items, 256), 256, 0, s>>>(idx_stm, idx_nstm, nnz, items, item_seg, n_keys, n_items, B, N, A, A_pad,
                                                        rps, codes, info, sb.outside_flag);
     const size_t smem = slice_smem_bytes(rps, A);
-    dim3 grid(max_work, F / 32);
-#define FT_SLICE_LAUNCH(M)                                                                                        \
-    do {                                                                                                          \
-        cudaFuncSetAttribute(k_ft_forward_slice<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-        k_ft_forward_slice<M><<<grid, 1024, smem, s>>>(table, bias, pre_stm, pre_nstm, combined, idx_stm, idx_nstm, \
-                                                       info, codes, wk, n_work, n_items, B, F, N, A, A_pad, rps,  \
-                                                       scale);                                                    \
+    dim3 grid(max_work, table_half ? F / 64 : F / 32);
+#define FT_SLICE_LAUNCH(M, TH, OH)                                                                                       \
+    do {                                                                                                                 \
+        cudaFuncSetAttribute(k_ft_forward_slice<M, TH, OH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+        k_ft_forward_slice<M, TH, OH><<<grid, 1024, smem, s>>>(table, bias, pre_stm, pre_nstm, combined, idx_stm, idx_nstm, \
+                                                               info, codes, wk, n_work, n_items, B, F, N, A, A_pad, rps, \
+                                                               scale);                                                   \
     } while (0)
-    switch (mode) {
-        case 0: FT_SLICE_LAUNCH(0); break;
-        case 1: FT_SLICE_LAUNCH(1); break;
-        case 2: FT_SLICE_LAUNCH(2); break;
-        default: FT_SLICE_LAUNCH(3); break;
+    if (table_half) {  // fp16 table: the raw gather (mode 0) and the LayerStack activation, with fp32 or fp16 pre-activations
+        if (mode == 0 && !out_half) FT_SLICE_LAUNCH(0, true, false);
+        else if (mode == 1 && !out_half) FT_SLICE_LAUNCH(1, true, false);
+        else if (mode == 1) FT_SLICE_LAUNCH(1, true, true);
+        else return -1;
+    } else {
+        if (out_half) return -1;
+        switch (mode) {
+            case 0: FT_SLICE_LAUNCH(0, false, false); break;
+            case 1: FT_SLICE_LAUNCH(1, false, false); break;
+            case 2: FT_SLICE_LAUNCH(2, false, false); break;
+            default: FT_SLICE_LAUNCH(3, false, false); break;
+        }
     }
 #undef FT_SLICE_LAUNCH
     return 3;
@@ -683,15 +764,16 @@ __global__ void k_bwd_plan(const int* __restrict__ offsets, int N, int n_persp, 
     for (int i = 0; i < parts; ++i) work[base + i] = make_int2(f, i);
 }
 
-static __device__ __forceinline__ float4 sum_rows(const float4* __restrict__ d, const int* __restrict__ L, int beg, int end,
-                                                  int row4, int c, float4 acc) {
+template <bool DH>
+static __device__ __forceinline__ float4 sum_rows(const void* __restrict__ d, const int* __restrict__ L, int beg, int end,
+                                                  int F, int c, float4 acc) {
     for (int j = beg; j < end; j += 8) {
         int bi[8];
         float4 v[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) bi[u] = __ldg(L + min(j + u, end - 1));
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = __ldg(d + (size_t)bi[u] * row4 + c);
+        for (int u = 0; u < 8; ++u) v[u] = ld4<DH>(d, (size_t)bi[u] * F + 4 * c);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (j + u < end) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
@@ -700,7 +782,10 @@ static __device__ __forceinline__ float4 sum_rows(const float4* __restrict__ d, 
     return acc;
 }
 
-__global__ void __launch_bounds__(512) k_ft_backward_short(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+// DH: the incoming gradient rows are fp16 (summed in fp32, native_kernels.cu:1081-1140); the sums are then left in the
+// rows' loss scale, which the optimizer takes out again
+template <bool DH>
+__global__ void __launch_bounds__(512) k_ft_backward_short(const void* __restrict__ dft_stm, const void* __restrict__ dft_nstm,
                                                              const int* __restrict__ offsets, const int* __restrict__ lists,
                                                              int B, int A, int N, int F, int n_persp, float* __restrict__ grad, const int* __restrict__ run_if) {
     if (run_if && *run_if == 0) return;  // gated: another path does this step's work
@@ -713,28 +798,16 @@ __global__ void __launch_bounds__(512) k_ft_backward_short(const float* __restri
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int p = 0; p < n_persp; ++p) {
         const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
-        const int* __restrict__ L = lists + (size_t)p * B * A;
-        const float4* __restrict__ d = reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm);
-        for (int j = beg; j < end; j += 8) {
-            // unconditional loads (a slot past the end re-reads the last row and is dropped below), so that all
-            // eight row loads are in flight together
-            int bi[8];
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) bi[u] = __ldg(L + min(j + u, end - 1));
-#pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = __ldg(d + (size_t)bi[u] * row4 + c);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (j + u < end) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
-            }
-        }
+        // unconditional loads (a slot past the end re-reads the last row and is dropped), so that all eight row loads
+        // are in flight together
+        acc = sum_rows<DH>(p ? dft_nstm : dft_stm, lists + (size_t)p * B * A, beg, end, F, c, acc);
     }
     reinterpret_cast<float4*>(grad)[(size_t)f * row4 + c] = acc;
     }
 }
 
-__global__ void __launch_bounds__(512) k_ft_backward_long(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+template <bool DH>
+__global__ void __launch_bounds__(512) k_ft_backward_long(const void* __restrict__ dft_stm, const void* __restrict__ dft_nstm,
                                                             const int* __restrict__ offsets, const int* __restrict__ lists,
                                                             int B, int A, int N, int F, int n_persp,
                                                             const int* __restrict__ counters, const int2* __restrict__ work,
@@ -752,8 +825,7 @@ __global__ void __launch_bounds__(512) k_ft_backward_long(const float* __restric
             const int beg = offsets[(size_t)p * (N + 1) + f], len = offsets[(size_t)p * (N + 1) + f + 1] - beg;
             const int a = max(lo, 0), b = min(hi, len);
             if (a < b)
-                acc = sum_rows(reinterpret_cast<const float4*>(p ? dft_nstm : dft_stm), lists + (size_t)p * B * A, beg + a, beg + b,
-                               row4, c, acc);
+                acc = sum_rows<DH>(p ? dft_nstm : dft_stm, lists + (size_t)p * B * A, beg + a, beg + b, F, c, acc);
             lo -= len;
             hi -= len;
         }
@@ -783,9 +855,9 @@ __global__ void __launch_bounds__(512) k_ft_backward_long_final(const int* __res
 int ft_backward_max_work(int B, int A, int n_persp) { return 2 * (int)(((long long)n_persp * B * A) / BWD_PART) + 2; }
 
 // plan: [2] counters, then [2 * max_work] work items, then [3 * N] long-feature records; partial: [max_work][F]
-int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft_stm, const float* dft_nstm, const int* offsets,
+int launch_ft_backward_split(cudaStream_t s, const int* run_if, const void* dft_stm, const void* dft_nstm, const int* offsets,
                              const int* lists, int B, int A, int N, int F, int n_persp, int* plan, float* partial,
-                             float* grad) {
+                             float* grad, int dft_half) {
     const int max_work = ft_backward_max_work(B, A, n_persp);
     int* counters = plan;
     int2* work = reinterpret_cast<int2*>(plan + 2);
@@ -794,8 +866,14 @@ int launch_ft_backward_split(cudaStream_t s, const int* run_if, const float* dft
     k_bwd_plan<<<ceil_div(N, 256), 256, 0, s>>>(offsets, N, n_persp, counters, work, longf, run_if);
     const int ny = ceil_div(F / 4, 512), bx = F / 4 / ny;  // at most 512 threads per block: room for 64 registers each
     // a gated launch (run_if) normally returns at once: a small grid of row-striding blocks keeps that cheap
-    k_ft_backward_short<<<dim3(run_if && N > 148 * 32 ? 148 * 32 : N, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
-    k_ft_backward_long<<<dim3(148 * 4, ny), bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial, run_if);
+    const dim3 gs(run_if && N > 148 * 32 ? 148 * 32 : N, ny), gl(148 * 4, ny);
+    if (dft_half) {
+        k_ft_backward_short<true><<<gs, bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
+        k_ft_backward_long<true><<<gl, bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial, run_if);
+    } else {
+        k_ft_backward_short<false><<<gs, bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, grad, run_if);
+        k_ft_backward_long<false><<<gl, bx, 0, s>>>(dft_stm, dft_nstm, offsets, lists, B, A, N, F, n_persp, counters, work, partial, run_if);
+    }
     k_ft_backward_long_final<<<dim3(148 * 2, ny), bx, 0, s>>>(counters, longf, partial, F, grad, run_if);
     return 4;
 }
@@ -821,8 +899,10 @@ int launch_ft_reduce_virtual(cudaStream_t s, float* grad, int N, int pi, int F) 
     return 1;
 }
 
-// ft_fold_virtual (sparse/ft_factorize.rs:78-99): comb[f] = w[f] + w[N + f % pi]
-__global__ void k_ft_fold(const float* __restrict__ w, float* __restrict__ comb, int N, int pi, int F) {
+// ft_fold_virtual (sparse/ft_factorize.rs:78-99): comb[f] = w[f] + w[N + f % pi]; HC: rounded to fp16
+// (ft_fold_virtual_f16, native_kernels.cu:262-318)
+template <bool HC>
+__global__ void k_ft_fold(const float* __restrict__ w, void* __restrict__ comb, int N, int pi, int F) {
     const int row4 = F >> 2;
     const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (i >= (long long)N * row4) return;
@@ -830,11 +910,31 @@ __global__ void k_ft_fold(const float* __restrict__ w, float* __restrict__ comb,
     const float4* w4 = reinterpret_cast<const float4*>(w);
     const float4 a = w4[i];
     const float4 b = w4[(size_t)(N + f % pi) * row4 + c];
-    reinterpret_cast<float4*>(comb)[i] = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+    const float4 v = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+    if (HC) static_cast<uint2*>(comb)[i] = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
+    else static_cast<float4*>(comb)[i] = v;
 }
 
-int launch_ft_fold(cudaStream_t s, const float* w, float* comb, int N, int pi, int F) {
+int launch_ft_fold(cudaStream_t s, const float* w, void* comb, int N, int pi, int F, int half_comb) {
     const long long n = (long long)N * (F / 4);
-    k_ft_fold<<<(int)((n + 255) / 256), 256, 0, s>>>(w, comb, N, pi, F);
+    if (half_comb) k_ft_fold<true><<<(int)((n + 255) / 256), 256, 0, s>>>(w, comb, N, pi, F);
+    else k_ft_fold<false><<<(int)((n + 255) / 256), 256, 0, s>>>(w, comb, N, pi, F);
+    return 1;
+}
+
+// cast_f32_to_f16 (native_kernels.cu:648): the fp16 mirror of an fp32 table
+__global__ void k_cast_half(const float4* __restrict__ src, uint2* __restrict__ dst, long long n4) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+        const float4 v = src[i];
+        dst[i] = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
+    }
+}
+
+int launch_cast_half(cudaStream_t s, const float* src, void* dst, int64_t n) {
+    const long long n4 = n / 4;
+    long long blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    k_cast_half<<<(int)blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(src), static_cast<uint2*>(dst), n4);
     return 1;
 }

@@ -64,7 +64,7 @@ static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
 
 bool ft_backward_slice_supported(int F, int N, int A, int rps) {
     const int n_slices = ceil_div(N, rps);
-    if (!(F % 32 == 0 && A <= 64 && rps <= INV_SORT_N && n_slices + 1 <= SORT_KEYS_LIMIT)) return false;
+    if (!(F % 128 == 0 && A <= 64 && rps <= INV_SORT_N && n_slices + 1 <= SORT_KEYS_LIMIT)) return false;
     return bwd_layout(1024, A, rps).CH >= 64;
 }
 
@@ -271,8 +271,10 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
     }
 }
 
-// grad[row][32-column strip] for the rows of one slice; see the head of the file.
-__global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __restrict__ dft_stm, const float* __restrict__ dft_nstm,
+// grad[row][column strip] for the rows of one slice; see the head of the file.  DH: the dft rows are fp16 (the strip is
+// then 64 columns wide, a lane sums eight columns in fp32; the sums keep the rows' loss scale).
+template <bool DH>
+__global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __restrict__ dft_stm, const void* __restrict__ dft_nstm,
                                                                 const int* __restrict__ info, const FwdWork* __restrict__ work,
                                                                 const int* __restrict__ first, const int* __restrict__ len,
                                                                 const unsigned long long* __restrict__ rowinfo,
@@ -280,7 +282,11 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                                                                 const int* __restrict__ outside_flag, int B, int F, int N, int rps,
                                                                 int rps_pad, int CH, int region, int slice_begin,
                                                                 float* __restrict__ grad) {
-    // dft strip [CH + 1][32] floats (the last row stays zero), row records [rps_pad] 64-bit, list cells [region] 16-bit
+    constexpr int W = DH ? 8 : 4;    // columns per lane
+    constexpr int DSZ = DH ? 2 : 4;  // bytes per dft element
+    typedef LaneAcc<DH> Acc;
+    // dft strip [CH + 1][8 W] elements, 128 bytes per row (the last row stays zero), row records [rps_pad] 64-bit, list
+    // cells [region] 16-bit
     extern __shared__ __align__(16) unsigned char s_raw[];
     __shared__ int s_ctl[4];
     __shared__ int s_desc[BWD_DESC][5];
@@ -290,11 +296,14 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
     const int rows = min(rps, N - row0);
     const int tid = threadIdx.x, lane = tid & 31;
     const int j = lane & 7;
-    const int col = 32 * strip + 4 * j;
+    const int col = 8 * W * strip + W * j;
     const int c_first = first[k], c_end = first[k + 1];
     if (c_first == c_end) {  // no item reads this slice: its gradient rows are zero
-        for (int e = tid; e < rows * 8; e += 1024)
-            *reinterpret_cast<float4*>(grad + (size_t)(row0 + (e >> 3)) * F + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int e = tid; e < rows * 8; e += 1024) {
+            float4* gp = reinterpret_cast<float4*>(grad + (size_t)(row0 + (e >> 3)) * F + col);
+#pragma unroll
+            for (int i = 0; i < W / 4; ++i) gp[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         return;
     }
     unsigned char* s_dft = s_raw;
@@ -302,6 +311,8 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
     unsigned char* s_lists = reinterpret_cast<unsigned char*>(s_info + rps_pad);
     if (tid < 32) reinterpret_cast<float*>(s_dft)[CH * 32 + tid] = 0.f;
     const unsigned char* s_lane = s_dft + 16 * j;
+    const unsigned char* __restrict__ d_stm = static_cast<const unsigned char*>(dft_stm);
+    const unsigned char* __restrict__ d_nstm = static_cast<const unsigned char*>(dft_nstm);
 
     // the slice's chunk descriptors, fetched once (BWD_DESC at most; a slice with more chunks reads the rest as it goes)
     for (int i = tid; i < min(c_end - c_first, BWD_DESC); i += 1024) {
@@ -340,7 +351,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 if (e < n * 8) {
                     const int it = itv[u] & ~SLICE_SLOW_BIT;
                     const int p = it >= B, b = it - p * B;
-                    cp_async16(s_dft + (size_t)e * 16, (p ? dft_nstm : dft_stm) + (size_t)b * F + col, 16);
+                    cp_async16(s_dft + (size_t)e * 16, (p ? d_nstm : d_stm) + ((size_t)b * F + col) * DSZ, 16);
                 }
             }
         }
@@ -355,9 +366,9 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
         // after the rest of the chunk.  All other records are handed out four at a time (neighbours in the order, so of
         // similar length) from a block-wide counter.
         const int n_rec = first_chunk ? rps : n_live;
-        // sum of the list cells [beg, end) of one record, continuing from (a0, a1); beg is a multiple of 8.  Called by all
+        // sum of the list cells [beg, end) of one record, continuing from acc; beg is a multiple of 8.  Called by all
         // 32 lanes together (a group without a list passes an empty range)
-        auto sum_range = [&](const unsigned char* lp, int beg, int end, unsigned long long& a0, unsigned long long& a1) {
+        auto sum_range = [&](const unsigned char* lp, int beg, int end, Acc& acc) {
             const int full = beg + ((end - beg) & ~7);
             for (int q = beg; q < full; q += 8) {
                 const uint4 cc = *reinterpret_cast<const uint4*>(lp + 2 * q);
@@ -369,14 +380,8 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                 const ulonglong2 v5 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.z >> 16) * 128u);
                 const ulonglong2 v6 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.w & 0xffffu) * 128u);
                 const ulonglong2 v7 = *reinterpret_cast<const ulonglong2*>(s_lane + (cc.w >> 16) * 128u);
-                a0 = fadd2(a0, v0.x); a1 = fadd2(a1, v0.y);
-                a0 = fadd2(a0, v1.x); a1 = fadd2(a1, v1.y);
-                a0 = fadd2(a0, v2.x); a1 = fadd2(a1, v2.y);
-                a0 = fadd2(a0, v3.x); a1 = fadd2(a1, v3.y);
-                a0 = fadd2(a0, v4.x); a1 = fadd2(a1, v4.y);
-                a0 = fadd2(a0, v5.x); a1 = fadd2(a1, v5.y);
-                a0 = fadd2(a0, v6.x); a1 = fadd2(a1, v6.y);
-                a0 = fadd2(a0, v7.x); a1 = fadd2(a1, v7.y);
+                acc.add(v0); acc.add(v1); acc.add(v2); acc.add(v3);
+                acc.add(v4); acc.add(v5); acc.add(v6); acc.add(v7);
             }
             // the last one to seven entries (the padding cells behind them are not read as rows).  All lanes of the warp
             // come here together: the loop runs as far as the longest remainder of the warp's four lists, so that no
@@ -402,7 +407,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
                     }
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
-                        if (h + u < rem) { a0 = fadd2(a0, v[u].x); a1 = fadd2(a1, v[u].y); }
+                        if (h + u < rem) acc.add(v[u]);
                 }
             }
         };
@@ -413,19 +418,19 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
             const int r = (int)(ri >> 32), off = (int)((ri >> 16) & 0xffffu), cnt = (int)(ri & 0xffffu);
             if (r >= rows) continue;
             const int qlen = (((cnt + 3) >> 2) + 7) & ~7;
-            unsigned long long p0 = 0ull, p1 = 0ull;
-            sum_range(s_lists + 2 * off, min(cnt, g * qlen), min(cnt, (g + 1) * qlen), p0, p1);
-            p0 = fadd2(p0, __shfl_xor_sync(0xffffffffu, p0, 8));
-            p1 = fadd2(p1, __shfl_xor_sync(0xffffffffu, p1, 8));
-            p0 = fadd2(p0, __shfl_xor_sync(0xffffffffu, p0, 16));
-            p1 = fadd2(p1, __shfl_xor_sync(0xffffffffu, p1, 16));
+            Acc part;
+            part.zero();
+            sum_range(s_lists + 2 * off, min(cnt, g * qlen), min(cnt, (g + 1) * qlen), part);
+            part.add(part.shfl_xor(8));
+            part.add(part.shfl_xor(16));
             if (g == 0) {
                 float* gp = grad + (size_t)(row0 + r) * F + col;
                 if (!first_chunk) {
-                    const ulonglong2 pv = __ldcg(reinterpret_cast<const ulonglong2*>(gp));
-                    p0 = fadd2(pv.x, p0); p1 = fadd2(pv.y, p1);
+                    Acc pv;
+                    pv.load_cg(gp);
+                    part.add_from(pv);
                 }
-                __stcg(reinterpret_cast<ulonglong2*>(gp), make_ulonglong2(p0, p1));
+                part.store_cg(gp);
             }
         }
         // all other lists: one group each, the terms added one by one onto the running sum.  The next record and its
@@ -435,32 +440,31 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const float* __re
             if (lane == 0) base = atomicAdd(&s_ctl[1], 4);
             return __shfl_sync(0xffffffffu, base, 0);
         };
-        auto fetch = [&](int base, unsigned long long& ri, ulonglong2& prev) {
+        auto fetch = [&](int base, unsigned long long& ri, Acc& prev) {
             ri = ~0ull;  // no record
-            prev = make_ulonglong2(0ull, 0ull);
+            prev.zero();
             if (base + g < n_rec) {
                 const unsigned long long x = s_info[base + g];
                 if ((int)(x >> 32) < rows) {
                     ri = x;
-                    if (!first_chunk) prev = __ldcg(reinterpret_cast<const ulonglong2*>(grad + (size_t)(row0 + (int)(x >> 32)) * F + col));
+                    if (!first_chunk) prev.load_cg(grad + (size_t)(row0 + (int)(x >> 32)) * F + col);
                 }
             }
         };
         int base = grab();
         unsigned long long ri;
-        ulonglong2 prev;
+        Acc prev;
         fetch(base, ri, prev);
         while (base < n_rec) {
             const int base_n = grab();
             unsigned long long ri_n;
-            ulonglong2 prev_n;
+            Acc prev_n;
             fetch(base_n, ri_n, prev_n);
             {
                 const bool have = ri != ~0ull;
                 const int r = (int)(ri >> 32), off = have ? (int)((ri >> 16) & 0xffffu) : 0, cnt = have ? (int)(ri & 0xffffu) : 0;
-                unsigned long long a0 = prev.x, a1 = prev.y;
-                sum_range(s_lists + 2 * off, 0, cnt, a0, a1);
-                if (have) __stcg(reinterpret_cast<ulonglong2*>(grad + (size_t)(row0 + r) * F + col), make_ulonglong2(a0, a1));
+                sum_range(s_lists + 2 * off, 0, cnt, prev);
+                if (have) prev.store_cg(grad + (size_t)(row0 + r) * F + col);
             }
             base = base_n; ri = ri_n; prev = prev_n;
         }
@@ -507,8 +511,8 @@ int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int
     return 2;
 }
 
-int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* dft_nstm, int* fwd_work, int* bwd_work, int B,
-                             int A, int N, int F, int rps, int n_persp, int slice_begin, int slice_count, float* grad) {
+int launch_ft_backward_slice(cudaStream_t s, const void* dft_stm, const void* dft_nstm, int* fwd_work, int* bwd_work, int B,
+                             int A, int N, int F, int rps, int n_persp, int slice_begin, int slice_count, float* grad, int dft_half) {
     if (B <= 0) return 0;
     const int n_items = n_persp * B;
     const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
@@ -517,10 +521,17 @@ int launch_ft_backward_slice(cudaStream_t s, const float* dft_stm, const float* 
     const BwdLayout L = bwd_layout(n_items, A, rps);
     const BwdPointers P = bwd_pointers(bwd_work, L);
     const size_t smem = bwd_smem_bytes(L.CH, rps, A_pad);
-    cudaFuncSetAttribute(k_ft_backward_slice, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (slice_begin < 0 || slice_count <= 0 || slice_begin + slice_count > n_slices) return 0;
-    k_ft_backward_slice<<<dim3(slice_count, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len, P.rowinfo,
-                                                                      P.lists, sb.outside_flag, B, F, N, rps, L.rps_pad, L.CH,
-                                                                      L.region, slice_begin, grad);
+    if (dft_half) {
+        cudaFuncSetAttribute(k_ft_backward_slice<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k_ft_backward_slice<true><<<dim3(slice_count, F / 64), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len,
+                                                                                P.rowinfo, P.lists, sb.outside_flag, B, F, N, rps,
+                                                                                L.rps_pad, L.CH, L.region, slice_begin, grad);
+    } else {
+        cudaFuncSetAttribute(k_ft_backward_slice<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k_ft_backward_slice<false><<<dim3(slice_count, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len,
+                                                                                 P.rowinfo, P.lists, sb.outside_flag, B, F, N, rps,
+                                                                                 L.rps_pad, L.CH, L.region, slice_begin, grad);
+    }
     return 1;
 }

@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "../../include/tatara_b200.h"
 
+#include <cuda_fp16.h>
 #include <dlfcn.h>
 #include <math.h>
 #include <stdarg.h>
@@ -23,6 +24,7 @@
 #define RANGER_ALPHA 0.5f
 #define RANGER_K 6
 #define N_SMA_THRESHOLD 5.0f
+#define FT_DFT_FP16_BASE_SCALE 16384.0f  // arch.rs:72-93: the fp16 dft rows carry gradient * 2^14 * batch
 #define DGRAD_CTAS (148 * 2)
 #define AR_PARTS_MAX 6
 // Number of launches the FT weight gradient is cut into in data-parallel runs (each part's all-reduce and row updates
@@ -127,6 +129,14 @@ struct tb_trainer {
     float* grad_arena = nullptr;
     int64_t arena_len = 0, arena_reduce_len = 0;
     float* comb = nullptr;
+    // reduced precision (bins/nnue_train/src/cli.rs:623-638): what each flag switches is in validate_config
+    bool p_tf32 = false, p_ft16 = false, p_out16 = false, p_state16 = false;
+    void* table_h = nullptr;          // fp16 forward table: folded table [N, F] (factorizer) or mirror of ft_w [N, F]
+    void *pre_h[2] = {nullptr, nullptr}, *dft_h[2] = {nullptr, nullptr};  // fp16 pre-activations / loss-scaled dft rows
+    void *ft_m_h = nullptr, *ft_v_h = nullptr;                           // fp16 moments of ft_w (scaled)
+    unsigned long long* clamp_counter = nullptr;                         // device: dft elements clamped to +-65504 so far
+    uint64_t clamp_elems = 0;                                            // dft elements written as fp16 so far
+    float grad_unscale = 1.0f;        // 1 / (loss scale of the FT gradient rows of the last backward)
     int Nt = 0, l1e = 0, l2in = 0, K = 0, max_tiles = 0, max_units = 0;
     uint64_t step_count = 0;
     // inputs
@@ -336,7 +346,9 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     const tb_config& c = t->cfg;
     const int B = d.n_pos, F = c.ft_out, N = c.ft_in, A = c.max_active;
     const bool ls = c.arch == TB_ARCH_LAYERSTACK;
-    const float* table = c.ft_factorize ? t->comb : t->groups[0].w;
+    const void* table = t->p_ft16 ? t->table_h : (c.ft_factorize ? (const void*)t->comb : (const void*)t->groups[0].w);
+    void* pre0 = t->p_out16 ? t->pre_h[0] : (void*)t->pre[0];
+    void* pre1 = t->p_out16 ? t->pre_h[1] : (void*)t->pre[1];
     t->last_n = B;
     if (backward) { t->opt_begun = false; t->ft_rows_updated = false; }
     { PhaseScope p(t, PH_SORT);
@@ -350,11 +362,12 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
       const int rps = c.piece_inputs > 0 ? c.piece_inputs : N;
       t->slice_fwd = ft_forward_slice_supported(F, N, A, rps);
       if (t->slice_fwd)
-          p.done(launch_ft_forward_slice(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1],
-                                         t->combined, t->items, t->item_seg, t->fwd_work, B, F, N, A, rps, FT_POST_SCALE, 2));
+          p.done(launch_ft_forward_slice(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, pre0, pre1,
+                                         t->combined, t->items, t->item_seg, t->fwd_work, B, F, N, A, rps, FT_POST_SCALE, 2,
+                                         t->p_ft16, t->p_out16));
       else
-          p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, t->pre[0], t->pre[1], t->combined,
-                                   t->items, B, F, N, A, FT_POST_SCALE, 2)); }
+          p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, pre0, pre1, t->combined,
+                                   t->items, B, F, N, A, FT_POST_SCALE, 2, t->p_ft16, t->p_out16)); }
     const LossParams lp = make_loss(loss, lambda, d.norm);
     if (ls) {
         { PhaseScope p(t, PH_L1_FWD);
@@ -395,9 +408,17 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
           p.done(launch_l1_wgrad(t->stream, t->combined, F, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, c.l1_out,
                                  c.num_buckets, t->l1w_partials, t->groups[2].grad, t->groups[4].grad)); }
         { PhaseScope p(t, PH_L1_DGRAD);
+          // fp16 dft rows carry gradient * 2^14 * batch (trainer_layerstack.rs:3617-3621); the FT weight gradient is summed
+          // in that scale and the optimizer takes it out again
+          const float dft_scale = t->p_out16 ? FT_DFT_FP16_BASE_SCALE * (float)B : 1.0f;
+          t->grad_unscale = 1.0f / dft_scale;
+          if (t->p_out16) t->clamp_elems += 2ull * (uint64_t)B * (uint64_t)F;
           p.done(launch_l1_dgrad_ftgrad(t->stream, 1, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
-                                        t->groups[4].w, t->pre[0], t->pre[1], t->groups[1].w, FT_POST_SCALE, B, F, c.l1_out,
-                                        c.num_buckets, t->dft[0], t->dft[1], t->bias_partials, t->groups[1].grad, t->dgrad_rows)); }
+                                        t->groups[4].w, t->p_out16 ? t->pre_h[0] : (void*)t->pre[0],
+                                        t->p_out16 ? t->pre_h[1] : (void*)t->pre[1], t->groups[1].w, FT_POST_SCALE, B, F, c.l1_out,
+                                        c.num_buckets, t->p_out16 ? t->dft_h[0] : (void*)t->dft[0],
+                                        t->p_out16 ? t->dft_h[1] : (void*)t->dft[1], t->bias_partials, t->groups[1].grad,
+                                        t->dgrad_rows, t->p_out16, dft_scale, t->clamp_counter)); }
     } else {
         { PhaseScope p(t, PH_SMALL_WGRAD);
           p.done(launch_small_wgrad_simple(t->stream, t->order, t->seg_start, B, c.l1_out, c.l2_out, t->tail_a, t->tail_b,
@@ -415,6 +436,8 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
     // slice-resident path when this step's forward was; the generic kernels then run only for a batch with a row outside
     // its item's slice (device-side gate)
     const int rps = c.piece_inputs > 0 ? c.piece_inputs : N;
+    const void* dft0 = t->p_out16 ? t->dft_h[0] : (const void*)t->dft[0];
+    const void* dft1 = t->p_out16 ? t->dft_h[1] : (const void*)t->dft[1];
     const bool slice_bwd = t->slice_fwd && t->bwd_slice != nullptr;
     const int* gate = slice_bwd ? ft_slice_outside_flag(t->fwd_work, 2 * B, N, rps) : nullptr;
     { PhaseScope p(t, PH_INV_INDEX);
@@ -424,8 +447,8 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                                 t->feat_lists);
       p.done(n); }
     { PhaseScope p(t, PH_FT_BWD);
-      int n = launch_ft_backward_split(t->stream, gate, t->dft[0], t->dft[1], t->feat_offsets, t->feat_lists, B, A, N, F, 2,
-                                       t->bwd_plan, t->bwd_partial, t->groups[0].grad);
+      int n = launch_ft_backward_split(t->stream, gate, dft0, dft1, t->feat_offsets, t->feat_lists, B, A, N, F, 2,
+                                       t->bwd_plan, t->bwd_partial, t->groups[0].grad, t->p_out16);
       if (slice_bwd) {
           // Data parallel: the slices are done in several launches (ar_parts_for) and the gradient rows of each part are all-reduced on a
           // second stream while the next part is computed (the small groups, ready since the dense backward, ride with the
@@ -439,8 +462,8 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
           for (int part = 0; part < parts; ++part) {
               // equal parts: a smaller last part cost more than it hid
               const int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
-              n += launch_ft_backward_slice(t->stream, t->dft[0], t->dft[1], t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
-                                            t->groups[0].grad);
+              n += launch_ft_backward_slice(t->stream, dft0, dft1, t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
+                                            t->groups[0].grad, t->p_out16);
               if (!pipeline) continue;
               CU(t, cudaEventRecord(t->ev_part[part], t->stream));
               CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_part[part], 0));
@@ -460,12 +483,16 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                   const int r0 = k0 * rps, r1 = k1 * rps < N ? k1 * rps : N;
                   CU(t, cudaEventRecord(t->ev_reduced[part], t->comm_stream));
                   CU(t, cudaStreamWaitEvent(t->opt_stream, t->ev_reduced[part], 0));
+                  const size_t msz = t->p_state16 ? 2 : 4, e0r = (size_t)r0 * F;
+                  void* gm = t->p_state16 ? t->ft_m_h : (void*)g.m;
+                  void* gv = t->p_state16 ? t->ft_v_h : (void*)g.v;
                   if (c.ft_factorize)
-                      n += launch_radam_factorized_rows(t->opt_stream, g.w, g.m, g.v, g.grad, g.slow, N, c.piece_inputs, F, k0, k1, sc);
+                      n += launch_radam_factorized_rows(t->opt_stream, g.w, gm, gv, g.grad, g.slow, N, c.piece_inputs, F, k0, k1, sc,
+                                                        t->p_state16);
                   else
-                      n += launch_radam(t->opt_stream, g.w + (size_t)r0 * F, g.m + (size_t)r0 * F, g.v + (size_t)r0 * F,
-                                        g.grad + (size_t)r0 * F, c.optimizer == TB_OPT_RANGER ? g.slow + (size_t)r0 * F : g.slow,
-                                        (int64_t)(r1 - r0) * F, sc);
+                      n += launch_radam(t->opt_stream, g.w + e0r, (char*)gm + e0r * msz, (char*)gv + e0r * msz, g.grad + e0r,
+                                        c.optimizer == TB_OPT_RANGER ? g.slow + e0r : g.slow, (int64_t)(r1 - r0) * F, sc, t->p_state16,
+                                        t->p_ft16 ? (char*)t->table_h + e0r * 2 : nullptr);
                   t->ft_rows_updated = true;
               }
           }
@@ -527,6 +554,7 @@ static OptScalars ft_scalars(tb_trainer* t, float lr) {
     sc.decay = t->cfg.wd_ft;
     sc.min_w = -g.clamp;
     sc.max_w = g.clamp;
+    sc.grad_scale = t->p_out16 ? t->grad_unscale : 1.0f;
     return sc;
 }
 
@@ -544,18 +572,25 @@ int run_optimizer(tb_trainer* t, float lr) {
         sc.decay = wd[0];
         sc.min_w = -g.clamp;
         sc.max_w = g.clamp;
+        sc.grad_scale = t->p_out16 ? t->grad_unscale : 1.0f;
+        void* gm = t->p_state16 ? t->ft_m_h : (void*)g.m;
+        void* gv = t->p_state16 ? t->ft_v_h : (void*)g.v;
+        void* fwd_table = t->p_ft16 ? t->table_h : (void*)t->comb;  // what the forward reads: written in the same pass
         if (t->ft_rows_updated) {
             // data parallel: the real rows were updated part by part behind their all-reduces; what is left are the
             // virtual rows and the folded table
             t->ft_rows_updated = false;
             if (c.ft_factorize)
-                p.done(launch_radam_factorized_fold(t->stream, g.w, g.m, g.v, g.grad, g.slow, t->comb, c.ft_in, c.piece_inputs, c.ft_out, sc));
+                p.done(launch_radam_factorized_fold(t->stream, g.w, gm, gv, g.grad, g.slow, fwd_table, c.ft_in, c.piece_inputs, c.ft_out, sc,
+                                                    t->p_state16, t->p_ft16));
             else
                 p.done(0);
         } else if (c.ft_factorize)
-            p.done(launch_radam_factorized(t->stream, g.w, g.m, g.v, g.grad, g.slow, t->comb, c.ft_in, c.piece_inputs, c.ft_out, sc));
+            p.done(launch_radam_factorized(t->stream, g.w, gm, gv, g.grad, g.slow, fwd_table, c.ft_in, c.piece_inputs, c.ft_out, sc,
+                                           t->p_state16, t->p_ft16));
         else
-            p.done(launch_radam(t->stream, g.w, g.m, g.v, g.grad, g.slow, g.len, sc));
+            p.done(launch_radam(t->stream, g.w, gm, gv, g.grad, g.slow, g.len, sc, t->p_state16, t->p_ft16 ? t->table_h : nullptr));
+        sc.grad_scale = 1.0f;  // the small groups' gradients are never scaled
     }
     {
         PhaseScope p(t, PH_OPT_SMALL);
@@ -675,6 +710,8 @@ void free_all(tb_trainer* t) {
     for (auto& g : t->groups) { cudaFree(g.w); cudaFree(g.m); cudaFree(g.v); cudaFree(g.slow); }
     cudaFree(t->grad_arena);
     cudaFree(t->comb);
+    cudaFree(t->table_h); cudaFree(t->ft_m_h); cudaFree(t->ft_v_h); cudaFree(t->clamp_counter);
+    for (int i = 0; i < 2; ++i) { cudaFree(t->pre_h[i]); cudaFree(t->dft_h[i]); }
     auto free_batch = [](DevBatch& d) { cudaFree(d.stm); cudaFree(d.nstm); cudaFree(d.nnz); cudaFree(d.bucket); cudaFree(d.score); cudaFree(d.wdl); };
     for (auto& d : t->ring) free_batch(d);
     for (auto& d : t->slots) free_batch(d);
@@ -725,6 +762,10 @@ int create_impl(tb_trainer* t) {
     CU(t, cudaStreamCreateWithFlags(&t->copy_stream, cudaStreamNonBlocking));
     const bool ls = c.arch == TB_ARCH_LAYERSTACK;
     const int64_t N = c.ft_in, F = c.ft_out, l1 = c.l1_out, l2 = c.l2_out, nb = c.num_buckets;
+    t->p_tf32 = (c.precision & TB_PREC_TF32) != 0;
+    t->p_ft16 = (c.precision & TB_PREC_FT_FP16) != 0;
+    t->p_out16 = (c.precision & TB_PREC_FT_FP16_OUT) != 0;
+    t->p_state16 = (c.precision & TB_PREC_FP16_OPT_STATE) != 0;
     t->Nt = c.ft_in + (c.ft_factorize ? c.piece_inputs : 0);
     t->l1e = c.l1_out - 1;
     t->l2in = 2 * t->l1e;
@@ -764,10 +805,18 @@ int create_impl(tb_trainer* t) {
     for (size_t i = 0; i < t->groups.size(); ++i) {
         Group& g = t->groups[i];
         g.grad = t->grad_arena + goff[i];
-        CU(t, dalloc(&g.w, (size_t)g.len)); CU(t, dalloc(&g.m, (size_t)g.len)); CU(t, dalloc(&g.v, (size_t)g.len));
+        CU(t, dalloc(&g.w, (size_t)g.len));
+        if (i == 0 && t->p_state16) {  // MomentBuf::F16 (trainer_common.rs:60-71): only the FT table's moments
+            CU(t, dalloc((__half**)&t->ft_m_h, (size_t)g.len)); CU(t, dalloc((__half**)&t->ft_v_h, (size_t)g.len));
+        } else {
+            CU(t, dalloc(&g.m, (size_t)g.len)); CU(t, dalloc(&g.v, (size_t)g.len));
+        }
         CU(t, dalloc(&g.slow, (size_t)(c.optimizer == TB_OPT_RANGER ? g.len : 1)));
     }
-    if (c.ft_factorize) CU(t, dalloc(&t->comb, (size_t)(N * F)));
+    // the table the forward reads: fp32 folded table, or one fp16 table (folded, or the mirror of the master rows)
+    if (t->p_ft16) CU(t, dalloc((__half**)&t->table_h, (size_t)(N * F)));
+    else if (c.ft_factorize) CU(t, dalloc(&t->comb, (size_t)(N * F)));
+    if (t->p_out16) CU(t, dalloc(&t->clamp_counter, 1));
 
     const size_t B = (size_t)c.batch_capacity, A = (size_t)c.max_active;
     for (auto& d : t->ring) { int rc = alloc_batch(t, &d); if (rc) return rc; }
@@ -785,8 +834,13 @@ int create_impl(tb_trainer* t) {
         CU(t, cudaEventCreateWithFlags(&t->ev_loss[i], cudaEventDisableTiming));
         CU(t, cudaHostAlloc((void**)&t->loss_pinned[i], sizeof(double), cudaHostAllocDefault));
         *t->loss_pinned[i] = 0.0;
-        CU(t, dalloc(&t->pre[i], B * F));
-        CU(t, dalloc(&t->dft[i], B * F));
+        if (t->p_out16) {
+            CU(t, dalloc((__half**)&t->pre_h[i], B * F));
+            CU(t, dalloc((__half**)&t->dft_h[i], B * F));
+        } else {
+            CU(t, dalloc(&t->pre[i], B * F));
+            CU(t, dalloc(&t->dft[i], B * F));
+        }
     }
     CU(t, dalloc(&t->combined, B * (size_t)t->K));
     CU(t, dalloc(&t->l1_out, B * l1)); CU(t, dalloc(&t->dl1, B * l1));
@@ -869,7 +923,17 @@ int validate_config(const tb_config* c) {
     // trainer_layerstack.rs:801-805
     if ((c->precision & TB_PREC_FT_FP16_OUT) && !(c->precision & TB_PREC_FT_FP16))
         return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "--ft-fp16-out requires --ft-fp16");
-    if (c->precision != 0) return fail(nullptr, TB_ERR_UNSUPPORTED, "reduced-precision modes (tf32 / fp16) are not implemented; precision must be 0");
+    if (c->precision & ~(TB_PREC_TF32 | TB_PREC_FT_FP16 | TB_PREC_FT_FP16_OUT | TB_PREC_FP16_OPT_STATE))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "unknown precision bits %#x", c->precision);
+    if (c->precision != 0) {
+        // What is built: the LayerStack trainer with l1_out of 8, 16 or 32 (the streaming L1 kernels) on a king-relative
+        // feature set (the slice-resident FT kernels are the only ones with fp16 rows at speed; the generic kernels serve
+        // batches that break the slice property).
+        if (c->arch != TB_ARCH_LAYERSTACK)
+            return fail(nullptr, TB_ERR_UNSUPPORTED, "reduced-precision modes are built for the LayerStack architecture only");
+        if (c->l1_out != 8 && c->l1_out != 16 && c->l1_out != 32)
+            return fail(nullptr, TB_ERR_UNSUPPORTED, "reduced-precision modes need l1_out of 8, 16 or 32 (got %d)", c->l1_out);
+    }
     if (c->world_size < 1 || c->rank < 0 || c->rank >= c->world_size) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad rank %d / world_size %d", c->rank, c->world_size);
     return TB_OK;
 }
@@ -921,13 +985,36 @@ int tb_upload_group(tb_trainer* t, const char* name, const float* w, const float
     CU(t, cudaSetDevice(t->cfg.device));
     CU(t, cudaStreamSynchronize(t->stream));
     const size_t bytes = (size_t)len * 4;
+    const bool ft = g == &t->groups[0];
     if (w) CU(t, cudaMemcpy(g->w, w, bytes, cudaMemcpyHostToDevice));
-    if (m) CU(t, cudaMemcpy(g->m, m, bytes, cudaMemcpyHostToDevice));
-    if (v) CU(t, cudaMemcpy(g->v, v, bytes, cudaMemcpyHostToDevice));
+    if (ft && t->p_state16) {
+        // MomentBuf::from_host_f32 (trainer_common.rs:107-126): true f32 moments are scaled, clamped to the fp16 range
+        // and rounded
+        std::vector<__half> h((size_t)len);
+        const float* src[2] = {m, v};
+        void* dst[2] = {t->ft_m_h, t->ft_v_h};
+        const float scale[2] = {TB_FT_OPT_M_SCALE, TB_FT_OPT_V_SCALE};
+        for (int k = 0; k < 2; ++k) {
+            if (!src[k]) continue;
+            for (int64_t i = 0; i < len; ++i) {
+                float x = src[k][i] * scale[k];
+                x = x > 65504.0f ? 65504.0f : (x < -65504.0f ? -65504.0f : x);
+                h[(size_t)i] = __float2half_rn(x);
+            }
+            CU(t, cudaMemcpy(dst[k], h.data(), (size_t)len * 2, cudaMemcpyHostToDevice));
+        }
+    } else {
+        if (m) CU(t, cudaMemcpy(g->m, m, bytes, cudaMemcpyHostToDevice));
+        if (v) CU(t, cudaMemcpy(g->v, v, bytes, cudaMemcpyHostToDevice));
+    }
     if (slow && t->cfg.optimizer == TB_OPT_RANGER) CU(t, cudaMemcpy(g->slow, slow, bytes, cudaMemcpyHostToDevice));
-    if (w && g == &t->groups[0] && t->cfg.ft_factorize) {
-        // sync_ft_forward_weights: the forward table follows the master weights
-        t->launches += launch_ft_fold(t->stream, g->w, t->comb, t->cfg.ft_in, t->cfg.piece_inputs, t->cfg.ft_out);
+    if (w && ft && (t->cfg.ft_factorize || t->p_ft16)) {
+        // sync_ft_forward_weights: the table the forward reads follows the master weights (fold, and / or fp16 cast)
+        if (t->cfg.ft_factorize)
+            t->launches += launch_ft_fold(t->stream, g->w, t->p_ft16 ? t->table_h : (void*)t->comb, t->cfg.ft_in, t->cfg.piece_inputs,
+                                          t->cfg.ft_out, t->p_ft16);
+        else
+            t->launches += launch_cast_half(t->stream, g->w, t->table_h, g->len);
         CU(t, cudaStreamSynchronize(t->stream));
     }
     return TB_OK;
@@ -942,8 +1029,21 @@ int tb_download_group(tb_trainer* t, const char* name, float* w, float* m, float
     CU(t, cudaStreamSynchronize(t->stream));
     const size_t bytes = (size_t)len * 4;
     if (w) CU(t, cudaMemcpy(w, g->w, bytes, cudaMemcpyDeviceToHost));
-    if (m) CU(t, cudaMemcpy(m, g->m, bytes, cudaMemcpyDeviceToHost));
-    if (v) CU(t, cudaMemcpy(v, g->v, bytes, cudaMemcpyDeviceToHost));
+    if (g == &t->groups[0] && t->p_state16) {
+        // MomentBuf::to_host_f32 (trainer_common.rs:89-105): stored fp16 values divided by their scale
+        std::vector<__half> h((size_t)len);
+        float* dst[2] = {m, v};
+        const void* src[2] = {t->ft_m_h, t->ft_v_h};
+        const float inv[2] = {1.0f / TB_FT_OPT_M_SCALE, 1.0f / TB_FT_OPT_V_SCALE};
+        for (int k = 0; k < 2; ++k) {
+            if (!dst[k]) continue;
+            CU(t, cudaMemcpy(h.data(), src[k], (size_t)len * 2, cudaMemcpyDeviceToHost));
+            for (int64_t i = 0; i < len; ++i) dst[k][i] = __half2float(h[(size_t)i]) * inv[k];
+        }
+    } else {
+        if (m) CU(t, cudaMemcpy(m, g->m, bytes, cudaMemcpyDeviceToHost));
+        if (v) CU(t, cudaMemcpy(v, g->v, bytes, cudaMemcpyDeviceToHost));
+    }
     if (slow) {
         if (t->cfg.optimizer == TB_OPT_RANGER) CU(t, cudaMemcpy(slow, g->slow, bytes, cudaMemcpyDeviceToHost));
         else memset(slow, 0, bytes);
@@ -1040,8 +1140,16 @@ int tb_validate_step(tb_trainer* t, const tb_batch* batch, float wdl_lambda, con
 
 int tb_read_fp16_clamp_count(tb_trainer* t, uint64_t* clamps, uint64_t* elems) {
     if (!t) return TB_ERR_INVALID_ARGUMENT;
-    if (clamps) *clamps = 0;  // no fp16 path: nothing is ever clamped
-    if (elems) *elems = 0;
+    // (clamped, written) dft elements so far, like GpuTrainer::read_fp16_clamp_count (crates/nnue-train/src/trainer.rs:1100-1119);
+    // zeros unless the FT activations are fp16
+    unsigned long long n = 0;
+    if (t->p_out16) {
+        CU(t, cudaSetDevice(t->cfg.device));
+        CU(t, cudaStreamSynchronize(t->stream));
+        CU(t, cudaMemcpy(&n, t->clamp_counter, sizeof n, cudaMemcpyDeviceToHost));
+    }
+    if (clamps) *clamps = n;
+    if (elems) *elems = t->clamp_elems;
     return TB_OK;
 }
 
@@ -1112,6 +1220,9 @@ int tb_download_grad(tb_trainer* t, const char* name, float* grad, int64_t len) 
     CU(t, cudaSetDevice(t->cfg.device));
     CU(t, cudaStreamSynchronize(t->stream));
     CU(t, cudaMemcpy(grad, g->grad, (size_t)len * 4, cudaMemcpyDeviceToHost));
+    // summed from loss-scaled fp16 rows: the rows still carry that scale (the optimizer takes it out on load)
+    if (g == &t->groups[0] && t->p_out16)
+        for (int64_t i = 0; i < len; ++i) grad[i] *= t->grad_unscale;
     return TB_OK;
 }
 
@@ -1119,17 +1230,26 @@ int tb_read_buffer(tb_trainer* t, const char* name, float* out, int64_t len) {
     if (!t || !name || !out) return TB_ERR_INVALID_ARGUMENT;
     const tb_config& c = t->cfg;
     const int64_t B = t->last_n, F = c.ft_out;
-    struct { const char* n; const float* p; int64_t l; } tab[] = {
-        {"ft_stm", t->pre[0], B * F}, {"ft_nstm", t->pre[1], B * F}, {"combined", t->combined, B * t->K},
-        {"l1_total", t->l1_out, B * c.l1_out}, {"net_output", t->net_output, B}, {"dy", t->dy, B},
-        {"dl1_total", t->dl1, B * c.l1_out}, {"dft_stm", t->dft[0], B * F}, {"dft_nstm", t->dft[1], B * F},
-        {"comb", t->comb, t->comb ? (int64_t)c.ft_in * F : 0}};
+    // fp16 buffers are returned as fp32 values; the fp16 dft rows with their loss scale taken out
+    const bool o16 = t->p_out16, t16 = t->p_ft16;
+    struct { const char* n; const void* p; int64_t l; bool half; float mul; } tab[] = {
+        {"ft_stm", o16 ? t->pre_h[0] : (void*)t->pre[0], B * F, o16, 1.f}, {"ft_nstm", o16 ? t->pre_h[1] : (void*)t->pre[1], B * F, o16, 1.f},
+        {"combined", t->combined, B * t->K, false, 1.f}, {"l1_total", t->l1_out, B * c.l1_out, false, 1.f},
+        {"net_output", t->net_output, B, false, 1.f}, {"dy", t->dy, B, false, 1.f}, {"dl1_total", t->dl1, B * c.l1_out, false, 1.f},
+        {"dft_stm", o16 ? t->dft_h[0] : (void*)t->dft[0], B * F, o16, o16 ? t->grad_unscale : 1.f},
+        {"dft_nstm", o16 ? t->dft_h[1] : (void*)t->dft[1], B * F, o16, o16 ? t->grad_unscale : 1.f},
+        {"comb", t16 ? t->table_h : (void*)t->comb, (t16 || t->comb) ? (int64_t)c.ft_in * F : 0, t16, 1.f}};
     for (auto& e : tab)
         if (strcmp(e.n, name) == 0) {
             if (len != e.l) return fail(t, TB_ERR_INVALID_ARGUMENT, "buffer '%s' has %lld elements, got %lld", name, (long long)e.l, (long long)len);
             CU(t, cudaSetDevice(c.device));
             CU(t, cudaStreamSynchronize(t->stream));
-            if (len > 0) CU(t, cudaMemcpy(out, e.p, (size_t)len * 4, cudaMemcpyDeviceToHost));
+            if (len > 0 && !e.half) CU(t, cudaMemcpy(out, e.p, (size_t)len * 4, cudaMemcpyDeviceToHost));
+            if (len > 0 && e.half) {
+                std::vector<__half> h((size_t)len);
+                CU(t, cudaMemcpy(h.data(), e.p, (size_t)len * 2, cudaMemcpyDeviceToHost));
+                for (int64_t i = 0; i < len; ++i) out[i] = __half2float(h[(size_t)i]) * e.mul;
+            }
             return TB_OK;
         }
     return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown buffer '%s'", name);

@@ -152,6 +152,14 @@ def lib():
     L.ora_trainer_validate.argtypes = [C.c_void_p, i32p, i32p, i32p, C.c_void_p, f32p, f32p, C.c_int, f,
                                        C.POINTER(Loss), f32p]
     L.ora_trainer_validate.restype = C.c_double
+    L.ora_trainer_set_precision.argtypes = [C.c_void_p, C.c_int]
+    L.ora_trainer_clamp_count.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    L.ora_round_half.argtypes = [f]
+    L.ora_round_half.restype = f
+    L.ora_tf32.argtypes = [f]
+    L.ora_tf32.restype = f
+    L.ora_radam_step_f16state.argtypes = [f32p, f32p, f32p, f32p, f, f, C.c_int32, f, f, f, f, f, f, f, f, sz]
+    L.ora_radam_step_f16state.restype = None
     L.ora_trainer_accumulate_grads.argtypes = [C.c_void_p, C.c_void_p]
     L.ora_trainer_apply_optimizer.argtypes = [C.c_void_p, f]
     _lib = L
@@ -195,13 +203,20 @@ class OracleTrainer:
     """Whole-step CPU oracle (LayerStack or Simple)."""
 
     def __init__(self, *, arch, ft_in, piece_inputs, factorize, max_active, ft_out, l1, l2, num_buckets=9,
-                 activation=0, optimizer="ranger", wd=(0.01, 0.01, 0.01), lr_mult=(1.0, 1.0, 1.0), capacity=1024):
+                 activation=0, optimizer="ranger", wd=(0.01, 0.01, 0.01), lr_mult=(1.0, 1.0, 1.0), capacity=1024, precision=0):
         self.L = lib()
         self.cfg = Config(0 if arch == "layerstack" else 1, ft_in, piece_inputs, int(factorize), max_active, ft_out,
                           l1, l2, num_buckets, activation, OPTIMIZERS[optimizer], wd[0], wd[1], wd[2],
                           lr_mult[0], lr_mult[1], lr_mult[2])
         self.h = self.L.ora_trainer_create(C.byref(self.cfg), capacity)
         self.names = [self.L.ora_trainer_group_name(self.h, i).decode() for i in range(self.L.ora_trainer_num_groups(self.h))]
+        if precision:
+            self.L.ora_trainer_set_precision(self.h, precision)   # 1 tf32, 2 ft_fp16, 4 ft_fp16_out, 8 fp16_opt_state
+
+    def clamp_count(self):
+        a, b = C.c_uint64(), C.c_uint64()
+        self.L.ora_trainer_clamp_count(self.h, C.byref(a), C.byref(b))
+        return a.value, b.value
 
     def close(self):
         if self.h:
