@@ -125,10 +125,17 @@ int launch_psv_extract(cudaStream_t s, int feature_set, const void* d_psv, long 
 bool psv_feature_set_dims(int feature_set, int* ft_in, int* max_active);
 
 // dense_kernels.cu
+// tf32: run the contraction on the tensor cores with TF32 operands (l1_tc.cu) where the shape allows; error_flag: device
+// int raised when one of that kernel's bounded waits ran out
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb /*[nb][l1][K] or NULL*/,
                       const float* bb, const float* ws /*[K][l1]*/, const float* bs, float* y /*[B][l1]*/,
-                      int l1, int nb, float* weff /*scratch [(nb + 1) * l1 * (K + 1)] or NULL*/);
+                      int l1, int nb, float* weff /*scratch [(nb + 1) * l1 * (K + 1)] or NULL*/, int tf32 = 0,
+                      int* error_flag = nullptr);
+// l1_tc.cu
+bool l1_forward_tc_supported(int K, int l1);
+int launch_l1_forward_tc(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles, const int* n_tiles,
+                         int max_tiles, const float* weff, const float* beff, float* y, int l1, int nb, int* error_flag);
 int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
                            const float* wdl, const float* l2_w, const float* l2_b, const float* l3_w,
                            const float* l3_b, LossParams lp, int B, int l1, int l2, int nb, float* net_output,

@@ -362,10 +362,12 @@ __global__ void __launch_bounds__(4 * L1) k_l1_forward_stream(const float* __res
 
 int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles,
                       const int* n_tiles, int max_tiles, const float* wb, const float* bb, const float* ws,
-                      const float* bs, float* y, int l1, int nb, float* weff) {
+                      const float* bs, float* y, int l1, int nb, float* weff, int tf32, int* error_flag) {
     if ((l1 == 8 || l1 == 16 || l1 == 32) && K % LF_KC == 0 && weff != nullptr) {
         float* beff = weff + (size_t)(nb + 1) * l1 * K;
         k_l1_weff<<<dim3(ceil_div(l1 * K, 256 * 4), nb + 1), 256, 0, s>>>(wb, bb, ws, bs, K, l1, wb ? nb : 0, weff, beff);
+        if (tf32 && error_flag && l1_forward_tc_supported(K, l1))
+            return 1 + launch_l1_forward_tc(s, x, K, order, tiles, n_tiles, max_tiles, weff, beff, y, l1, wb ? nb : 0, error_flag);
         const int max_units = sort_max_units(max_tiles);
         const size_t smem = (size_t)LF_STAGES * (LF_POS + l1) * LF_LD * sizeof(float);
         const TileDesc* units = tiles + max_tiles;
@@ -1419,8 +1421,13 @@ __global__ void __launch_bounds__(256) k_l1_dgrad_ftgrad_stream(const float* __r
     // stores a thread's four gradient values of one row: fp32 as they are; fp16 scaled, clamped, rounded
     auto store_dft = [&](unsigned char* dst, const float4& gv) {
         if constexpr (HALF) {
-            const float a = clamp_half_count(gv.x * grad_scale, clamps), b = clamp_half_count(gv.y * grad_scale, clamps);
-            const float c = clamp_half_count(gv.z * grad_scale, clamps), d = clamp_half_count(gv.w * grad_scale, clamps);
+            float a = gv.x * grad_scale, b = gv.y * grad_scale, c = gv.z * grad_scale, d = gv.w * grad_scale;
+            // one test for the four values; beyond the fp16 range (rare) each is clamped and counted.  A NaN passes the
+            // test as it passes the reference's comparisons, and is stored as NaN.
+            if (fmaxf(fmaxf(fabsf(a), fabsf(b)), fmaxf(fabsf(c), fabsf(d))) > 65504.0f) {
+                a = clamp_half_count(a, clamps); b = clamp_half_count(b, clamps);
+                c = clamp_half_count(c, clamps); d = clamp_half_count(d, clamps);
+            }
             *reinterpret_cast<uint2*>(dst) = make_uint2(dk_pack_h2(a, b), dk_pack_h2(c, d));
         } else {
             *reinterpret_cast<float4*>(dst) = gv;

@@ -137,6 +137,8 @@ struct tb_trainer {
     unsigned long long* clamp_counter = nullptr;                         // device: dft elements clamped to +-65504 so far
     uint64_t clamp_elems = 0;                                            // dft elements written as fp16 so far
     float grad_unscale = 1.0f;        // 1 / (loss scale of the FT gradient rows of the last backward)
+    int* tc_error = nullptr;          // device: raised by the tensor-core L1 kernel when a bounded wait ran out
+    int* tc_error_pinned = nullptr;   // its host copy, refreshed with every loss read-back
     int Nt = 0, l1e = 0, l2in = 0, K = 0, max_tiles = 0, max_units = 0;
     uint64_t step_count = 0;
     // inputs
@@ -372,7 +374,8 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
     if (ls) {
         { PhaseScope p(t, PH_L1_FWD);
           p.done(launch_l1_forward(t->stream, t->combined, F, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
-                                   t->groups[3].w, t->groups[4].w, t->groups[5].w, t->l1_out, c.l1_out, c.num_buckets, t->l1_weff)); }
+                                   t->groups[3].w, t->groups[4].w, t->groups[5].w, t->l1_out, c.l1_out, c.num_buckets, t->l1_weff,
+                                   t->p_tf32, t->tc_error)); }
         { PhaseScope p(t, PH_TAIL);
           p.done(launch_tail_layerstack(t->stream, t->l1_out, d.bucket, d.score, d.wdl, t->groups[6].w, t->groups[7].w,
                                         t->groups[8].w, t->groups[9].w, lp, B, c.l1_out, c.l2_out, c.num_buckets,
@@ -616,6 +619,10 @@ int run_optimizer(tb_trainer* t, float lr) {
 // queues the read-back of this step's loss and returns the previous one (AsyncLossRing::read_and_queue_next)
 int loss_ring_next(tb_trainer* t, double* out) {
     const int cur = (int)(t->loss_step % 2);
+    if (t->tc_error) {
+        if (*t->tc_error_pinned) return fail(t, TB_ERR_CUDA, "the tensor-core L1 kernel gave up waiting for its MMAs (an earlier step's results are invalid)");
+        CU(t, cudaMemcpyAsync(t->tc_error_pinned, t->tc_error, sizeof(int), cudaMemcpyDeviceToHost, t->stream));
+    }
     CU(t, cudaMemcpyAsync(t->loss_pinned[cur], t->loss_acc, sizeof(double), cudaMemcpyDeviceToHost, t->stream));
     CU(t, cudaEventRecord(t->ev_loss[cur], t->stream));
     double returned = 0.0;
@@ -711,6 +718,7 @@ void free_all(tb_trainer* t) {
     cudaFree(t->grad_arena);
     cudaFree(t->comb);
     cudaFree(t->table_h); cudaFree(t->ft_m_h); cudaFree(t->ft_v_h); cudaFree(t->clamp_counter);
+    cudaFree(t->tc_error); cudaFreeHost(t->tc_error_pinned);
     for (int i = 0; i < 2; ++i) { cudaFree(t->pre_h[i]); cudaFree(t->dft_h[i]); }
     auto free_batch = [](DevBatch& d) { cudaFree(d.stm); cudaFree(d.nstm); cudaFree(d.nnz); cudaFree(d.bucket); cudaFree(d.score); cudaFree(d.wdl); };
     for (auto& d : t->ring) free_batch(d);
@@ -817,6 +825,11 @@ int create_impl(tb_trainer* t) {
     if (t->p_ft16) CU(t, dalloc((__half**)&t->table_h, (size_t)(N * F)));
     else if (c.ft_factorize) CU(t, dalloc(&t->comb, (size_t)(N * F)));
     if (t->p_out16) CU(t, dalloc(&t->clamp_counter, 1));
+    if (t->p_tf32) {
+        CU(t, dalloc(&t->tc_error, 1));
+        CU(t, cudaHostAlloc((void**)&t->tc_error_pinned, sizeof(int), cudaHostAllocDefault));
+        *t->tc_error_pinned = 0;
+    }
 
     const size_t B = (size_t)c.batch_capacity, A = (size_t)c.max_active;
     for (auto& d : t->ring) { int rc = alloc_batch(t, &d); if (rc) return rc; }
@@ -1194,9 +1207,11 @@ int tb_forward_backward(tb_trainer* t, const tb_batch* batch, float wdl_lambda, 
         t->launches += launch_ft_reduce_virtual(t->stream, t->groups[0].grad, t->cfg.ft_in, t->cfg.piece_inputs, t->cfg.ft_out);
     double l = 0.0;
     CU(t, cudaMemcpyAsync(&l, t->loss_acc, sizeof(double), cudaMemcpyDeviceToHost, t->stream));
+    if (t->tc_error) CU(t, cudaMemcpyAsync(t->tc_error_pinned, t->tc_error, sizeof(int), cudaMemcpyDeviceToHost, t->stream));
     CU(t, cudaStreamSynchronize(t->stream));
     CU(t, cudaGetLastError());
     profile_collect(t);
+    if (t->tc_error && *t->tc_error_pinned) return fail(t, TB_ERR_CUDA, "the tensor-core L1 kernel gave up waiting for its MMAs");
     if (loss_now) *loss_now = l;
     return TB_OK;
 }

@@ -61,6 +61,18 @@ def _pair(fs, F, l1, l2, nb, B, mask, init, optimizer="ranger"):
     return tr, ot
 
 
+def _assert_close_fp16_stored(got, want, store_scale, tol, what):
+    """A value kept as fp16(value * store_scale): beside the relative tolerance (against the tensor's scale) one fp16
+    step of the stored value is allowed (2^-24 below the normal range), since inputs that differ in the last fp32 bits
+    can round to neighbouring fp16 values."""
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    stored = np.abs(want) * store_scale
+    ulp = np.maximum(2.0 ** -24, 2.0 ** (np.floor(np.log2(np.maximum(stored, 2.0 ** -14))) - 10)) / store_scale
+    err = np.abs(got - want) - tol * (np.abs(want).max() + np.abs(want)) - 1.01 * ulp
+    i = int(np.argmax(err))
+    assert err[i] <= 0, "%s: element %d got %r want %r" % (what, i, got[i], want[i])
+
+
 def _check_step(tr, ot, batch, B, F, l1, mask, fs):
     tf32 = bool(mask & TF32)
     tol_fwd = 2e-3 if tf32 else 1e-5
@@ -96,9 +108,12 @@ def _check_step(tr, ot, batch, B, F, l1, mask, fs):
     for name in ot.names:
         got = tr.download_group(name, ("w", "m", "v"))
         assert_close(got["w"], ot.group(name, "w"), tol_w, "w " + name)
-        tol_m = max(1e-3 if (name == "ft_w" and mask & STATE16) else 1e-4, tol_grad)
-        assert_close_scaled(got["m"], ot.group(name, "m"), tol_m, "m " + name)
-        assert_close_scaled(got["v"], ot.group(name, "v"), tol_m, "v " + name)
+        if name == "ft_w" and mask & STATE16:
+            _assert_close_fp16_stored(got["m"], ot.group(name, "m"), 2.0 ** 28, tol_grad, "m " + name)
+            _assert_close_fp16_stored(got["v"], ot.group(name, "v"), 2.0 ** 40, tol_grad, "v " + name)
+        else:
+            assert_close_scaled(got["m"], ot.group(name, "m"), tol_grad, "m " + name)
+            assert_close_scaled(got["v"], ot.group(name, "v"), tol_grad, "v " + name)
     if mask & STATE16:
         m = tr.download_group("ft_w", ("m",))["m"] * np.float32(2.0 ** 28)
         assert np.array_equal(m, m.astype(np.float16).astype(np.float32)), "moments are stored as fp16 of m * 2^28"
