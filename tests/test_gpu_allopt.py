@@ -5,10 +5,11 @@ kernels, and against those kernels themselves run on the GPU (oracle/_ref).
 Tolerances (|g - c| <= tol (1 + |c|), gradient tensors against their scale), looser than fp32 where a value passes
 through fp16 or TF32 storage:
   fp16 FT sums (stored pre-activations)   bit-exact: fp16 rows are summed in fp32 in slot order, then rounded once
-  forward values, loss                    1e-5 without --tf32, 2e-3 with it (TF32 operands carry 10 mantissa bits)
+  forward values, loss                    1e-5 without --tf32; 5e-3 with it: the reference's own bar for its TF32 products
+                                          (bins/nnue_train/src/tests/gpu_cpu_equivalence_tests.rs:718, 773, 829)
   fp16 dft rows                           1e-3 (one fp16 ulp is 2^-11 relative)
-  FT weight gradient                      2e-4 (a rounding flip of single fp16 terms), other gradients 1e-4 (2e-3 with --tf32)
-  weights after one step                  1e-5 (1e-4 with --tf32); fp16 moments 1e-3
+  FT weight gradient                      2e-4 (a rounding flip of single fp16 terms), other gradients 1e-4 (5e-3 with --tf32)
+  weights after one step                  1e-5 (1e-4 with --tf32); fp16 moments one fp16 step of the stored value
 The reference's own whole-trainer bar for these modes is GPU-vs-GPU (bins/nnue_train/src/tests/native_cuda_tests.rs:24-42).
 """
 import ctypes as C
@@ -75,8 +76,8 @@ def _assert_close_fp16_stored(got, want, store_scale, tol, what):
 
 def _check_step(tr, ot, batch, B, F, l1, mask, fs):
     tf32 = bool(mask & TF32)
-    tol_fwd = 2e-3 if tf32 else 1e-5
-    tol_grad = 2e-3 if tf32 else 1e-4
+    tol_fwd = 5e-3 if tf32 else 1e-5
+    tol_grad = 5e-3 if tf32 else 1e-4
     loss_t, loss_o = tb.LossKind.sigmoid(1.0 / 290.0), O.sigmoid_loss(1.0 / 290.0)
     l_gpu = tr.forward_backward(batch, 0.0, loss_t)
     l_cpu = ot.step(_batch_dict(batch), LR, 0.0, loss_o, do_optimizer=False)
