@@ -339,9 +339,13 @@ def dp_parity_check(tb, dist, device, world, rank, nccl_id):
     mine = shards[rank]
     tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=device, world_size=world, rank=rank, nccl_id=nccl_id)
     batch = tb.BatchData(mine["stm"], mine["nstm"], mine["nnz"], mine["score"], mine["wdl"], mine["bucket"])
+    if os.environ.get("TB_BENCH_TRACE"):
+        print("[dp check rank %d] trainer created" % rank, file=sys.stderr, flush=True)
     for _ in range(6):
         tr.train_step(batch, 1e-3, 0.0, tb.LossKind.sigmoid())
     loss = tr.flush_pending_loss()
+    if os.environ.get("TB_BENCH_TRACE"):
+        print("[dp check rank %d] six steps done" % rank, file=sys.stderr, flush=True)
     ok = True
     if rank == 0:
         full = {k: np.concatenate([s[k] for s in shards]) for k in mine}
@@ -398,6 +402,9 @@ def short_config(tb, wname, device, steps, peak):
             "roofline_step_frac": round(alg / (ms * 1e-3) / 1e9 / peak, 4)}
 
 
+T0 = time.time()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -412,6 +419,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="progress lines on stderr")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -419,6 +427,10 @@ def main():
     w = WORKLOADS[args.workload]
     K, Wm = max(1, args.steps), max(3, args.warmup)
     threads = os.cpu_count() or 1
+
+    def trace(msg):
+        if args.trace:
+            print("[bench rank %d %.1fs] %s" % (rank, time.time() - T0, msg), file=sys.stderr, flush=True)
 
     if args.impl == "reference":
         if rank != 0:
@@ -456,8 +468,10 @@ def main():
     device = local_rank
     B = args.batch
     dp_ok = dp_same_small = None
+    trace("rendezvous done")
     if world > 1:
         dp_ok, dp_same_small = dp_parity_check(tb, dist, device, world, rank, ids[1])
+        trace("dp self check done: %s %s" % (dp_ok, dp_same_small))
         if not (dp_ok and dp_same_small):
             if rank == 0:
                 print(json.dumps({"error": "data-parallel self check failed", "dp_parity": dp_ok, "replicas_identical": dp_same_small}), flush=True)
@@ -471,6 +485,7 @@ def main():
     batches = [tb.extract_batch(p, fs, with_bucket=w["arch"] == "layerstack", device=device, pinned=True) for p in psvs]
     for i, b in enumerate(batches):
         tr.stage_batch(i, b)
+    trace("trainer and batches ready")
 
     def barrier():
         tr.synchronize()
@@ -505,6 +520,7 @@ def main():
         tr.synchronize()
         rep_ms.append(max_over_ranks(m))
     t_wall1 = time.time()
+    trace("timed repeats done: %s" % rep_ms)
     launches = (tr.launch_count - launches0) // max(1, args.repeats)
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     barrier()
@@ -528,6 +544,7 @@ def main():
         return max_over_ranks(m)
 
     ms_e2e = e2e_run(lambda i: tr.train_step(batches[i % n_batches], LR, 0.0, loss))
+    trace("e2e (index feed) done")
     e2e_value = world * B * K / (ms_e2e * 1e-3)
     A = fs.max_active
     h2d = 2 * B * A * 4 + (4 if w["arch"] == "layerstack" else 3) * B * 4
@@ -538,6 +555,7 @@ def main():
         pa.array[:] = p
         pinned_psv.append(pa)
     ms_psv = e2e_run(lambda i: tr.train_step_psv(pinned_psv[i % n_batches].array, LR, 0.0, loss))
+    trace("e2e (record feed) done")
 
     # ---- per-kernel timing (CUDA events around every phase, on the launching stream) -----------------------------
     tr.profile_enable(True)
@@ -548,7 +566,9 @@ def main():
     prof = tr.profile_read()
     tr.profile_enable(False)
     barrier()
+    trace("per-phase profile done")
     same = replicas_identical(tr, dist, ("ft_w", "l1_w")) if dist is not None else None
+    trace("replica comparison done")
     if dist is not None and not same:
         if rank == 0:
             print(json.dumps({"error": "replicas diverged during the timed steps"}), flush=True)
@@ -601,8 +621,8 @@ def main():
         if world > 1:
             line["dp_parity"] = "ok" if dp_ok else "failed"
             line["replicas_identical"] = bool(same and dp_same_small)
-        tr.close()
         if world == 1:
+            tr.close()   # (with several ranks the communicator is torn down by all of them together, below)
             if not args.no_other_configs:
                 line["other_configs"] = [short_config(tb, n, device, 10, peak) for n in ("cfg1", "cfg2") if n != args.workload]
             if not args.no_microbench:
@@ -613,6 +633,8 @@ def main():
                                         "sample": "%d steps of 4096 synthetic positions on the CPU restatement of the reference step (%.0f ms/step)" % (done, cms)}
         print(json.dumps(line), flush=True)
     if dist is not None:
+        dist.barrier()
+        tr.close()
         dist.barrier()
         dist.destroy_process_group()
 
