@@ -39,7 +39,9 @@ extern "C" {
 #define TB_ERR_NO_DEVICE (-6)
 
 enum { TB_ARCH_LAYERSTACK = 0, TB_ARCH_SIMPLE = 1 };
-enum { TB_ACT_CRELU = 0, TB_ACT_SCRELU = 1 };
+/* SimpleActivation (bins/nnue_train/src/trainer_simple.rs): Pairwise is the FT-output pairwise product of the LayerStack
+ * net (the L1 input is then ft_out wide instead of 2 * ft_out); L1 and L2 are CReLU then */
+enum { TB_ACT_CRELU = 0, TB_ACT_SCRELU = 1, TB_ACT_PAIRWISE = 2 };
 /* crates/nnue-train/src/optimizer.rs:32-37 OptimizerKind */
 enum { TB_OPT_RANGER = 0, TB_OPT_RADAM = 1, TB_OPT_ADAMW = 2 };
 /* bins/nnue_train/src/cli.rs:623-638 precision flags; --all-optim sets all four */
@@ -67,7 +69,7 @@ typedef struct tb_config {
     int32_t l1_out;         /* LayerStack: includes the skip output; Simple: hidden 1 */
     int32_t l2_out;
     int32_t num_buckets;    /* LayerStack: 2..9; ignored for Simple */
-    int32_t activation;     /* Simple: TB_ACT_*; LayerStack is always pairwise CReLU */
+    int32_t activation;     /* Simple: TB_ACT_* (CReLU, SCReLU, Pairwise); LayerStack is always pairwise CReLU */
     int32_t optimizer;      /* TB_OPT_* */
     int32_t precision;      /* bit mask of TB_PREC_* */
     float wd_ft, wd_dense, wd_bias;                /* OptimGroupConfig, trainer_layerstack.rs:640-705 */
@@ -107,8 +109,8 @@ const char* tb_last_error(const tb_trainer* t);
 /* ---- parameter groups -------------------------------------------------------------
  * Names and order follow raw_ckpt_group_sources / uniform_optim_group_layout
  * (trainer_layerstack.rs:740-762): ft_w, ft_b, l1_w, l1_b, l1_shared_weight,
- * l1_shared_bias, l2_w, l2_b, l3_w, l3_b; Simple: ft_w, ft_b, l1_w, l1_b, l2_w, l2_b,
- * l3_w, l3_b.  Initial weights always come from the host (init.rs or a checkpoint). */
+ * l1_shared_bias, l2_w, l2_b, l3_w, l3_b; Simple: ft_w, ft_b, l1_w ([2 * ft_out, l1]; Pairwise [ft_out, l1]), l1_b, l2_w,
+ * l2_b, l3_w, l3_b.  Initial weights always come from the host (init.rs or a checkpoint). */
 int tb_num_groups(const tb_trainer* t);
 const char* tb_group_name(const tb_trainer* t, int group);
 int64_t tb_group_len(const tb_trainer* t, const char* name);

@@ -983,7 +983,7 @@ ora_trainer* ora_trainer_create(const ora_config* cfg, int cap) {
     } else {
         add_group(t, "ft_w", 0, CLAMP_NONE, Nt * F);
         add_group(t, "ft_b", 2, CLAMP_NONE, F);
-        add_group(t, "l1_w", 1, CLAMP_Q, 2 * F * l1);
+        add_group(t, "l1_w", 1, CLAMP_Q, (cfg->activation == 2 ? F : 2 * F) * l1); /* Pairwise: the L1 input is ft_out wide */
         add_group(t, "l1_b", 2, CLAMP_Q, l1);
         add_group(t, "l2_w", 1, CLAMP_Q, l1 * l2);
         add_group(t, "l2_b", 2, CLAMP_Q, l2);
@@ -1068,11 +1068,11 @@ const float* ora_trainer_buffer(const ora_trainer* t, const char* name, size_t* 
     size_t B = (size_t)t->last_n, F = (size_t)c->ft_out;
     struct { const char* n; const float* p; size_t l; } tab[] = {
         {"ft_stm", t->ft_stm, B * F}, {"ft_nstm", t->ft_nstm, B * F},
-        {"combined", t->combined, B * F * (c->arch == 0 ? 1 : 2)},
+        {"combined", t->combined, B * F * ((c->arch == 0 || c->activation == 2) ? 1 : 2)},
         {"l1_total", c->arch == 0 ? t->l1_total : t->l1_pre, B * (size_t)c->l1},
         {"net_output", t->net_output, B}, {"dy", t->dy, B},
         {"dl1_total", c->arch == 0 ? t->dl1_total : t->dl1_pre, B * (size_t)c->l1},
-        {"dcombined", t->dcombined, B * F * (c->arch == 0 ? 1 : 2)},
+        {"dcombined", t->dcombined, B * F * ((c->arch == 0 || c->activation == 2) ? 1 : 2)},
         {"dft_stm", t->dft_stm, B * F}, {"dft_nstm", t->dft_nstm, B * F},
         {"comb", t->comb, t->comb ? (size_t)c->ft_in * F : 0},
     };
@@ -1258,9 +1258,13 @@ static double simple_forward(ora_trainer* t, const int32_t* stm_idx, const int32
     const float* table = forward_table(t);
     ora_sparse_ft_forward(table, stm_idx, nnz, t->ft_stm, B, F, N, A);
     ora_sparse_ft_forward(table, nstm_idx, nnz, t->ft_nstm, B, F, N, A);
-    /* native_kernels.cu:1406-1450 simple_ft_post_fused_*: x = ft + bias stored back, act -> combined */
     const float* bias = t->g[1].w;
-    for (int p = 0; p < 2; ++p) {
+    size_t K1 = c->activation == 2 ? F : 2 * F;
+    int act = c->activation == 1 ? 1 : 0; /* the dense layers: SCReLU, or CReLU (also under Pairwise, trainer_simple.rs:1304) */
+    if (c->activation == 2) /* SimpleActivation::Pairwise: the LayerStack FT post, raw sums kept (trainer_simple.rs:1241-1262) */
+        ora_ft_post_perspective_fwd(t->ft_stm, t->ft_nstm, bias, t->combined, B, F, FT_POST_SCALE);
+    /* native_kernels.cu:1406-1450 simple_ft_post_fused_*: x = ft + bias stored back, act -> combined */
+    for (int p = 0; p < 2 && c->activation != 2; ++p) {
         float* ft = p == 0 ? t->ft_stm : t->ft_nstm;
         size_t off = p == 0 ? 0 : F;
         PAR_FOR
@@ -1272,10 +1276,10 @@ static double simple_forward(ora_trainer* t, const int32_t* stm_idx, const int32
                 t->combined[b * 2 * F + off + col] = c->activation == 0 ? a : a * a;
             }
     }
-    ora_dense_mm_fwd(t->combined, t->g[2].w, t->g[3].w, t->l1_pre, B, 2 * F, l1);
-    act_fwd(c->activation, t->l1_pre, t->l1_acted, B * l1);
+    ora_dense_mm_fwd(t->combined, t->g[2].w, t->g[3].w, t->l1_pre, B, K1, l1);
+    act_fwd(act, t->l1_pre, t->l1_acted, B * l1);
     ora_dense_mm_fwd(t->l1_acted, t->g[4].w, t->g[5].w, t->l2_pre, B, l1, l2);
-    act_fwd(c->activation, t->l2_pre, t->l2_acted, B * l2);
+    act_fwd(act, t->l2_pre, t->l2_acted, B * l2);
     ora_dense_mm_fwd(t->l2_acted, t->g[6].w, t->g[7].w, t->net_output, B, l2, 1);
     return run_loss(t, score, wdl, n, lambda, L);
 }
@@ -1284,18 +1288,26 @@ static double simple_forward(ora_trainer* t, const int32_t* stm_idx, const int32
 static void simple_backward(ora_trainer* t, const int32_t* stm_idx, const int32_t* nstm_idx, const int32_t* nnz, int n) {
     const ora_config* c = &t->cfg;
     size_t B = (size_t)n, F = (size_t)c->ft_out, l1 = (size_t)c->l1, l2 = (size_t)c->l2;
+    size_t K1 = c->activation == 2 ? F : 2 * F;
+    int act = c->activation == 1 ? 1 : 0;
     zero_grads(t);
     ora_dense_mm_bwd_input(t->dy, t->g[6].w, t->dl2_acted, B, l2, 1);
     ora_dense_mm_bwd_weight(t->l2_acted, t->dy, t->g[6].grad, B, l2, 1);
     ora_bias_grad(t->dy, t->g[7].grad, B, 1);
-    act_grad(c->activation, t->l2_pre, t->dl2_acted, t->dl2_pre, B * l2);
+    act_grad(act, t->l2_pre, t->dl2_acted, t->dl2_pre, B * l2);
     ora_dense_mm_bwd_input(t->dl2_pre, t->g[4].w, t->dl1_acted, B, l1, l2);
     ora_dense_mm_bwd_weight(t->l1_acted, t->dl2_pre, t->g[4].grad, B, l1, l2);
     ora_bias_grad(t->dl2_pre, t->g[5].grad, B, l2);
-    act_grad(c->activation, t->l1_pre, t->dl1_acted, t->dl1_pre, B * l1);
-    ora_dense_mm_bwd_input(t->dl1_pre, t->g[2].w, t->dcombined, B, 2 * F, l1);
-    ora_dense_mm_bwd_weight(t->combined, t->dl1_pre, t->g[2].grad, B, 2 * F, l1);
+    act_grad(act, t->l1_pre, t->dl1_acted, t->dl1_pre, B * l1);
+    ora_dense_mm_bwd_input(t->dl1_pre, t->g[2].w, t->dcombined, B, K1, l1);
+    ora_dense_mm_bwd_weight(t->combined, t->dl1_pre, t->g[2].grad, B, K1, l1);
     ora_bias_grad(t->dl1_pre, t->g[3].grad, B, l1);
+    if (c->activation == 2) { /* Pairwise: ft_post_perspective_grad per perspective, which also adds the bias gradient (trainer_simple.rs:2008-2040) */
+        ora_ft_post_perspective_grad(t->dcombined, t->ft_stm, t->g[1].w, t->dft_stm, t->g[1].grad, B, F, 0, F, FT_POST_SCALE);
+        ora_ft_post_perspective_grad(t->dcombined, t->ft_nstm, t->g[1].w, t->dft_nstm, t->g[1].grad, B, F, F / 2, F, FT_POST_SCALE);
+        ft_backward(t, stm_idx, nstm_idx, nnz, B);
+        return;
+    }
     /* native_kernels.cu:1452-1497 simple_bwd_ft_act_*_fused (x is the biased pre-activation) */
     for (int p = 0; p < 2; ++p) {
         const float* x = p == 0 ? t->ft_stm : t->ft_nstm;

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libtatara_b200.so")
 
 TB_OK = 0
 ARCH_LAYERSTACK, ARCH_SIMPLE = 0, 1
-ACT_CRELU, ACT_SCRELU = 0, 1
+ACT_CRELU, ACT_SCRELU, ACT_PAIRWISE = 0, 1, 2
 OPT_RANGER, OPT_RADAM, OPT_ADAMW = 0, 1, 2
 LOSS_SIGMOID, LOSS_WRM = 0, 1
 NUM_SLOTS = 4

@@ -26,6 +26,12 @@ struct LossParams {
     float nnue2score, in_scaling, in_offset, target_offset, target_scaling;
     float lambda;
     float norm;  // per-position gradient normaliser
+    // extended WRM (LossKind::wrm_extended, crates/nnue-train/src/trainer.rs:127-137): error power, asymmetry, per-position
+    // weights normalised by their sum over the batch (*weight_sum, on the device, filled by launch_wrm_weight_sum)
+    int extended = 0;
+    float pow_exp = 2.0f, qp_asymmetry = 0.0f, w1 = 0.0f, w2 = 0.5f;
+    float n_pos = 0.0f;
+    const double* weight_sum = nullptr;
 };
 
 struct OptScalars {
@@ -136,6 +142,9 @@ int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, c
 bool l1_forward_tc_supported(int K, int l1);
 int launch_l1_forward_tc(cudaStream_t s, const float* x, int K, const int* order, const TileDesc* tiles, const int* n_tiles,
                          int max_tiles, const float* weff, const float* beff, float* y, int l1, int nb, int* error_flag);
+// sum over the batch of the extended WRM loss's per-position weights (wrm_weight_sum, native_kernels.cu:520-545), in a
+// fixed order; partials: scratch of ceil(B / 256) doubles
+int launch_wrm_weight_sum(cudaStream_t s, const float* score, int B, LossParams lp, double* partials, double* weight_sum);
 int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
                            const float* wdl, const float* l2_w, const float* l2_b, const float* l3_w,
                            const float* l3_b, LossParams lp, int B, int l1, int l2, int nb, float* net_output,

@@ -399,14 +399,21 @@ int launch_l1_forward(cudaStream_t s, const float* x, int K, const int* order, c
 // ------------------------------------------------------------------------------------------------
 static __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-static __device__ __forceinline__ float loss_point(const LossParams& lp, float out, float score, float wdl, float* dy) {
+// the extended WRM loss's per-position weight (loss_wrm / wrm_weight_sum, native_kernels.cu:455-458, 538-543)
+static __device__ __forceinline__ float wrm_weight(const LossParams& lp, float target_wrm) {
+    const float wb = (target_wrm - 0.5f) * (target_wrm - 0.5f) * target_wrm * (1.0f - target_wrm);
+    return 1.0f + (powf(2.0f, lp.w1) - 1.0f) * powf(wb, lp.w2);
+}
+
+// returns the position's contribution to the reported loss sum (err^2 for the plain losses) and its output gradient
+static __device__ __forceinline__ double loss_point(const LossParams& lp, float out, float score, float wdl, float* dy) {
     if (lp.kind == 0) {
         const float p = sigmoidf_(out * lp.scale);
         const float ys = sigmoidf_(score * lp.scale);
         const float y = lp.lambda * wdl + (1.0f - lp.lambda) * ys;
         const float err = p - y;
         *dy = 2.0f * err * p * (1.0f - p) * lp.scale * lp.norm;
-        return err;
+        return (double)err * (double)err;
     }
     const float pt = (score - lp.target_offset) / lp.target_scaling;
     const float pmt = (-score - lp.target_offset) / lp.target_scaling;
@@ -417,8 +424,40 @@ static __device__ __forceinline__ float loss_point(const LossParams& lp, float o
     const float qm = sigmoidf_((-scorenet - lp.in_offset) / lp.in_scaling);
     const float qf = 0.5f * (1.0f + q - qm);
     const float err = qf - target;
-    *dy = err * (lp.nnue2score / lp.in_scaling) * (q * (1.0f - q) + qm * (1.0f - qm)) * lp.norm;
-    return err;
+    if (!lp.extended) {
+        *dy = err * (lp.nnue2score / lp.in_scaling) * (q * (1.0f - q) + qm * (1.0f - qm)) * lp.norm;
+        return (double)err * (double)err;
+    }
+    // loss_wrm, extended branch (native_kernels.cu:454-474): |err|^pow_exp, asymmetry above the target, weights
+    // normalised by their sum over the batch (which replaces the per-position normaliser)
+    const float weight = wrm_weight(lp, target_wrm);
+    const float asym = qf > target ? 1.0f + lp.qp_asymmetry : 1.0f;
+    const float abs_err = fabsf(err);
+    const float abs_pow = powf(abs_err, lp.pow_exp - 1.0f);
+    const float signed_pow = err < 0.0f ? -abs_pow : abs_pow;
+    const float inv_wsum = (float)(1.0 / *lp.weight_sum);
+    const float pred_grad = 0.5f * (lp.nnue2score / lp.in_scaling) * (q * (1.0f - q) + qm * (1.0f - qm));
+    *dy = (weight * inv_wsum) * (asym * lp.pow_exp * signed_pow) * pred_grad;
+    return (double)(asym * powf(abs_err, lp.pow_exp) * weight * lp.n_pos * inv_wsum);
+}
+
+__global__ void __launch_bounds__(256) k_wrm_weight_partials(const float* __restrict__ score, int B, LossParams lp,
+                                                             double* __restrict__ partials) {
+    __shared__ double s[256];
+    const int b = blockIdx.x * 256 + threadIdx.x;
+    double w = 0.0;
+    if (b < B) {
+        const float sc = score[b];
+        const float tp = sigmoidf_((sc - lp.target_offset) / lp.target_scaling), tn = sigmoidf_((-sc - lp.target_offset) / lp.target_scaling);
+        w = (double)wrm_weight(lp, 0.5f * (1.0f + tp - tn));
+    }
+    s[threadIdx.x] = w;
+    __syncthreads();
+    for (int d = 128; d > 0; d >>= 1) {
+        if ((int)threadIdx.x < d) s[threadIdx.x] += s[threadIdx.x + d];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partials[blockIdx.x] = s[0];
 }
 
 // sum of err^2 over the block in f64, one partial per block (fixed order: no atomics)
@@ -505,8 +544,7 @@ __global__ void __launch_bounds__(128) k_tail_layerstack(const float* __restrict
         }
         const float out = l3 + skip;
         float dyv;
-        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
-        e2 = (double)err * (double)err;
+        e2 = loss_point(lp, out, score[b], wdl[b], &dyv);
         net_output[b] = out;
         dy_out[b] = dyv;
         if (backward) {
@@ -603,9 +641,9 @@ __global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __res
         }
         const float out = l3 + skip;
         float dyv;
-        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
+        const double contrib = loss_point(lp, out, score[b], wdl[b], &dyv);
         if (lane == 0) {
-            e2 += (double)err * (double)err;
+            e2 += contrib;
             net_output[b] = out;
             dy_out[b] = dyv;
         }
@@ -642,6 +680,13 @@ __global__ void __launch_bounds__(256) k_tail_layerstack_warp(const float* __res
         }
     }
     block_loss_partial(e2, loss_partials);
+}
+
+int launch_wrm_weight_sum(cudaStream_t s, const float* score, int B, LossParams lp, double* partials, double* weight_sum) {
+    const int blocks = ceil_div(B, 256);
+    k_wrm_weight_partials<<<blocks, 256, 0, s>>>(score, B, lp, partials);
+    k_reduce_double<<<1, 256, 0, s>>>(partials, blocks, weight_sum);
+    return 2;
 }
 
 int launch_tail_layerstack(cudaStream_t s, const float* l1_total, const int* bucket, const float* score,
@@ -713,8 +758,7 @@ __global__ void __launch_bounds__(128) k_tail_simple(const float* __restrict__ l
         float out = l3_b[0];
         for (int o = 0; o < l2; ++o) out += a2[o] * sw3[o];
         float dyv;
-        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
-        e2 = (double)err * (double)err;
+        e2 = loss_point(lp, out, score[b], wdl[b], &dyv);
         net_output[b] = out;
         dy_out[b] = dyv;
         if (backward) {
@@ -774,9 +818,9 @@ __global__ void __launch_bounds__(256) k_tail_simple_warp(const float* __restric
         for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(full, part, d);
         const float out = b3 + part;
         float dyv;
-        const float err = loss_point(lp, out, score[b], wdl[b], &dyv);
+        const double contrib = loss_point(lp, out, score[b], wdl[b], &dyv);
         if (lane == 0) {
-            e2 += (double)err * (double)err;
+            e2 += contrib;
             net_output[b] = out;
             dy_out[b] = dyv;
         }

@@ -153,7 +153,7 @@ struct tb_trainer {
     float *pre[2] = {nullptr, nullptr}, *dft[2] = {nullptr, nullptr}, *combined = nullptr;
     float *l1_out = nullptr, *dl1 = nullptr, *net_output = nullptr, *dy = nullptr;
     float *tail_a = nullptr, *tail_b = nullptr, *tail_c = nullptr;  // LS: l2_input, dl2_out, l2_acted; Simple: l1_acted, dl2_pre, l2_acted
-    double *loss_partials = nullptr, *loss_acc = nullptr;
+    double *loss_partials = nullptr, *loss_acc = nullptr, *wrm_weight_sum = nullptr;
     int *order = nullptr, *n_tiles = nullptr, *seg_start = nullptr;
     TileDesc* tiles = nullptr;
     float *small_partials = nullptr, *l1w_partials = nullptr, *bias_partials = nullptr, *l1_weff = nullptr;
@@ -324,6 +324,12 @@ LossParams make_loss(const tb_loss* l, float lambda, float norm) {
     p.target_scaling = l->target_scaling;
     p.lambda = lambda;
     p.norm = norm;
+    // LossKind::wrm_extended (crates/nnue-train/src/trainer.rs:127-137)
+    p.extended = l->kind == TB_LOSS_WRM && !(l->pow_exp == 2.0f && l->qp_asymmetry == 0.0f && l->weight_boost_w1 == 0.0f);
+    p.pow_exp = l->pow_exp;
+    p.qp_asymmetry = l->qp_asymmetry;
+    p.w1 = l->weight_boost_w1;
+    p.w2 = l->weight_boost_w2;
     return p;
 }
 
@@ -337,9 +343,11 @@ int check_loss(tb_trainer* t, const tb_loss* l) {
     if (l->kind != TB_LOSS_WRM) return fail(t, TB_ERR_INVALID_ARGUMENT, "unknown loss kind %d", l->kind);
     if (!(l->nnue2score > 0.f) || !(l->in_scaling > 0.f) || !(l->target_scaling > 0.f))
         return fail(t, TB_ERR_INVALID_ARGUMENT, "wrm nnue2score / in_scaling / target_scaling must be > 0");
-    // LossKind::wrm_extended (crates/nnue-train/src/trainer.rs:127-137)
-    if (l->pow_exp != 2.0f || l->qp_asymmetry != 0.0f || l->weight_boost_w1 != 0.0f)
-        return fail(t, TB_ERR_UNSUPPORTED, "the extended WRM loss (pow_exp / qp_asymmetry / weight boost) is not implemented");
+    // LossKind::wrm_extended (crates/nnue-train/src/trainer.rs:127-137): its per-position weights are normalised by their sum
+    // over the batch, which with several ranks would have to be the sum over all ranks' shards
+    if ((l->pow_exp != 2.0f || l->qp_asymmetry != 0.0f || l->weight_boost_w1 != 0.0f) && t->cfg.world_size > 1)
+        return fail(t, TB_ERR_UNSUPPORTED, "the extended WRM loss (pow_exp / qp_asymmetry / weight boost) is built for one GPU only");
+    if (!(l->pow_exp > 0.0f) || !isfinite(l->pow_exp)) return fail(t, TB_ERR_INVALID_ARGUMENT, "wrm pow_exp must be finite and > 0");
     return TB_OK;
 }
 
@@ -360,7 +368,7 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
                                 t->items, t->item_seg, t->sort_hist);
       p.done(n); }
     { PhaseScope p(t, PH_FT_FWD);
-      const int mode = ls ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
+      const int mode = (ls || c.activation == TB_ACT_PAIRWISE) ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3);
       const int rps = c.piece_inputs > 0 ? c.piece_inputs : N;
       t->slice_fwd = ft_forward_slice_supported(F, N, A, rps);
       if (t->slice_fwd)
@@ -370,7 +378,13 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
       else
           p.done(launch_ft_forward(t->stream, mode, table, d.stm, d.nstm, d.nnz, t->groups[1].w, pre0, pre1, t->combined,
                                    t->items, B, F, N, A, FT_POST_SCALE, 2, t->p_ft16, t->p_out16)); }
-    const LossParams lp = make_loss(loss, lambda, d.norm);
+    LossParams lp = make_loss(loss, lambda, d.norm);
+    if (lp.extended) {  // the weight sum of this batch first (trainer_simple.rs:1430-1478 launches wrm_weight_sum before loss_wrm)
+        PhaseScope p(t, PH_TAIL);
+        lp.n_pos = (float)B;
+        lp.weight_sum = t->wrm_weight_sum;
+        p.done(launch_wrm_weight_sum(t->stream, d.score, B, lp, t->loss_partials, t->wrm_weight_sum));
+    }
     if (ls) {
         { PhaseScope p(t, PH_L1_FWD);
           p.done(launch_l1_forward(t->stream, t->combined, F, t->order, t->tiles, t->n_tiles, t->max_tiles, t->groups[2].w,
@@ -383,11 +397,11 @@ int run_forward(tb_trainer* t, const DevBatch& d, const tb_loss* loss, float lam
                                         t->loss_acc, backward)); }
     } else {
         { PhaseScope p(t, PH_L1_FWD);
-          p.done(launch_l1_forward(t->stream, t->combined, 2 * F, t->order, t->tiles, t->n_tiles, t->max_tiles, nullptr, nullptr,
+          p.done(launch_l1_forward(t->stream, t->combined, t->K, t->order, t->tiles, t->n_tiles, t->max_tiles, nullptr, nullptr,
                                    t->groups[2].w, t->groups[3].w, t->l1_out, c.l1_out, 0, t->l1_weff)); }
         { PhaseScope p(t, PH_TAIL);
           p.done(launch_tail_simple(t->stream, t->l1_out, d.score, d.wdl, t->groups[4].w, t->groups[5].w, t->groups[6].w,
-                                    t->groups[7].w, lp, c.activation, B, c.l1_out, c.l2_out, t->net_output, t->dy, t->dl1,
+                                    t->groups[7].w, lp, c.activation == TB_ACT_SCRELU ? 1 : 0, B, c.l1_out, c.l2_out, t->net_output, t->dy, t->dl1,
                                     t->tail_a, t->tail_b, t->tail_c, t->loss_partials, t->loss_acc, backward)); }
     }
     return TB_OK;
@@ -428,10 +442,10 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                                            t->tail_c, t->dy, t->dl1, t->small_partials, t->groups[4].grad, t->groups[5].grad,
                                            t->groups[6].grad, t->groups[7].grad, t->groups[3].grad)); }
         { PhaseScope p(t, PH_L1_WGRAD);
-          p.done(launch_l1_wgrad(t->stream, t->combined, 2 * F, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, c.l1_out, 0,
+          p.done(launch_l1_wgrad(t->stream, t->combined, t->K, t->dl1, t->order, t->tiles, t->n_tiles, t->max_tiles, c.l1_out, 0,
                                  t->l1w_partials, nullptr, t->groups[2].grad)); }
         { PhaseScope p(t, PH_L1_DGRAD);
-          p.done(launch_l1_dgrad_ftgrad(t->stream, c.activation == TB_ACT_CRELU ? 2 : 3, t->dl1, t->order, t->tiles, t->n_tiles,
+          p.done(launch_l1_dgrad_ftgrad(t->stream, c.activation == TB_ACT_PAIRWISE ? 1 : (c.activation == TB_ACT_CRELU ? 2 : 3), t->dl1, t->order, t->tiles, t->n_tiles,
                                         t->max_tiles, nullptr, t->groups[2].w, t->pre[0], t->pre[1], t->groups[1].w,
                                         FT_POST_SCALE, B, F, c.l1_out, 0, t->dft[0], t->dft[1], t->bias_partials,
                                         t->groups[1].grad, t->dgrad_rows)); }
@@ -733,7 +747,7 @@ void free_all(tb_trainer* t) {
         cudaFreeHost(t->loss_pinned[i]);
     }
     cudaFree(t->combined); cudaFree(t->l1_out); cudaFree(t->dl1); cudaFree(t->net_output); cudaFree(t->dy);
-    cudaFree(t->tail_a); cudaFree(t->tail_b); cudaFree(t->tail_c); cudaFree(t->loss_partials); cudaFree(t->loss_acc);
+    cudaFree(t->tail_a); cudaFree(t->tail_b); cudaFree(t->tail_c); cudaFree(t->loss_partials); cudaFree(t->loss_acc); cudaFree(t->wrm_weight_sum);
     cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
     cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials); cudaFree(t->l1_weff);
     cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
@@ -777,7 +791,7 @@ int create_impl(tb_trainer* t) {
     t->Nt = c.ft_in + (c.ft_factorize ? c.piece_inputs : 0);
     t->l1e = c.l1_out - 1;
     t->l2in = 2 * t->l1e;
-    t->K = ls ? c.ft_out : 2 * c.ft_out;
+    t->K = (ls || c.activation == TB_ACT_PAIRWISE) ? c.ft_out : 2 * c.ft_out;  // width of the L1 input
     auto add = [&](const char* name, int kind, float clamp, int64_t len) {
         Group g; g.name = name; g.kind = kind; g.clamp = clamp; g.len = len; t->groups.push_back(g);
     };
@@ -794,7 +808,7 @@ int create_impl(tb_trainer* t) {
         add("l3_w", 1, CLAMP_Q, nb * l2);
         add("l3_b", 2, CLAMP_NONE, nb);
     } else {
-        add("l1_w", 1, CLAMP_Q, 2 * F * l1);
+        add("l1_w", 1, CLAMP_Q, (int64_t)t->K * l1);
         add("l1_b", 2, CLAMP_Q, l1);
         add("l2_w", 1, CLAMP_Q, l1 * l2);
         add("l2_b", 2, CLAMP_Q, l2);
@@ -861,6 +875,7 @@ int create_impl(tb_trainer* t) {
     CU(t, dalloc(&t->tail_a, B * (size_t)(ls ? t->l2in : l1)));
     CU(t, dalloc(&t->tail_b, B * l2)); CU(t, dalloc(&t->tail_c, B * l2));
     CU(t, dalloc(&t->loss_partials, B / 128 + 1024)); CU(t, dalloc(&t->loss_acc, 1));  // one partial per tail block (<= 148 * 4 or B / 128)
+    CU(t, dalloc(&t->wrm_weight_sum, 1));
     t->max_tiles = (int)(B / TB_TILE_M) + TB_MAX_BUCKETS + 2;
     t->max_units = sort_max_units(t->max_tiles);
     CU(t, dalloc(&t->order, B)); CU(t, dalloc(&t->n_tiles, 2)); CU(t, dalloc(&t->seg_start, TB_MAX_BUCKETS + 3));
@@ -922,7 +937,11 @@ int validate_config(const tb_config* c) {
         return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "batch_capacity must be a multiple of 16 in [16, 2^20] (got %d)", c->batch_capacity);
     if (c->ft_out < 128 || c->ft_out % 128 != 0 || c->ft_out > 4096)
         return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "ft_out must be a multiple of 128 in [128, 4096] (got %d)", c->ft_out);
-    if (c->arch == TB_ARCH_LAYERSTACK && c->ft_out < 256)
+    if (c->arch == TB_ARCH_SIMPLE && (c->activation < TB_ACT_CRELU || c->activation > TB_ACT_PAIRWISE))
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "unknown activation %d", c->activation);
+    if ((c->arch == TB_ARCH_LAYERSTACK || c->activation == TB_ACT_PAIRWISE) && c->ft_out < 256)
+        return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "the pairwise FT activation needs ft_out >= 256 (got %d)", c->ft_out);
+    if (false)
         return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "LayerStack needs ft_out >= 256 (got %d)", c->ft_out);
     if (c->ft_in < 1 || c->max_active < 1 || c->max_active > 256) return fail(nullptr, TB_ERR_INVALID_ARGUMENT, "bad ft_in / max_active");
     if (c->ft_factorize && (c->piece_inputs < 1 || c->ft_in % c->piece_inputs != 0))

@@ -162,14 +162,16 @@ def layerstack_default_init(fs: FeatureSetSpec, ft_out: int, l1: int, l2: int, n
     }
 
 
-def simple_default_init(fs: FeatureSetSpec, ft_out: int, l1: int, l2: int) -> Dict[str, np.ndarray]:
-    """SimpleInit::default_uniform with the call shapes of trainer_simple.rs:454-463."""
+def simple_default_init(fs: FeatureSetSpec, ft_out: int, l1: int, l2: int, pairwise: bool = False) -> Dict[str, np.ndarray]:
+    """SimpleInit::default_uniform with the call shapes of trainer_simple.rs:454-463 (the L1 input is 2 * ft_out wide,
+    ft_out with the Pairwise activation)."""
     N, F = fs.ft_in, ft_out
+    K1 = F if pairwise else 2 * F
     ft_w = np.zeros(fs.train_ft_in * F, np.float32)
     ft_w[:N * F] = _sample(N * F, 1, N, 1, 0, 0.01, 0x5071E001)
     return {
         "ft_w": ft_w, "ft_b": _sample(F, 1, N, 1, 0, 0.01, 0x5071E002),
-        "l1_w": _sample(2 * F * l1, 1, 2 * F, 1, 0, 0.01, 0x5071E003), "l1_b": _sample(l1, 1, 2 * F, 1, 0, 0.01, 0x5071E004),
+        "l1_w": _sample(K1 * l1, 1, K1, 1, 0, 0.01, 0x5071E003), "l1_b": _sample(l1, 1, K1, 1, 0, 0.01, 0x5071E004),
         "l2_w": _sample(l1 * l2, 1, l1, 1, 0, 0.01, 0x5071E005), "l2_b": _sample(l2, 1, l1, 1, 0, 0.01, 0x5071E006),
         "l3_w": _sample(l2, 1, l2, 1, 0, 0.01, 0x5071E007), "l3_b": _sample(1, 1, l2, 1, 0, 0.01, 0x5071E008),
     }
@@ -393,12 +395,12 @@ class SimpleGpuTrainer(_Trainer):
         cfg.device, cfg.arch, cfg.batch_capacity = device, L.ARCH_SIMPLE, batch_size
         cfg.ft_in, cfg.piece_inputs, cfg.ft_factorize = feature_set.ft_in, feature_set.piece_inputs, int(feature_set.ft_factorize)
         cfg.max_active, cfg.ft_out, cfg.l1_out, cfg.l2_out, cfg.num_buckets = feature_set.max_active, ft_out, l1_out, l2_out, 0
-        cfg.activation = {"crelu": L.ACT_CRELU, "screlu": L.ACT_SCRELU}[activation]
+        cfg.activation = {"crelu": L.ACT_CRELU, "screlu": L.ACT_SCRELU, "pairwise": L.ACT_PAIRWISE}[activation]
         cfg.optimizer, cfg.precision = OPTIMIZERS[optimizer], precision.mask()
         cfg.wd_ft = cfg.wd_dense = cfg.wd_bias = weight_decay
         cfg.lr_mult_ft = cfg.lr_mult_dense = cfg.lr_mult_bias = 1.0
         _dp(cfg, world_size, rank, nccl_id)
         self.feature_set = feature_set
         if isinstance(init, str):
-            init = simple_default_init(feature_set, ft_out, l1_out, l2_out)
+            init = simple_default_init(feature_set, ft_out, l1_out, l2_out, pairwise=activation == "pairwise")
         super().__init__(cfg, init)

@@ -280,6 +280,80 @@ def test_simple_step_matches_oracle(F, l1, l2, B, act, factorize):
         assert_close_scaled(got["m"], ot.group(name, "m"), TOL_GRAD, "m " + name)
 
 
+def test_simple_pairwise_step_matches_oracle():
+    """SimpleActivation::Pairwise (bins/nnue_train/src/trainer_simple.rs:1241-1262, 2008-2040): the LayerStack FT post in
+    front of the Simple dense layers; the L1 input is ft_out wide."""
+    F, l1, l2, B = 256, 32, 32, 272
+    fs = KP_FS
+    rng = np.random.default_rng(44)
+    init = tb.simple_default_init(fs, F, l1, l2, pairwise=True)
+    init["ft_w"][:fs.ft_in * F] *= 12.0
+    for k in ("l1_w", "l2_w", "l3_w"):
+        init[k] *= 8.0
+    init["ft_w"][fs.ft_in * F:] = (rng.standard_normal(fs.piece_inputs * F) * 0.02).astype(np.float32)
+    assert init["l1_w"].size == F * l1
+    tr = tb.SimpleGpuTrainer(B, F, l1, l2, fs, activation="pairwise", optimizer="adamw", weight_decay=0.0, init=init)
+    ot = _oracle_for(tr, "simple", fs, F, l1, l2, 0, "adamw", (0.0, 0.0, 0.0), B, activation=2)
+    _sync_weights(tr, ot, init)
+    batch = tb.synthetic_batch(tb.SYNTH_SEED + 4, B, fs, with_bucket=False)
+    lt = tb.LossKind.wrm(nnue2score=290.0, in_scaling=290.0, in_offset=0.0, target_offset=0.0, target_scaling=290.0)
+    lo = O.wrm_loss(290.0, 290.0, 0.0, 0.0, 290.0)
+    l_gpu = tr.forward_backward(batch, 0.25, lt)
+    l_cpu = ot.step(_batch_dict(batch), 8.75e-4, 0.25, lo, do_optimizer=False)
+    assert np.array_equal(tr.read_buffer("ft_stm", B * F).view(np.uint32), ot.buffer("ft_stm").view(np.uint32))   # raw sums are kept
+    assert_close(tr.read_buffer("combined", B * F), ot.buffer("combined"), TOL_FWD, "combined")
+    assert_close(tr.read_buffer("net_output", B), ot.buffer("net_output"), TOL_FWD, "net_output")
+    assert abs(l_gpu - l_cpu) <= TOL_FWD * (1 + abs(l_cpu))
+    assert_close_scaled(tr.read_buffer("dft_stm", B * F), ot.buffer("dft_stm"), TOL_GRAD, "dft_stm")
+    for name in ot.names:
+        assert_close_scaled(tr.download_grad(name), ot.group(name, "grad"), TOL_GRAD, "grad " + name)
+    tr.apply_optimizer(8.75e-4); ot.apply_optimizer(8.75e-4)
+    for name in ot.names:
+        assert_close(tr.download_group(name)["w"], ot.group(name, "w"), TOL_FWD, "w " + name)
+
+
+@pytest.mark.parametrize("arch", ["simple", "layerstack"])
+def test_extended_wrm_loss_matches_oracle(arch):
+    """LossKind::Wrm with pow_exp, qp_asymmetry and the weight boost (loss_wrm extended branch + wrm_weight_sum,
+    native_kernels.cu:408-545): the per-position weights are normalised by their sum over the batch."""
+    B = 256
+    rng = np.random.default_rng(9)
+    kw = dict(nnue2score=600.0, in_scaling=340.0, in_offset=270.0, target_offset=270.0, target_scaling=380.0, pow_exp=2.5,
+              qp_asymmetry=0.3, weight_boost_w1=1.5, weight_boost_w2=0.5)
+    lt = tb.LossKind.wrm(**kw)
+    lo = O.wrm_loss(600.0, 340.0, 270.0, 270.0, 380.0, 2.5, 0.3, 1.5, 0.5)
+    if arch == "simple":
+        F, l1, l2, fs = 256, 32, 32, KP_FS
+        init = tb.simple_default_init(fs, F, l1, l2)
+        init["ft_w"][:fs.ft_in * F] *= 4.0
+        for k in ("l1_w", "l2_w", "l3_w"):
+            init[k] *= 20.0
+        tr = tb.SimpleGpuTrainer(B, F, l1, l2, fs, activation="crelu", optimizer="adamw", weight_decay=0.0, init=init)
+        ot = _oracle_for(tr, "simple", fs, F, l1, l2, 0, "adamw", (0.0, 0.0, 0.0), B)
+        batch = tb.synthetic_batch(31, B, fs, with_bucket=False)
+    else:
+        F, l1, l2, fs = 256, 16, 32, LS_FS
+        init = _perturb(tb.layerstack_default_init(fs, F, l1, l2, 9), rng, ["ft_b", "l1_b", "l1_shared_bias", "l2_b", "l3_b"])
+        init["ft_w"][:fs.ft_in * F] *= 30.0
+        for k in ("l1_w", "l1_shared_weight", "l2_w", "l3_w"):
+            init[k] = init[k] * np.float32(40.0)
+        tr = tb.GpuTrainer(B, F, l1, l2, 9, fs, optimizer="adamw", init=init)
+        ot = _oracle_for(tr, "layerstack", fs, F, l1, l2, 9, "adamw", (0.01, 0.01, 0.01), B)
+        batch = tb.synthetic_batch(32, B, fs)
+    _sync_weights(tr, ot, init)
+    l_gpu = tr.forward_backward(batch, 0.25, lt)
+    l_cpu = ot.step(_batch_dict(batch), 1e-3, 0.25, lo, do_optimizer=False)
+    assert abs(l_gpu - l_cpu) <= 1e-5 * (1 + abs(l_cpu)), (l_gpu, l_cpu)
+    assert_close_scaled(tr.read_buffer("dy", B), ot.buffer("dy"), TOL_GRAD, "dy")
+    assert np.abs(ot.buffer("dy")).max() > 0
+    for name in ot.names:
+        assert_close_scaled(tr.download_grad(name), ot.group(name, "grad"), TOL_GRAD, "grad " + name)
+    # the plain parameters still take the default path: same loss as the sigmoid-shaped WRM
+    plain = tb.LossKind.wrm(nnue2score=600.0, in_scaling=340.0, in_offset=270.0, target_offset=270.0, target_scaling=380.0)
+    assert tr.validate_step(batch, 0.25, plain)[0] != l_gpu
+    tr.close()
+
+
 def test_layerstack_loss_curve_and_lag():
     """8 steps on changing batches: the per-step loss follows the oracle within 1e-3 relative, the reported
     loss lags by one step, Ranger's look-ahead fires on step 6."""
