@@ -199,7 +199,7 @@ def run_cpu(w, wname, threads, sample_b, steps, warmup, limit_s=None):
     return sample_b * done / dt, done, dt / done * 1e3
 
 
-def micro_lists(rng, B, A, space, lo=30, hi=38, slices=0):
+def micro_lists(rng, B, A, space, lo=30, hi=38, slices=0, slice_p=None):
     """Index lists of the FT microbenchmark: per position `lo..hi` distinct indices drawn uniformly from `space` rows,
     unsorted, padded with -1 to A slots.  With `slices` > 0 every position draws its rows inside one uniformly chosen
     slice of `space` rows (king-relative feature sets: `slices` king buckets x `space` piece inputs)."""
@@ -216,7 +216,8 @@ def micro_lists(rng, B, A, space, lo=30, hi=38, slices=0):
         np.put_along_axis(dup, order, dup_sorted, axis=1)
         idx[dup] = rng.integers(0, space, int(dup.sum()))
     if slices:
-        idx += rng.integers(0, slices, B)[:, None] * space
+        pick = rng.integers(0, slices, B) if slice_p is None else rng.choice(slices, B, p=slice_p)
+        idx += pick[:, None] * space
     out = np.full((B, A), -1, np.int32)
     out[:, :hi] = idx
     out[np.arange(A)[None, :] >= nnz[:, None]] = -1
@@ -379,6 +380,42 @@ def replicas_identical(tr, dist, names):
     t = torch.tensor([1 if same else 0], dtype=torch.int32)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     return bool(t[0])
+
+
+def skewed_run(tb, w, device, steps, uniform_ms, prec):
+    """The headline workload on king-skewed batches: every position's rows lie in one king-bucket slice per perspective, the
+    slice drawn from a Zipf law (p_k ~ 1 / k^1.2: the most frequent king bucket holds about 30 % of the items), as real
+    game positions crowd a few king squares.  Reports the step time beside the uniform generator's."""
+    kb, pi, A = FS_DIMS[w["fs"]]
+    rng = np.random.default_rng(12)
+    p = 1.0 / np.arange(1, kb + 1) ** 1.2
+    p /= p.sum()
+    tr, loss, fs = make_trainer(tb, w, device, 1, 0, None, precision=prec)
+    batches = []
+    for i in range(2):
+        stm, nnz = micro_lists(rng, BATCH, A, pi, lo=A - 2, hi=A - 2, slices=kb, slice_p=p)
+        nstm, _ = micro_lists(rng, BATCH, A, pi, lo=A - 2, hi=A - 2, slices=kb, slice_p=p)
+        batches.append(tb.BatchData(stm, nstm, nnz, np.clip(np.round(rng.normal(0, 400, BATCH)), -3000, 3000).astype(np.float32),
+                                    rng.choice(np.array([0.0, 0.5, 1.0], np.float32), BATCH),
+                                    rng.integers(0, 9, BATCH).astype(np.int32) if w["arch"] == "layerstack" else None))
+    for i, b in enumerate(batches):
+        tr.stage_batch(i, b)
+    for i in range(3):
+        tr.train_step_staged(i % 2, LR, 0.0, loss)
+    tr.synchronize()
+    tr.timer_start()
+    for i in range(steps):
+        tr.train_step_staged(i % 2, LR, 0.0, loss)
+    ms = tr.timer_stop() / steps
+    tr.profile_enable(True)
+    tr.profile_reset()
+    for i in range(4):
+        tr.train_step_staged(i % 2, LR, 0.0, loss)
+    prof = {k: round(v[0] / 4, 4) for k, v in tr.profile_read().items() if v[1] > 0 and k in ("ft_forward", "ft_backward", "inverse_index")}
+    tr.close()
+    return {"generator": "king bucket of each perspective ~ Zipf(1.2) over %d slices (top slice %.0f %% of the items)" % (kb, 100 * p[0]),
+            "ms_per_step": round(ms, 4), "uniform_ms_per_step": round(uniform_ms, 4), "slowdown": round(ms / uniform_ms, 4),
+            "kernels_ms": prof}
 
 
 def short_config(tb, wname, device, steps, peak):
@@ -625,6 +662,8 @@ def main():
             tr.close()   # (with several ranks the communicator is torn down by all of them together, below)
             if not args.no_other_configs:
                 line["other_configs"] = [short_config(tb, n, device, 10, peak) for n in ("cfg1", "cfg2") if n != args.workload]
+            if not args.no_other_configs:
+                line["skewed"] = skewed_run(tb, w, device, 10, ms / K, prec)
             if not args.no_microbench:
                 line["ft_microbench"] = run_microbench(tb, device, peak)
             if not args.no_cpu_baseline:

@@ -105,13 +105,15 @@ int launch_ft_backward_split(cudaStream_t s, const int* run_if, const void* dft_
 // kernels, launched with it as run_if, do the work instead.
 bool ft_backward_slice_supported(int F, int N, int A, int rows_per_slice);
 size_t ft_backward_slice_ints(int n_items, int A, int rows_per_slice);
+// floats of the partial slabs launch_ft_backward_slice needs (slices of many chunks are shared by several blocks)
+size_t ft_backward_slice_slab_floats(int n_items, int A, int rows_per_slice, int F);
 const int* ft_slice_outside_flag(int* fwd_work, int n_items, int N, int rows_per_slice);
 int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int* bwd_work, int B, int A, int N,
                          int rows_per_slice, int n_persp);
 // the rows of slices [slice_begin, slice_begin + slice_count)
 int launch_ft_backward_slice(cudaStream_t s, const void* dft_stm, const void* dft_nstm, int* fwd_work, int* bwd_work, int B,
                              int A, int N, int F, int rows_per_slice, int n_persp, int slice_begin, int slice_count, float* grad,
-                             int dft_half = 0);
+                             float* slabs, int dft_half = 0);
 int sort_max_units(int max_tiles);
 // The two sorts of a step: positions by bucket -> order, bucket segments seg_start [nb + 2], tiles (room for max_tiles
 // tiles followed by the work units; n_tiles is {tile count, unit count}); items (position, perspective) of both

@@ -15,6 +15,12 @@
 // reproducible run to run, but not the sequential one.  (The reference's own kernel keeps four interleaved partial
 // sums over a list whose order is set by atomics, native_kernels.cu:1767-1806.)
 //
+// Skewed data (real king squares crowd a few buckets): a slice's chunks are handed out in groups of BWD_GROUP consecutive
+// chunks, a block per (group, column strip), so that a slice holding a third of the batch does not leave its strips'
+// blocks running alone.  The first group of a slice writes the gradient rows, every further group a partial slab of its
+// own, and k_bwd_combine adds the slabs onto the rows in group order: one more fixed, non-sequential association, used
+// only by slices of more than BWD_GROUP chunks (about 3600 items).
+//
 // Both kernels return at once when the batch has a row outside its item's slice (outside_flag != 0); the generic
 // kernels, gated the other way round, then do the work.
 #include "ft_slice.cuh"
@@ -22,13 +28,15 @@
 #define INV_SORT_N 2048  // rows per slice limit (bitonic sort size)
 #define BWD_HOT 256      // list length from which a list is summed as four quarters by the four groups of one warp
 #define BWD_DESC 64      // chunk descriptors a block stages in shared memory
+#define BWD_GROUP 4      // chunks per block: a slice of more chunks is shared by several blocks
 
 struct BwdLayout {
     int CH;             // slots per chunk (multiple of 8)
     int rps_pad;        // row records per chunk
     int region;         // 16-bit list cells per chunk (every list is padded to a multiple of 8 cells: 16-byte code loads)
     int max_chunks;
-    size_t off_first, off_len, off_rowinfo, off_lists, total_ints;
+    int max_groups, max_slabs;  // (slice, chunk group) work units; partial slabs of the groups behind a slice's first
+    size_t off_first, off_len, off_groups, off_rowinfo, off_lists, total_ints;
 };
 
 static inline size_t bwd_region(int CH, int rps, int A_pad) { return (size_t)CH * A_pad + 8 * (size_t)rps; }
@@ -53,9 +61,13 @@ static inline BwdLayout bwd_layout(int n_items, int A, int rps) {
     L.rps_pad = (rps + 3) / 4 * 4;
     L.region = (int)bwd_region(CH, rps, A_pad);
     L.max_chunks = CH > 0 ? n_items / CH + SORT_KEYS_LIMIT + 2 : 0;
+    L.max_slabs = CH > 0 ? n_items / (CH * BWD_GROUP) + SORT_KEYS_LIMIT / BWD_GROUP + 2 : 0;
+    L.max_groups = SORT_KEYS_LIMIT + L.max_slabs;
     size_t o = 4 * (size_t)L.max_chunks + 4;            // chunk records + their count
     L.off_first = o; o += SORT_KEYS_LIMIT + 4;          // first chunk of every slice (+ end)
     L.off_len = o; o += 4 * (size_t)L.max_chunks;  // per chunk {list cells, long-list records, non-empty records, 0}
+    // groups: [0] their count, [4 ..] first group of every slice (+ end), then {slice, first chunk, end chunk, slab or -1}
+    L.off_groups = o; o += 4 + (SORT_KEYS_LIMIT + 4) + 4 * (size_t)L.max_groups;
     L.off_rowinfo = o; o += 2 * (size_t)L.max_chunks * L.rps_pad;
     L.off_lists = o; o += ((size_t)L.max_chunks * L.region + 1) / 2 + 4;
     L.total_ints = o;
@@ -69,10 +81,13 @@ bool ft_backward_slice_supported(int F, int N, int A, int rps) {
 }
 
 size_t ft_backward_slice_ints(int n_items, int A, int rps) { return bwd_layout(n_items, A, rps).total_ints; }
+size_t ft_backward_slice_slab_floats(int n_items, int A, int rps, int F) {
+    return (size_t)bwd_layout(n_items, A, rps).max_slabs * (size_t)rps * (size_t)F;
+}
 
 // chunks of <= ipc consecutive slots of one slice; first[k] = index of slice k's first chunk, first[n_keys] = total
 __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int ipc, FwdWork* __restrict__ work,
-                             int* __restrict__ n_work, int* __restrict__ first) {
+                             int* __restrict__ n_work, int* __restrict__ first, int* __restrict__ groups, int max_groups) {
     __shared__ int s_base[SORT_KEYS_LIMIT + 1], s_seg[SORT_KEYS_LIMIT + 2];
     for (int k = threadIdx.x; k <= n_keys; k += blockDim.x) s_seg[k] = item_seg[k];  // one round trip, not n_keys
     __syncthreads();
@@ -84,6 +99,18 @@ __global__ void k_chunk_plan(const int* __restrict__ item_seg, int n_keys, int i
         }
         s_base[n_keys] = run;
         *n_work = run;
+        // (slice, chunk group) work units of the real slices (the last key holds items without a slice: they have no rows)
+        int* group_first = groups + 4;
+        int4* rec = reinterpret_cast<int4*>(groups + 4 + SORT_KEYS_LIMIT + 4);
+        int gi = 0, slab = 0;
+        for (int k = 0; k < n_keys - 1; ++k) {
+            group_first[k] = gi;
+            const int c0 = s_base[k], nc = s_base[k + 1] - c0;
+            if (nc == 0 && gi < max_groups) rec[gi++] = make_int4(k, c0, c0, -1);  // an empty slice: its rows are zeroed
+            for (int c = 0; c < nc && gi < max_groups; c += BWD_GROUP) rec[gi++] = make_int4(k, c0 + c, c0 + min(nc, c + BWD_GROUP), c == 0 ? -1 : slab++);
+        }
+        group_first[n_keys - 1] = gi;
+        groups[0] = gi;
     }
     __syncthreads();
     for (int k = threadIdx.x; k <= n_keys; k += blockDim.x) first[k] = s_base[k];
@@ -276,12 +303,12 @@ __global__ void __launch_bounds__(1024) k_inv_chunk(const unsigned short* __rest
 template <bool DH>
 __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __restrict__ dft_stm, const void* __restrict__ dft_nstm,
                                                                 const int* __restrict__ info, const FwdWork* __restrict__ work,
-                                                                const int* __restrict__ first, const int* __restrict__ len,
+                                                                const int* __restrict__ groups, const int* __restrict__ len,
                                                                 const unsigned long long* __restrict__ rowinfo,
                                                                 const unsigned short* __restrict__ lists,
                                                                 const int* __restrict__ outside_flag, int B, int F, int N, int rps,
-                                                                int rps_pad, int CH, int region, int slice_begin,
-                                                                float* __restrict__ grad) {
+                                                                int rps_pad, int CH, int region, int slice_begin, int slice_count,
+                                                                float* __restrict__ grad, float* __restrict__ slabs) {
     constexpr int W = DH ? 8 : 4;    // columns per lane
     constexpr int DSZ = DH ? 2 : 4;  // bytes per dft element
     typedef LaneAcc<DH> Acc;
@@ -291,20 +318,28 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __res
     __shared__ int s_ctl[4];
     __shared__ int s_desc[BWD_DESC][5];
     if (*outside_flag) return;
-    const int k = slice_begin + blockIdx.x, strip = blockIdx.y;
+    // the groups of this launch's slices; the grid has a block row per slice, so a block takes a second group only when
+    // some slice is shared (skewed data)
+    const int g_lo = groups[4 + slice_begin], g_hi = groups[4 + slice_begin + slice_count];
+    for (int gid = g_lo + (int)blockIdx.x; gid < g_hi; gid += (int)gridDim.x) {
+    __syncthreads();  // the previous group's last reads of the shared buffers
+    const int4 gr = reinterpret_cast<const int4*>(groups + 4 + SORT_KEYS_LIMIT + 4)[gid];
+    const int k = gr.x, strip = blockIdx.y;
     const int row0 = k * rps;
     const int rows = min(rps, N - row0);
     const int tid = threadIdx.x, lane = tid & 31;
     const int j = lane & 7;
     const int col = 8 * W * strip + W * j;
-    const int c_first = first[k], c_end = first[k + 1];
+    const int c_first = gr.y, c_end = gr.z;
+    // the slice's first group sums into the gradient rows, a later one into its own slab (combined by k_bwd_combine)
+    float* __restrict__ out = gr.w < 0 ? grad + (size_t)row0 * F : slabs + (size_t)gr.w * rps * F;
     if (c_first == c_end) {  // no item reads this slice: its gradient rows are zero
         for (int e = tid; e < rows * 8; e += 1024) {
-            float4* gp = reinterpret_cast<float4*>(grad + (size_t)(row0 + (e >> 3)) * F + col);
+            float4* gp = reinterpret_cast<float4*>(out + (size_t)(e >> 3) * F + col);
 #pragma unroll
             for (int i = 0; i < W / 4; ++i) gp[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        return;
+        continue;
     }
     unsigned char* s_dft = s_raw;
     unsigned long long* s_info = reinterpret_cast<unsigned long long*>(s_raw + ((size_t)CH + 1) * 128);
@@ -424,7 +459,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __res
             part.add(part.shfl_xor(8));
             part.add(part.shfl_xor(16));
             if (g == 0) {
-                float* gp = grad + (size_t)(row0 + r) * F + col;
+                float* gp = out + (size_t)r * F + col;
                 if (!first_chunk) {
                     Acc pv;
                     pv.load_cg(gp);
@@ -447,7 +482,7 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __res
                 const unsigned long long x = s_info[base + g];
                 if ((int)(x >> 32) < rows) {
                     ri = x;
-                    if (!first_chunk) prev.load_cg(grad + (size_t)(row0 + (int)(x >> 32)) * F + col);
+                    if (!first_chunk) prev.load_cg(out + (size_t)(int)(x >> 32) * F + col);
                 }
             }
         };
@@ -464,16 +499,40 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __res
                 const bool have = ri != ~0ull;
                 const int r = (int)(ri >> 32), off = have ? (int)((ri >> 16) & 0xffffu) : 0, cnt = have ? (int)(ri & 0xffffu) : 0;
                 sum_range(s_lists + 2 * off, 0, cnt, prev);
-                if (have) prev.store_cg(grad + (size_t)(row0 + r) * F + col);
+                if (have) prev.store_cg(out + (size_t)r * F + col);
             }
             base = base_n; ri = ri_n; prev = prev_n;
         }
+    }
+    }  // groups of this block
+}
+
+// grad rows of a slice += its groups' slabs, in group order
+__global__ void __launch_bounds__(256) k_bwd_combine(const int* __restrict__ groups, const int* __restrict__ outside_flag,
+                                                      const float4* __restrict__ slabs, float4* __restrict__ grad, int rps, int F,
+                                                      int N, int slice_begin) {
+    if (*outside_flag) return;
+    const int k = slice_begin + blockIdx.y;
+    const int* group_first = groups + 4;
+    const int4* rec = reinterpret_cast<const int4*>(groups + 4 + SORT_KEYS_LIMIT + 4);
+    const int g0 = group_first[k], g1 = group_first[k + 1];
+    if (g1 - g0 <= 1) return;
+    const int rows = min(rps, N - k * rps);
+    const size_t n4 = (size_t)rows * F / 4, slab4 = (size_t)rps * F / 4;
+    float4* dst = grad + (size_t)k * rps * F / 4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = dst[i];
+        for (int g = g0 + 1; g < g1; ++g) {
+            const float4 v = __ldcs(slabs + (size_t)rec[g].w * slab4 + i);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        dst[i] = a;
     }
 }
 
 struct BwdPointers {
     FwdWork* chunks;
-    int *n_chunks, *first, *len;
+    int *n_chunks, *first, *len, *groups;
     unsigned long long* rowinfo;
     unsigned short* lists;
 };
@@ -483,6 +542,7 @@ static inline BwdPointers bwd_pointers(int* bwd_work, const BwdLayout& L) {
     p.n_chunks = bwd_work + 4 * (size_t)L.max_chunks;
     p.first = bwd_work + L.off_first;
     p.len = bwd_work + L.off_len;
+    p.groups = bwd_work + L.off_groups;
     p.rowinfo = reinterpret_cast<unsigned long long*>(bwd_work + L.off_rowinfo);
     p.lists = reinterpret_cast<unsigned short*>(bwd_work + L.off_lists);
     return p;
@@ -501,7 +561,7 @@ int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int
     const SliceBuffers sb = slice_buffers(fwd_work, n_items, n_keys);
     const BwdLayout L = bwd_layout(n_items, A, rps);
     const BwdPointers P = bwd_pointers(bwd_work, L);
-    k_chunk_plan<<<1, 128, 0, s>>>(item_seg, n_keys, L.CH, P.chunks, P.n_chunks, P.first);
+    k_chunk_plan<<<1, 128, 0, s>>>(item_seg, n_keys, L.CH, P.chunks, P.n_chunks, P.first, P.groups, L.max_groups);
     const int rps_h = (rps + 1) & ~1;
     const size_t inv_smem = (size_t)32 * rps_h * 2 + (size_t)INV_SORT_N * 4 * 2 + (size_t)L.region * 2;
     cudaFuncSetAttribute(k_inv_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)inv_smem);
@@ -512,7 +572,8 @@ int launch_inverse_slice(cudaStream_t s, const int* item_seg, int* fwd_work, int
 }
 
 int launch_ft_backward_slice(cudaStream_t s, const void* dft_stm, const void* dft_nstm, int* fwd_work, int* bwd_work, int B,
-                             int A, int N, int F, int rps, int n_persp, int slice_begin, int slice_count, float* grad, int dft_half) {
+                             int A, int N, int F, int rps, int n_persp, int slice_begin, int slice_count, float* grad, float* slabs,
+                             int dft_half) {
     if (B <= 0) return 0;
     const int n_items = n_persp * B;
     const int n_slices = ceil_div(N, rps), n_keys = n_slices + 1;
@@ -522,16 +583,21 @@ int launch_ft_backward_slice(cudaStream_t s, const void* dft_stm, const void* df
     const BwdPointers P = bwd_pointers(bwd_work, L);
     const size_t smem = bwd_smem_bytes(L.CH, rps, A_pad);
     if (slice_begin < 0 || slice_count <= 0 || slice_begin + slice_count > n_slices) return 0;
+    const int grid_x = slice_count;  // a block row per slice; rows take the extra groups of shared slices in turn
     if (dft_half) {
         cudaFuncSetAttribute(k_ft_backward_slice<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k_ft_backward_slice<true><<<dim3(slice_count, F / 64), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len,
-                                                                                P.rowinfo, P.lists, sb.outside_flag, B, F, N, rps,
-                                                                                L.rps_pad, L.CH, L.region, slice_begin, grad);
+        k_ft_backward_slice<true><<<dim3(grid_x, F / 64), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.groups, P.len,
+                                                                                 P.rowinfo, P.lists, sb.outside_flag, B, F, N, rps,
+                                                                                 L.rps_pad, L.CH, L.region, slice_begin, slice_count, grad,
+                                                                                 slabs);
     } else {
         cudaFuncSetAttribute(k_ft_backward_slice<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k_ft_backward_slice<false><<<dim3(slice_count, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.first, P.len,
-                                                                                 P.rowinfo, P.lists, sb.outside_flag, B, F, N, rps,
-                                                                                 L.rps_pad, L.CH, L.region, slice_begin, grad);
+        k_ft_backward_slice<false><<<dim3(grid_x, F / 32), 1024, smem, s>>>(dft_stm, dft_nstm, sb.info, P.chunks, P.groups, P.len,
+                                                                                  P.rowinfo, P.lists, sb.outside_flag, B, F, N, rps,
+                                                                                  L.rps_pad, L.CH, L.region, slice_begin, slice_count, grad,
+                                                                                  slabs);
     }
-    return 1;
+    k_bwd_combine<<<dim3(148, slice_count), 256, 0, s>>>(P.groups, sb.outside_flag, reinterpret_cast<const float4*>(slabs),
+                                                         reinterpret_cast<float4*>(grad), rps, F, N, slice_begin);
+    return 2;
 }

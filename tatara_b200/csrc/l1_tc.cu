@@ -20,7 +20,7 @@
 
 #define TC_POS 128   // positions per block = rows of the accumulator tile
 #define TC_KC 32     // fp32 elements per stage along K: four MMAs of K = 8
-#define TC_STAGES 4
+#define TC_STAGES 3
 #define TC_WAIT_LIMIT (1 << 18)
 
 namespace {

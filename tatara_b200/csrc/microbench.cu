@@ -61,6 +61,7 @@ extern "C" int tb_ft_microbench(int device, const int32_t* indices, const int32_
     int *d_idx = nullptr, *d_nnz = nullptr, *d_cnt = nullptr, *d_off = nullptr, *d_cur = nullptr, *d_lists = nullptr, *d_plan = nullptr;
     int *d_order = nullptr, *d_ntiles = nullptr, *d_seg = nullptr, *d_hist = nullptr, *d_items = nullptr, *d_itemseg = nullptr;
     int *d_fwd_work = nullptr, *d_bwd_work = nullptr;
+    float* d_slabs = nullptr;
     TileDesc* d_tiles = nullptr;
     Timer tm;
     int rc = TB_OK;
@@ -114,6 +115,7 @@ extern "C" int tb_ft_microbench(int device, const int32_t* indices, const int32_
         MB(cudaMalloc(&d_items, B * 4)); MB(cudaMalloc(&d_itemseg, 130 * 4));
         MB(cudaMalloc(&d_fwd_work, ft_forward_slice_work_ints(batch, n_keys, max_active) * 4));
         MB(cudaMalloc(&d_bwd_work, ft_backward_slice_ints(batch, max_active, rps) * 4));
+        MB(cudaMalloc(&d_slabs, ft_backward_slice_slab_floats(batch, max_active, rps, ft_out) * 4));
         k_fill_pattern<<<148 * 8, 256>>>(d_table, N * F, 0.05f, 1u);
         MB(tm.run(iters, [&] {
             launch_step_sorts(0, nullptr, batch, 0, d_order, d_tiles, d_ntiles, d_seg, max_tiles, d_idx, d_idx, d_nnz, max_active, ft_in, rps, 1,
@@ -128,7 +130,7 @@ extern "C" int tb_ft_microbench(int device, const int32_t* indices, const int32_
             k_fill_pattern<<<148 * 8, 256>>>(d_x, B * F, 1e-3f, 3u);
             MB(tm.run(iters, [&] {
                 launch_inverse_slice(0, d_itemseg, d_fwd_work, d_bwd_work, batch, max_active, ft_in, rps, 1);
-                launch_ft_backward_slice(0, d_x, d_x, d_fwd_work, d_bwd_work, batch, max_active, ft_in, ft_out, rps, 1, 0, ceil_div(ft_in, rps), d_grad);
+                launch_ft_backward_slice(0, d_x, d_x, d_fwd_work, d_bwd_work, batch, max_active, ft_in, ft_out, rps, 1, 0, ceil_div(ft_in, rps), d_grad, d_slabs);
             }));
             out->bwd_slice_ms = (float)(tm.total / iters);
         }
@@ -136,7 +138,7 @@ extern "C" int tb_ft_microbench(int device, const int32_t* indices, const int32_
 done:
     cudaFree(d_table); cudaFree(d_x); cudaFree(d_grad); cudaFree(d_m); cudaFree(d_v); cudaFree(d_part); cudaFree(d_idx); cudaFree(d_nnz);
     cudaFree(d_cnt); cudaFree(d_off); cudaFree(d_cur); cudaFree(d_lists); cudaFree(d_plan); cudaFree(d_order); cudaFree(d_ntiles);
-    cudaFree(d_seg); cudaFree(d_hist); cudaFree(d_items); cudaFree(d_itemseg); cudaFree(d_fwd_work); cudaFree(d_bwd_work); cudaFree(d_tiles);
+    cudaFree(d_seg); cudaFree(d_hist); cudaFree(d_items); cudaFree(d_itemseg); cudaFree(d_fwd_work); cudaFree(d_bwd_work); cudaFree(d_tiles); cudaFree(d_slabs);
     cudaFree(tm.flush);
     if (tm.e0) cudaEventDestroy(tm.e0);
     if (tm.e1) cudaEventDestroy(tm.e1);

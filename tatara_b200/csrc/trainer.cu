@@ -170,6 +170,7 @@ struct tb_trainer {
     bool slice_fwd = false;  // this step's forward ran slice-resident (its row codes are in fwd_work)
     bool poisoned = false;   // a step failed after its optimizer had begun: parameters are part old, part new
     float* bwd_partial = nullptr;
+    float* bwd_slabs = nullptr;  // partial gradient slabs of slices that several blocks share (ft_slice_bwd.cu)
     int last_n = 0;
     // loss ring (AsyncLossRing, trainer_common.rs:909-1000)
     double* loss_pinned[2] = {nullptr, nullptr};
@@ -480,7 +481,7 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
               // equal parts: a smaller last part cost more than it hid
               const int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
               n += launch_ft_backward_slice(t->stream, dft0, dft1, t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
-                                            t->groups[0].grad, t->p_out16);
+                                            t->groups[0].grad, t->bwd_slabs, t->p_out16);
               if (!pipeline) continue;
               CU(t, cudaEventRecord(t->ev_part[part], t->stream));
               CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_part[part], 0));
@@ -751,7 +752,7 @@ void free_all(tb_trainer* t) {
     cudaFree(t->order); cudaFree(t->n_tiles); cudaFree(t->seg_start); cudaFree(t->tiles);
     cudaFree(t->small_partials); cudaFree(t->l1w_partials); cudaFree(t->bias_partials); cudaFree(t->l1_weff);
     cudaFree(t->feat_counts); cudaFree(t->feat_offsets); cudaFree(t->feat_cursor); cudaFree(t->feat_lists);
-    cudaFree(t->fwd_work); cudaFree(t->bwd_slice); cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial);
+    cudaFree(t->fwd_work); cudaFree(t->bwd_slice); cudaFree(t->sort_hist); cudaFree(t->items); cudaFree(t->item_seg); cudaFree(t->bwd_plan); cudaFree(t->bwd_partial); cudaFree(t->bwd_slabs);
     if (t->ev_t0) cudaEventDestroy(t->ev_t0);
     if (t->ev_t1) cudaEventDestroy(t->ev_t1);
     for (int i = 0; i < PH_COUNT; ++i) {
@@ -894,7 +895,10 @@ int create_impl(tb_trainer* t) {
     {
         const int rps = c.piece_inputs > 0 ? c.piece_inputs : (int)N;
         if (ft_forward_slice_supported((int)F, (int)N, (int)A, rps) && ft_backward_slice_supported((int)F, (int)N, (int)A, rps))
+        {
             CU(t, dalloc(&t->bwd_slice, ft_backward_slice_ints((int)(2 * B), (int)A, rps)));
+            CU(t, cudaMalloc((void**)&t->bwd_slabs, ft_backward_slice_slab_floats((int)(2 * B), (int)A, rps, (int)F) * sizeof(float)));
+        }
     }
     {
         const size_t max_work = (size_t)ft_backward_max_work((int)B, (int)A, 2);
