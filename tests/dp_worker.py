@@ -94,11 +94,31 @@ def main():
         assert tr.step_count == 6 == ref.step_count
         for n in ref.names:
             assert_close(tr.download_group(n)["w"], ref.group(n), 1e-4, "weights after 6 steps " + n)
+        first = {}
         for n in ref.names:
-            w = torch.from_numpy(tr.download_group(n)["w"])
+            first[n] = tr.download_group(n, which=("w", "m", "v", "slow"))
+            w = torch.from_numpy(first[n]["w"])
             w0 = w.clone()
             dist.broadcast(w0, src=0)
             assert torch.equal(w, w0), "replicas diverged in " + n
+        dist.barrier()
+        tr.close()
+        dist.barrier()
+        # run to run: a second communicator and trainer, the same six steps: weights and optimizer state bit for bit
+        ids = [tb.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=int(os.environ["LOCAL_RANK"]),
+                           world_size=world, rank=rank, nccl_id=ids[0])
+        tr.forward_backward(batch, 0.0, tb.LossKind.sigmoid())
+        tr.apply_optimizer(LR)
+        for s in range(5):
+            tr.train_step(batch, LR, 0.0, tb.LossKind.sigmoid())
+        tr.flush_pending_loss()
+        for n in ref.names:
+            grp = tr.download_group(n, which=("w", "m", "v", "slow"))
+            for k, v in first[n].items():
+                assert np.array_equal(grp[k], v), "second run differs in %s.%s" % (n, k)
+        dist.barrier()
         tr.close()
     dist.barrier()
     if rank == 0:
