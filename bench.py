@@ -154,9 +154,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def make_trainer(tb, w, device, world, rank, nccl_id, capacity=BATCH, precision=None):
+NCCL_ENV = {"NCCL_NVLS_ENABLE": "0", "NCCL_ALGO": "Ring", "NCCL_PROTO": "Simple"}
+
+
+def make_trainer(tb, w, device, world, rank, nccl_id, capacity=BATCH, precision=None, nccl_ctas=0):
     fs = tb.FEATURE_SETS[w["fs"]]
     kw = {} if precision is None else {"precision": precision}
+    if nccl_ctas:
+        kw["nccl_ctas"] = nccl_ctas
     if w["arch"] == "layerstack":
         tr = tb.GpuTrainer(capacity, w["F"], w["l1"], w["l2"], w["nb"], fs, optimizer=w["optimizer"], device=device,
                            world_size=world, rank=rank, nccl_id=nccl_id, **kw)
@@ -457,6 +462,7 @@ def main():
     ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
     ap.add_argument("--trace", action="store_true", help="progress lines on stderr")
+    ap.add_argument("--nccl-ctas", type=int, default=0, help="fixed CTA (channel) count of the library's communicator; 0: NCCL chooses")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -498,6 +504,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # This application's NCCL settings (the library sets none): one algorithm and protocol, so that the order in which
+        # the gradient sum is formed is fixed; NVLS off because the all-reduce runs next to a kernel that holds every SM.
+        for k, v in NCCL_ENV.items():
+            os.environ.setdefault(k, v)
         dist.init_process_group(backend="gloo", rank=rank, world_size=world)
         ids = [tb.nccl_unique_id() if rank == 0 else None, tb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
@@ -515,7 +525,7 @@ def main():
             sys.exit(1)
     all_optim = args.precision == "all-optim"
     prec = tb.PrecisionFlags(tf32=True, ft_fp16=True, ft_fp16_out=True, fp16_opt_state=True) if all_optim else None
-    tr, loss, fs = make_trainer(tb, w, device, world, rank, nccl_id, capacity=B, precision=prec)
+    tr, loss, fs = make_trainer(tb, w, device, world, rank, nccl_id, capacity=B, precision=prec, nccl_ctas=args.nccl_ctas)
     n_batches = 3
     seed0 = SYNTH_SEED + CONFIG_INDEX[args.workload] + 7919 * rank
     psvs = [tb.synthesize_psv(seed0 + 104729 * i, B) for i in range(n_batches)]
@@ -656,6 +666,7 @@ def main():
             "kernels_ms": {k: round(v, 4) for k, v in phases.items()},
         }
         if world > 1:
+            line["config"]["nccl"] = dict({k: os.environ.get(k) for k in NCCL_ENV}, ctas=args.nccl_ctas or "NCCL's choice")
             line["dp_parity"] = "ok" if dp_ok else "failed"
             line["replicas_identical"] = bool(same and dp_same_small)
         if world == 1:

@@ -77,6 +77,10 @@ typedef struct tb_config {
     int32_t world_size;     /* data-parallel ranks (1 = single GPU, NCCL not loaded) */
     int32_t rank;
     uint8_t nccl_unique_id[128]; /* from tb_nccl_unique_id() on rank 0, same bytes on every rank */
+    int32_t nccl_ctas;      /* > 0: this handle's communicator is created by ncclCommInitRankConfig with minCTAs = maxCTAs =
+                               this value (a fixed channel count); 0: ncclCommInitRank, NCCL chooses.  Algorithm, protocol and
+                               NVLS have no per-communicator setting in NCCL: they are the application's NCCL_ALGO, NCCL_PROTO
+                               and NCCL_NVLS_ENABLE, which this library neither sets nor changes. */
 } tb_config;
 
 /* nnue_train::trainer::LossKind, crates/nnue-train/src/trainer.rs:75-95 */

@@ -13,6 +13,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <climits>
 #include <string>
 #include <vector>
 
@@ -58,6 +59,7 @@ struct NcclApi {
     void* lib = nullptr;
     int (*GetUniqueId)(void*) = nullptr;
     int (*CommInitRank)(void**, int, Uid, int) = nullptr;
+    int (*CommInitRankConfig)(void**, int, Uid, int, void*) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
@@ -68,10 +70,10 @@ NcclApi g_nccl;
 
 bool load_nccl(std::string* err) {
     if (g_nccl.lib) return true;
-    // The all-reduces of this library run next to kernels that hold every SM (one block per SM of the FT weight gradient).
-    // Measured on eight B200s, 460 MB in five parts behind that kernel: 5.32 ms per step with NCCL's NVLS algorithm, 5.11 ms
-    // with it switched off (its ranks' blocks wait for one another while they wait for SMs).  A value set by the caller wins.
-    setenv("NCCL_NVLS_ENABLE", "0", 0);
+    // NCCL's environment belongs to the application: nothing is set here.  (The all-reduces of this library run next to
+    // kernels that hold every SM; on eight B200s, 460 MB in five parts behind the FT weight gradient, a step measured 5.32 ms
+    // with NCCL's NVLS algorithm and 5.11 ms with NCCL_NVLS_ENABLE=0, so the benchmark sets that, and a fixed NCCL_ALGO /
+    // NCCL_PROTO, itself.)
     const char* names[] = {getenv("TATARA_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
     for (const char* n : names) {
         if (!n || !*n) continue;
@@ -82,6 +84,7 @@ bool load_nccl(std::string* err) {
 #define SYM(field, name) *(void**)(&g_nccl.field) = dlsym(g_nccl.lib, name); if (!g_nccl.field) { *err = std::string("missing symbol ") + name; g_nccl.lib = nullptr; return false; }
     SYM(GetUniqueId, "ncclGetUniqueId")
     SYM(CommInitRank, "ncclCommInitRank")
+    SYM(CommInitRankConfig, "ncclCommInitRankConfig")
     SYM(AllReduce, "ncclAllReduce")
     SYM(CommDestroy, "ncclCommDestroy")
     SYM(GetErrorString, "ncclGetErrorString")
@@ -915,8 +918,18 @@ int create_impl(tb_trainer* t) {
         if (!load_nccl(&e)) return fail(t, TB_ERR_NCCL, "%s", e.c_str());
         Uid id;
         memcpy(id.internal, c.nccl_unique_id, 128);
-        const int rc = g_nccl.CommInitRank(&t->comm, c.world_size, id, c.rank);
-        if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(rc));
+        int rc;
+        if (c.nccl_ctas > 0) {
+            // ncclConfig_t as NCCL 2.17 declares it (later versions only append fields, and the library reads `size` bytes
+            // and takes its defaults for the rest): a fixed number of CTAs = channels for this communicator alone
+            struct { size_t size; unsigned magic, version; int blocking, cga_cluster_size, min_ctas, max_ctas; const char* net_name; } nc;
+            nc.size = sizeof(nc); nc.magic = 0xcafebeefu; nc.version = 21700;
+            nc.blocking = INT_MIN; nc.cga_cluster_size = INT_MIN; nc.min_ctas = nc.max_ctas = c.nccl_ctas; nc.net_name = nullptr;
+            rc = g_nccl.CommInitRankConfig(&t->comm, c.world_size, id, c.rank, &nc);
+        } else {
+            rc = g_nccl.CommInitRank(&t->comm, c.world_size, id, c.rank);
+        }
+        if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclCommInitRank%s: %s", c.nccl_ctas > 0 ? "Config" : "", g_nccl.GetErrorString(rc));
         {   // highest priority: when an SM frees up, the waiting all-reduce gets it before the next gradient block does
             int lo = 0, hi = 0;
             CU(t, cudaDeviceGetStreamPriorityRange(&lo, &hi));

@@ -38,6 +38,8 @@ def main():
     mode = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    for k, v in (("NCCL_NVLS_ENABLE", "0"), ("NCCL_ALGO", "Ring"), ("NCCL_PROTO", "Simple")):   # a fixed summation order
+        os.environ.setdefault(k, v)
     dist.init_process_group(backend="gloo", rank=rank, world_size=world)
     fs = tb.FEATURE_SETS["halfka-hm-merged"]
     init = tb.layerstack_default_init(fs, F, L1, L2, NB)
@@ -75,8 +77,9 @@ def main():
     else:
         ids = [tb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
+        # communicators with a fixed channel count (ncclCommInitRankConfig); the benchmark covers ncclCommInitRank
         tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=int(os.environ["LOCAL_RANK"]),
-                           world_size=world, rank=rank, nccl_id=ids[0])
+                           world_size=world, rank=rank, nccl_id=ids[0], nccl_ctas=8)
         batch = tb.BatchData(mine["stm"], mine["nstm"], mine["nnz"], mine["score"], mine["wdl"], mine["bucket"])
         loss = tr.forward_backward(batch, 0.0, tb.LossKind.sigmoid())
         assert abs(loss - ref_loss) <= 1e-5 * (1 + abs(ref_loss)), (loss, ref_loss)    # the all-reduced loss
@@ -108,7 +111,7 @@ def main():
         ids = [tb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=int(os.environ["LOCAL_RANK"]),
-                           world_size=world, rank=rank, nccl_id=ids[0])
+                           world_size=world, rank=rank, nccl_id=ids[0], nccl_ctas=8)
         tr.forward_backward(batch, 0.0, tb.LossKind.sigmoid())
         tr.apply_optimizer(LR)
         for s in range(5):

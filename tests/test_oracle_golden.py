@@ -107,6 +107,29 @@ def test_factorizer_fold_and_reduce_equal_virtual_index_semantics():
     np.testing.assert_allclose(g1, g2, rtol=0, atol=1e-6)
 
 
+def test_factorizer_fold_and_reduce_cell_by_cell():
+    # crates/gpu-kernels/src/sparse/ft_factorize.rs: fold_adds_matching_virtual_row, reduce_sums_over_king_buckets
+    L = lib()
+    FT_IN, FT_OUT, PI = 6, 4, 2
+    rows = FT_IN + PI
+    w = A([((i * 37 % 101) - 50.0) * 0.013 for i in range(rows * FT_OUT)])
+    comb = np.zeros(FT_IN * FT_OUT, f32)
+    L.ora_ft_fold_virtual(w, comb, FT_IN, FT_OUT, PI)
+    for feat in range(FT_IN):
+        for ri in range(FT_OUT):
+            assert comb[feat * FT_OUT + ri] == w[feat * FT_OUT + ri] + w[(FT_IN + feat % PI) * FT_OUT + ri]
+    grad = A([float(i) for i in range(rows * FT_OUT)])
+    real = grad[:FT_IN * FT_OUT].copy()
+    L.ora_ft_reduce_virtual_grad(grad, FT_IN, FT_OUT, PI)
+    assert np.array_equal(grad[:FT_IN * FT_OUT], real)                      # the real block is untouched
+    for p in range(PI):
+        for ri in range(FT_OUT):
+            want = f32(0)
+            for kb in range(FT_IN // PI):
+                want = f32(want + f32((kb * PI + p) * FT_OUT + ri))
+            assert grad[(FT_IN + p) * FT_OUT + ri] == want
+
+
 # ---------------------------------------------------------------- pairwise FT post
 SCALE = f32(127.0) / f32(128.0)
 
@@ -391,6 +414,32 @@ def test_ranger_lerp_literals():
     w = A([2, -4, 0]); s = A([4, 4, 10])
     L.ora_ranger_lookahead_lerp(w, s, 0.5, 3)
     assert w.tolist() == [3, 0, 5] and s.tolist() == [3, 0, 5]
+
+
+def test_composed_ranger_step_lerps_only_every_kth_step():
+    # crates/gpu-kernels/src/pointwise/ranger_step.rs: step_cpu_invokes_lerp_only_at_k_step, restated on the composed
+    # optimizer of the oracle's trainer (RangerParams::DEFAULT: k = 6, alpha = 0.5; slow weights start at 0): steps 1..5
+    # leave slow untouched, step 6 synchronises weights and slow and pulls the weights towards slow = 0
+    import oracle_lib as O
+    ot = O.OracleTrainer(arch="simple", ft_in=8, piece_inputs=4, factorize=False, max_active=2, ft_out=128, l1=8, l2=8,
+                         optimizer="ranger", wd=(0.0, 0.0, 0.0), capacity=16)
+    names = list(ot.names)
+    for n in names:
+        ot.group(n)[:] = 1.0
+    before = None
+    for step in range(1, 7):
+        for n in names:
+            ot.group(n, "grad")[:] = 0.1 if step == 1 else 0.0   # (the reference's kernel zeroes the gradient itself)
+        if step == 6:
+            before = {n: ot.group(n).copy() for n in names}
+        ot.apply_optimizer(0.1)
+        assert ot.step_count == step
+        for n in names:
+            if step < 6:
+                assert not ot.group(n, "slow").any(), (n, step)
+            else:
+                assert np.array_equal(ot.group(n), ot.group(n, "slow")), n
+                assert (np.abs(ot.group(n)) < np.abs(before[n])).all(), n
 
 
 # ---------------------------------------------------------------- init
