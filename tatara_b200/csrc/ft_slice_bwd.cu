@@ -320,9 +320,15 @@ __global__ void __launch_bounds__(1024, 1) k_ft_backward_slice(const void* __res
     if (*outside_flag) return;
     // the groups of this launch's slices; the grid has a block row per slice, so a block takes a second group only when
     // some slice is shared (skewed data)
-    const int g_lo = groups[4 + slice_begin], g_hi = groups[4 + slice_begin + slice_count];
-    for (int gid = g_lo + (int)blockIdx.x; gid < g_hi; gid += (int)gridDim.x) {
-    __syncthreads();  // the previous group's last reads of the shared buffers
+    // (the loop's state lives in shared memory: the body needs every register)
+    __shared__ int s_gid;
+    if (threadIdx.x == 0) s_gid = groups[4 + slice_begin] + (int)blockIdx.x;
+    for (;;) {
+    __syncthreads();  // s_gid written; the previous group's last reads of the shared buffers
+    const int gid = s_gid;
+    if (gid >= groups[4 + slice_begin + slice_count]) break;
+    __syncthreads();  // every thread has read s_gid
+    if (threadIdx.x == 0) s_gid = gid + (int)gridDim.x;
     const int4 gr = reinterpret_cast<const int4*>(groups + 4 + SORT_KEYS_LIMIT + 4)[gid];
     const int k = gr.x, strip = blockIdx.y;
     const int row0 = k * rps;
