@@ -157,11 +157,13 @@ class ClockSampler:
 NCCL_ENV = {"NCCL_NVLS_ENABLE": "0", "NCCL_ALGO": "Ring", "NCCL_PROTO": "Simple"}
 
 
-def make_trainer(tb, w, device, world, rank, nccl_id, capacity=BATCH, precision=None, nccl_ctas=0):
+def make_trainer(tb, w, device, world, rank, nccl_id, capacity=BATCH, precision=None, nccl_ctas=0, dp_exchange="nccl"):
     fs = tb.FEATURE_SETS[w["fs"]]
     kw = {} if precision is None else {"precision": precision}
     if nccl_ctas:
         kw["nccl_ctas"] = nccl_ctas
+    if world > 1:
+        kw["dp_exchange"] = dp_exchange
     if w["arch"] == "layerstack":
         tr = tb.GpuTrainer(capacity, w["F"], w["l1"], w["l2"], w["nb"], fs, optimizer=w["optimizer"], device=device,
                            world_size=world, rank=rank, nccl_id=nccl_id, **kw)
@@ -331,7 +333,7 @@ def run_reference_gpu_kernels(iters=5):
 
 
 # ---------------------------------------------------------------------------------------------- data-parallel self check
-def dp_parity_check(tb, dist, device, world, rank, nccl_id):
+def dp_parity_check(tb, dist, device, world, rank, nccl_id, dp_exchange):
     """Before the timed region at N > 1: six pipelined data-parallel steps on a small LayerStack shape against the CPU
     oracle stepping on the concatenated batch (the check of tests/dp_worker.py), then bitwise equality of the replicas."""
     import torch
@@ -343,7 +345,8 @@ def dp_parity_check(tb, dist, device, world, rank, nccl_id):
     init["ft_w"][:fs.ft_in * F] *= 30.0
     shards = [O.psv_to_batch(fs.name, O.synthesize_psv(SYNTH_SEED + 7919 * r, B).tobytes()) for r in range(world)]
     mine = shards[rank]
-    tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=device, world_size=world, rank=rank, nccl_id=nccl_id)
+    tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=device, world_size=world, rank=rank, nccl_id=nccl_id,
+                       dp_exchange=dp_exchange)
     batch = tb.BatchData(mine["stm"], mine["nstm"], mine["nnz"], mine["score"], mine["wdl"], mine["bucket"])
     if os.environ.get("TB_BENCH_TRACE"):
         print("[dp check rank %d] trainer created" % rank, file=sys.stderr, flush=True)
@@ -462,6 +465,8 @@ def main():
     ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
     ap.add_argument("--trace", action="store_true", help="progress lines on stderr")
+    ap.add_argument("--dp-exchange", default="peer-copy", choices=["nccl", "peer-copy"],
+                    help="how the gradient parts are summed over the ranks: ncclAllReduce, or copy engines over peer mappings")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="fixed CTA (channel) count of the library's communicator; 0: NCCL chooses")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -517,7 +522,7 @@ def main():
     dp_ok = dp_same_small = None
     trace("rendezvous done")
     if world > 1:
-        dp_ok, dp_same_small = dp_parity_check(tb, dist, device, world, rank, ids[1])
+        dp_ok, dp_same_small = dp_parity_check(tb, dist, device, world, rank, ids[1], args.dp_exchange)
         trace("dp self check done: %s %s" % (dp_ok, dp_same_small))
         if not (dp_ok and dp_same_small):
             if rank == 0:
@@ -525,7 +530,7 @@ def main():
             sys.exit(1)
     all_optim = args.precision == "all-optim"
     prec = tb.PrecisionFlags(tf32=True, ft_fp16=True, ft_fp16_out=True, fp16_opt_state=True) if all_optim else None
-    tr, loss, fs = make_trainer(tb, w, device, world, rank, nccl_id, capacity=B, precision=prec, nccl_ctas=args.nccl_ctas)
+    tr, loss, fs = make_trainer(tb, w, device, world, rank, nccl_id, capacity=B, precision=prec, nccl_ctas=args.nccl_ctas, dp_exchange=args.dp_exchange)
     n_batches = 3
     seed0 = SYNTH_SEED + CONFIG_INDEX[args.workload] + 7919 * rank
     psvs = [tb.synthesize_psv(seed0 + 104729 * i, B) for i in range(n_batches)]
@@ -666,6 +671,7 @@ def main():
             "kernels_ms": {k: round(v, 4) for k, v in phases.items()},
         }
         if world > 1:
+            line["config"]["dp_exchange"] = args.dp_exchange
             line["config"]["nccl"] = dict({k: os.environ.get(k) for k in NCCL_ENV}, ctas=args.nccl_ctas or "NCCL's choice")
             line["dp_parity"] = "ok" if dp_ok else "failed"
             line["replicas_identical"] = bool(same and dp_same_small)

@@ -37,6 +37,7 @@ extern "C" {
 #define TB_ERR_UNSUPPORTED (-4)
 #define TB_ERR_NCCL (-5)
 #define TB_ERR_NO_DEVICE (-6)
+#define TB_ERR_TIMEOUT (-7) /* a data-parallel step did not finish within the deadline: a peer is gone; the handle is poisoned */
 
 enum { TB_ARCH_LAYERSTACK = 0, TB_ARCH_SIMPLE = 1 };
 /* SimpleActivation (bins/nnue_train/src/trainer_simple.rs): Pairwise is the FT-output pairwise product of the LayerStack
@@ -56,6 +57,9 @@ typedef struct tb_trainer tb_trainer;
  * (bins/nnue_train/src/trainer_simple.rs:392-402).  The feature set is passed by its
  * dimensions (crates/shogi-features/src/feature_set.rs:1031-1038) instead of by name.
  */
+#define TB_DP_NCCL 0
+#define TB_DP_PEER_COPY 1
+
 typedef struct tb_config {
     int32_t struct_size;    /* sizeof(tb_config) of the caller */
     int32_t device;         /* CUDA device ordinal */
@@ -81,6 +85,10 @@ typedef struct tb_config {
                                this value (a fixed channel count); 0: ncclCommInitRank, NCCL chooses.  Algorithm, protocol and
                                NVLS have no per-communicator setting in NCCL: they are the application's NCCL_ALGO, NCCL_PROTO
                                and NCCL_NVLS_ENABLE, which this library neither sets nor changes. */
+    int32_t dp_exchange;    /* TB_DP_NCCL (0): the gradient parts are summed by ncclAllReduce.  TB_DP_PEER_COPY (1): ranks of
+                               one node, one process each: reduce-scatter and all-gather by the copy engines over peer
+                               mappings (CUDA IPC) with stream memory operations as signals and a small summing kernel in
+                               rank order; NCCL then only carries the start-up handshake and batches off the fast path */
 } tb_config;
 
 /* nnue_train::trainer::LossKind, crates/nnue-train/src/trainer.rs:75-95 */

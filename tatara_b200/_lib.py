@@ -30,7 +30,7 @@ class Config(C.Structure):
         ("piece_inputs", i32), ("ft_factorize", i32), ("max_active", i32), ("ft_out", i32), ("l1_out", i32),
         ("l2_out", i32), ("num_buckets", i32), ("activation", i32), ("optimizer", i32), ("precision", i32),
         ("wd_ft", f), ("wd_dense", f), ("wd_bias", f), ("lr_mult_ft", f), ("lr_mult_dense", f), ("lr_mult_bias", f),
-        ("world_size", i32), ("rank", i32), ("nccl_unique_id", C.c_uint8 * 128), ("nccl_ctas", i32),
+        ("world_size", i32), ("rank", i32), ("nccl_unique_id", C.c_uint8 * 128), ("nccl_ctas", i32), ("dp_exchange", i32),
     ]
 
 

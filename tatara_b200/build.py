@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libtatara_b200.so")
-SOURCES = ["ft_kernels.cu", "ft_slice_bwd.cu", "sort_kernels.cu", "dense_kernels.cu", "opt_kernels.cu", "psv.cu", "host_util.cu", "trainer.cu", "noalloc.cu", "microbench.cu", "l1_tc.cu"]
+SOURCES = ["ft_kernels.cu", "ft_slice_bwd.cu", "sort_kernels.cu", "dense_kernels.cu", "opt_kernels.cu", "psv.cu", "host_util.cu", "trainer.cu", "noalloc.cu", "microbench.cu", "l1_tc.cu", "peer_exchange.cu"]
 # every object depends on every header: csrc/*.cuh and the public C header
 HEADERS = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [
     os.path.join(os.path.dirname(HERE), "include", "tatara_b200.h")]

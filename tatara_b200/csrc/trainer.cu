@@ -3,6 +3,7 @@
 // copy stream).  Mirrors GpuTrainer (bins/nnue_train/src/trainer_layerstack.rs) and SimpleGpuTrainer
 // (bins/nnue_train/src/trainer_simple.rs) at the level of the TrainerBackend trait.
 #include "common.cuh"
+#include "peer_exchange.cuh"
 #include "../../include/tatara_b200.h"
 
 #include <cuda_fp16.h>
@@ -13,8 +14,10 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <chrono>
 #include <climits>
 #include <string>
+#include <thread>
 #include <vector>
 
 #define FT_POST_SCALE (127.0f / 128.0f)  // bins/nnue_train/src/arch.rs:64-70
@@ -27,15 +30,17 @@
 #define N_SMA_THRESHOLD 5.0f
 #define FT_DFT_FP16_BASE_SCALE 16384.0f  // arch.rs:72-93: the fp16 dft rows carry gradient * 2^14 * batch
 #define DGRAD_CTAS (148 * 2)
-#define AR_PARTS_MAX 6
+#define AR_PARTS_MAX 9
+#define PEER_DEADLINE_S 120  // peer exchange: longest wait for a step before the peers are given up
 // Number of launches the FT weight gradient is cut into in data-parallel runs (each part's all-reduce and row updates
 // overlap the next part).  A part runs slices x strips blocks of one per SM: the count that wastes the fewest block
 // slots wins, a shorter last part (whose communication nothing hides) breaking near ties.  Measured on two B200s at
 // 45 slices x 48 strips: 5 parts 4.81 ms per step, 3 parts 4.97, 4 parts 4.99, 6 parts 4.95, 8 parts 5.05.
 static int ar_parts_for(int n_slices, int strips, int n_sm) {
+    if (const char* dbg = getenv("TATARA_DBG_PARTS")) { const int v = atoi(dbg); if (v >= 2 && v <= AR_PARTS_MAX) return v; }
     int best = 1;
     double best_cost = 1e30;
-    for (int parts = 3; parts <= AR_PARTS_MAX; ++parts) {
+    for (int parts = 3; parts <= 6; ++parts) {
         if (n_slices < 2 * parts) break;
         double waves = 0, last = 0;
         for (int p = 0; p < parts; ++p) {
@@ -61,6 +66,7 @@ struct NcclApi {
     int (*CommInitRank)(void**, int, Uid, int) = nullptr;
     int (*CommInitRankConfig)(void**, int, Uid, int, void*) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     int (*GroupStart)() = nullptr;
@@ -86,6 +92,7 @@ bool load_nccl(std::string* err) {
     SYM(CommInitRank, "ncclCommInitRank")
     SYM(CommInitRankConfig, "ncclCommInitRankConfig")
     SYM(AllReduce, "ncclAllReduce")
+    SYM(AllGather, "ncclAllGather")
     SYM(CommDestroy, "ncclCommDestroy")
     SYM(GetErrorString, "ncclGetErrorString")
     SYM(GroupStart, "ncclGroupStart")
@@ -190,6 +197,7 @@ struct tb_trainer {
     int64_t launches = 0;
     // data parallel
     void* comm = nullptr;
+    PeerExchange* px = nullptr;  // TB_DP_PEER_COPY
 };
 
 namespace {
@@ -211,6 +219,20 @@ cudaError_t dalloc(T** p, size_t n) {
     cudaError_t e = cudaMalloc((void**)p, (n ? n : 1) * sizeof(T));
     if (e == cudaSuccess) e = cudaMemset(*p, 0, (n ? n : 1) * sizeof(T));
     return e;
+}
+
+// start-up handshake of the peer exchange: `bytes` bytes per rank between host buffers, through NCCL
+int nccl_host_allgather(void* ctx, const void* send, void* recv, size_t bytes) {
+    tb_trainer* t = static_cast<tb_trainer*>(ctx);
+    unsigned char *ds = nullptr, *dr = nullptr;
+    int rc = -1;
+    if (cudaMalloc((void**)&ds, bytes) == cudaSuccess && cudaMalloc((void**)&dr, bytes * t->cfg.world_size) == cudaSuccess &&
+        cudaMemcpy(ds, send, bytes, cudaMemcpyHostToDevice) == cudaSuccess &&
+        g_nccl.AllGather(ds, dr, bytes, /*ncclUint8*/ 1, t->comm, t->stream) == 0 && cudaStreamSynchronize(t->stream) == cudaSuccess &&
+        cudaMemcpy(recv, dr, bytes * t->cfg.world_size, cudaMemcpyDeviceToHost) == cudaSuccess)
+        rc = 0;
+    cudaFree(ds); cudaFree(dr);
+    return rc;
 }
 
 Group* find_group(tb_trainer* t, const char* name) {
@@ -476,13 +498,22 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
           // first part, the loss with the last).  Whichever path wrote the rows (the gated generic kernels come first), they
           // are final when the part's event is recorded.
           const int n_slices = (N + rps - 1) / rps;
-          const int parts = c.world_size > 1 ? ar_parts_for(n_slices, F / 32, t->n_sm) : 1;
+          int parts = c.world_size > 1 ? ar_parts_for(n_slices, F / 32, t->n_sm) : 1;
+          int dbg_bounds[AR_PARTS_MAX] = {};
+          if (const char* dbg = getenv("TATARA_DBG_BOUNDS")) {
+              if (c.world_size > 1) {
+                  int np = 0; const char* q = dbg;
+                  while (*q && np < AR_PARTS_MAX) { dbg_bounds[np++] = atoi(q); while (*q && *q != ',') ++q; if (*q == ',') ++q; }
+                  if (np >= 2 && dbg_bounds[np - 1] == n_slices) parts = np; else dbg_bounds[0] = 0;
+              }
+          }
           const bool pipeline = parts > 1;
           const int64_t ft_off = t->groups[0].grad - t->grad_arena;
           int rc = 0;
           for (int part = 0; part < parts; ++part) {
               // equal parts: a smaller last part cost more than it hid
-              const int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
+              int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
+              if (dbg_bounds[0] > 0) { k0 = part == 0 ? 0 : dbg_bounds[part - 1]; k1 = dbg_bounds[part]; }
               n += launch_ft_backward_slice(t->stream, dft0, dft1, t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
                                             t->groups[0].grad, t->bwd_slabs, t->p_out16);
               if (!pipeline) continue;
@@ -490,12 +521,21 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
               CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_part[part], 0));
               const int64_t e0 = part == 0 ? 0 : ft_off + (int64_t)(k0 * rps < N ? k0 * rps : N) * F;
               const int64_t e1 = ft_off + (int64_t)(k1 * rps < N ? k1 * rps : N) * F;
-              if (rc == 0) rc = g_nccl.GroupStart();
-              if (rc == 0) rc = g_nccl.AllReduce(t->grad_arena + e0, t->grad_arena + e0, (size_t)(e1 - e0), /*ncclFloat*/ 7, /*ncclSum*/ 0, t->comm, t->comm_stream);
-              if (rc == 0 && part == parts - 1) rc = g_nccl.AllReduce(t->loss_acc, t->loss_acc, 1, /*ncclDouble*/ 8, 0, t->comm, t->comm_stream);
-              const int rc2 = g_nccl.GroupEnd();
-              if (rc == 0) rc = rc2;
-              if (rc == 0 && lr >= 0.0f) {
+              if (t->px) {
+                  // copy engines and peer mappings: the reduce kernel on the communication stream, the consumer's waits on
+                  // the optimizer stream
+                  if (part == 0) px_begin_step(t->px);
+                  std::string e;
+                  if (px_exchange_part(t->px, part, e0, e1, part == parts - 1, t->ev_part[part], t->comm_stream, t->opt_stream, &n, &e) != 0)
+                      return fail(t, TB_ERR_CUDA, "%s", e.c_str());
+              } else {
+                  if (rc == 0) rc = g_nccl.GroupStart();
+                  if (rc == 0) rc = g_nccl.AllReduce(t->grad_arena + e0, t->grad_arena + e0, (size_t)(e1 - e0), /*ncclFloat*/ 7, /*ncclSum*/ 0, t->comm, t->comm_stream);
+                  if (rc == 0 && part == parts - 1) rc = g_nccl.AllReduce(t->loss_acc, t->loss_acc, 1, /*ncclDouble*/ 8, 0, t->comm, t->comm_stream);
+                  const int rc2 = g_nccl.GroupEnd();
+                  if (rc == 0) rc = rc2;
+              }
+              if (rc == 0 && lr >= 0.0f && !getenv("TATARA_DBG_NO_ROWS_OPT")) {
                   // consumer side of the pipeline: the optimizer of this part's real rows follows its all-reduce on the
                   // same stream, next to the gradient launch of the next part (and alone on the GPU behind the last)
                   // (a third stream: the next part's all-reduce does not wait for this part's optimizer)
@@ -519,9 +559,13 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
           }
           if (pipeline) {
               if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString(rc));
-              if (t->ft_rows_updated) {  // the optimizer stream joins the communication stream
+              if (t->ft_rows_updated || t->px) {  // the optimizer stream (with the peer exchange: its waits) joins the communication stream
                   CU(t, cudaEventRecord(t->ev_opt_done, t->opt_stream));
                   CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_opt_done, 0));
+              }
+              if (t->px) {
+                  std::string e;
+                  if (px_join(t->px, t->comm_stream, &e) != 0) return fail(t, TB_ERR_CUDA, "%s", e.c_str());
               }
               CU(t, cudaEventRecord(t->ev_comm_done, t->comm_stream));
               t->ar_pipelined = true;
@@ -634,6 +678,23 @@ int run_optimizer(tb_trainer* t, float lr) {
     return TB_OK;
 }
 
+// Waits for a loss read-back.  With the peer exchange a lost peer shows as a stream that never finishes (its flags never
+// arrive): the wait then has a deadline, after which the handle refuses further steps.
+int wait_loss_event(tb_trainer* t, cudaEvent_t ev) {
+    if (!t->px) { CU(t, cudaEventSynchronize(ev)); return TB_OK; }
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const cudaError_t e = cudaEventQuery(ev);
+        if (e == cudaSuccess) return TB_OK;
+        if (e != cudaErrorNotReady) return fail(t, TB_ERR_CUDA, "cudaEventQuery: %s", cudaGetErrorString(e));
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(PEER_DEADLINE_S)) {
+            t->poisoned = true;
+            return fail(t, TB_ERR_TIMEOUT, "a data-parallel step did not finish within %d s: a peer rank is gone or stuck", PEER_DEADLINE_S);
+        }
+        std::this_thread::yield();
+    }
+}
+
 // queues the read-back of this step's loss and returns the previous one (AsyncLossRing::read_and_queue_next)
 int loss_ring_next(tb_trainer* t, double* out) {
     const int cur = (int)(t->loss_step % 2);
@@ -646,7 +707,7 @@ int loss_ring_next(tb_trainer* t, double* out) {
     double returned = 0.0;
     if (t->loss_primed) {
         const int prev = (int)((t->loss_step + 1) % 2);
-        CU(t, cudaEventSynchronize(t->ev_loss[prev]));
+        { const int wrc = wait_loss_event(t, t->ev_loss[prev]); if (wrc != TB_OK) return wrc; }
         returned = *t->loss_pinned[prev];
     } else {
         t->loss_primed = true;
@@ -733,6 +794,7 @@ void free_all(tb_trainer* t) {
     if (t->copy_stream) cudaStreamSynchronize(t->copy_stream);
     if (t->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(t->comm);
     for (auto& g : t->groups) { cudaFree(g.w); cudaFree(g.m); cudaFree(g.v); cudaFree(g.slow); }
+    px_destroy(t->px);
     cudaFree(t->grad_arena);
     cudaFree(t->comb);
     cudaFree(t->table_h); cudaFree(t->ft_m_h); cudaFree(t->ft_v_h); cudaFree(t->clamp_counter);
@@ -784,7 +846,16 @@ int create_impl(tb_trainer* t) {
     const tb_config& c = t->cfg;
     CU(t, cudaSetDevice(c.device));
     CU(t, cudaDeviceGetAttribute(&t->n_sm, cudaDevAttrMultiProcessorCount, c.device));
-    CU(t, cudaStreamCreateWithFlags(&t->stream, cudaStreamNonBlocking));
+    {
+        // Data parallel: the step's own kernels go before the FT row updates that run behind the exchanged gradient parts
+        // (opt_stream, lowest priority).  Both want whole SMs (the weight gradient holds all registers of its SM), so
+        // running them side by side gains nothing; deferring the row updates fills the wave tails of the gradient parts
+        // and the time the last part's exchange is in flight.
+        int lo = 0, hi = 0;
+        CU(t, cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        const int mid = c.world_size > 1 && getenv("TATARA_DP_FLAT_PRIORITY") == nullptr ? (hi < lo ? lo - 1 : lo) : lo;
+        CU(t, cudaStreamCreateWithPriority(&t->stream, cudaStreamNonBlocking, mid));
+    }
     CU(t, cudaStreamCreateWithFlags(&t->copy_stream, cudaStreamNonBlocking));
     const bool ls = c.arch == TB_ARCH_LAYERSTACK;
     const int64_t N = c.ft_in, F = c.ft_out, l1 = c.l1_out, l2 = c.l2_out, nb = c.num_buckets;
@@ -930,6 +1001,12 @@ int create_impl(tb_trainer* t) {
             rc = g_nccl.CommInitRank(&t->comm, c.world_size, id, c.rank);
         }
         if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclCommInitRank%s: %s", c.nccl_ctas > 0 ? "Config" : "", g_nccl.GetErrorString(rc));
+        if (c.dp_exchange == TB_DP_PEER_COPY) {
+            std::string e2;
+            if (px_create(&t->px, c.rank, c.world_size, t->grad_arena, (size_t)t->arena_reduce_len, AR_PARTS_MAX, t->loss_acc,
+                          nccl_host_allgather, t, &e2) != 0)
+                return fail(t, TB_ERR_CUDA, "%s", e2.c_str());
+        }
         {   // highest priority: when an SM frees up, the waiting all-reduce gets it before the next gradient block does
             int lo = 0, hi = 0;
             CU(t, cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -1154,7 +1231,7 @@ int tb_flush_pending_loss(tb_trainer* t, double* loss) {
     double returned = 0.0;
     if (t->loss_primed) {
         const int last = (int)((t->loss_step + 1) % 2);
-        CU(t, cudaEventSynchronize(t->ev_loss[last]));
+        { const int wrc = wait_loss_event(t, t->ev_loss[last]); if (wrc != TB_OK) return wrc; }
         returned = *t->loss_pinned[last];
     }
     t->loss_primed = false;

@@ -354,8 +354,11 @@ class _Trainer:
         self._check(self._lib.tb_synchronize(self._h), "tb_synchronize")
 
 
-def _dp(cfg: L.Config, world_size: int, rank: int, nccl_id: Optional[bytes], nccl_ctas: int = 0):
-    cfg.world_size, cfg.rank, cfg.nccl_ctas = world_size, rank, nccl_ctas
+DP_EXCHANGE = {"nccl": 0, "peer-copy": 1}
+
+
+def _dp(cfg: L.Config, world_size: int, rank: int, nccl_id: Optional[bytes], nccl_ctas: int = 0, dp_exchange: str = "nccl"):
+    cfg.world_size, cfg.rank, cfg.nccl_ctas, cfg.dp_exchange = world_size, rank, nccl_ctas, DP_EXCHANGE[dp_exchange]
     if world_size > 1:
         if nccl_id is None or len(nccl_id) != 128:
             raise TrainerError("data parallel needs the 128-byte NCCL id of rank 0")
@@ -369,7 +372,7 @@ class GpuTrainer(_Trainer):
                  feature_set: FeatureSetSpec, optimizer: str = "ranger",
                  optim_groups: OptimGroupConfig = OptimGroupConfig(), precision: PrecisionFlags = PrecisionFlags(),
                  init: Optional[Dict[str, np.ndarray]] = "default", device: int = 0, world_size: int = 1, rank: int = 0,
-                 nccl_id: Optional[bytes] = None, nccl_ctas: int = 0):
+                 nccl_id: Optional[bytes] = None, nccl_ctas: int = 0, dp_exchange: str = "nccl"):
         cfg = L.Config()
         cfg.device, cfg.arch, cfg.batch_capacity = device, L.ARCH_LAYERSTACK, batch_size
         cfg.ft_in, cfg.piece_inputs, cfg.ft_factorize = feature_set.ft_in, feature_set.piece_inputs, int(feature_set.ft_factorize)
@@ -377,7 +380,7 @@ class GpuTrainer(_Trainer):
         cfg.activation, cfg.optimizer, cfg.precision = 0, OPTIMIZERS[optimizer], precision.mask()
         (cfg.wd_ft, cfg.lr_mult_ft), (cfg.wd_dense, cfg.lr_mult_dense), (cfg.wd_bias, cfg.lr_mult_bias) = \
             optim_groups.ft, optim_groups.dense, optim_groups.bias
-        _dp(cfg, world_size, rank, nccl_id, nccl_ctas)
+        _dp(cfg, world_size, rank, nccl_id, nccl_ctas, dp_exchange)
         self.feature_set = feature_set
         if isinstance(init, str):
             init = layerstack_default_init(feature_set, ft_out, l1_out, l2_out, num_buckets)
@@ -390,7 +393,7 @@ class SimpleGpuTrainer(_Trainer):
     def __init__(self, batch_size: int, ft_out: int, l1_out: int, l2_out: int, feature_set: FeatureSetSpec,
                  activation: str = "crelu", optimizer: str = "ranger", weight_decay: float = 0.01,
                  precision: PrecisionFlags = PrecisionFlags(), init: Optional[Dict[str, np.ndarray]] = "default",
-                 device: int = 0, world_size: int = 1, rank: int = 0, nccl_id: Optional[bytes] = None, nccl_ctas: int = 0):
+                 device: int = 0, world_size: int = 1, rank: int = 0, nccl_id: Optional[bytes] = None, nccl_ctas: int = 0, dp_exchange: str = "nccl"):
         cfg = L.Config()
         cfg.device, cfg.arch, cfg.batch_capacity = device, L.ARCH_SIMPLE, batch_size
         cfg.ft_in, cfg.piece_inputs, cfg.ft_factorize = feature_set.ft_in, feature_set.piece_inputs, int(feature_set.ft_factorize)
@@ -399,7 +402,7 @@ class SimpleGpuTrainer(_Trainer):
         cfg.optimizer, cfg.precision = OPTIMIZERS[optimizer], precision.mask()
         cfg.wd_ft = cfg.wd_dense = cfg.wd_bias = weight_decay
         cfg.lr_mult_ft = cfg.lr_mult_dense = cfg.lr_mult_bias = 1.0
-        _dp(cfg, world_size, rank, nccl_id, nccl_ctas)
+        _dp(cfg, world_size, rank, nccl_id, nccl_ctas, dp_exchange)
         self.feature_set = feature_set
         if isinstance(init, str):
             init = simple_default_init(feature_set, ft_out, l1_out, l2_out, pairwise=activation == "pairwise")

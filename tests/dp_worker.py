@@ -3,6 +3,7 @@
 MODE cpu : the host-side logic on the CPU oracle over gloo (no GPU): shard seeds per rank, gradient sum,
            identical optimizer step, loss sum — compared with one rank stepping on the concatenated batch.
 MODE gpu : the same through the CUDA library and its NCCL all-reduce, one rank per GPU.
+MODE gpu-peer : the same with the gradient parts summed by the copy engines over peer mappings (dp_exchange "peer-copy").
 """
 import os
 import sys
@@ -75,11 +76,12 @@ def main():
             dist.broadcast(w0, src=0)
             assert torch.equal(w, w0), "replicas diverged in " + n
     else:
+        exchange = "peer-copy" if mode == "gpu-peer" else "nccl"
         ids = [tb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         # communicators with a fixed channel count (ncclCommInitRankConfig); the benchmark covers ncclCommInitRank
         tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=int(os.environ["LOCAL_RANK"]),
-                           world_size=world, rank=rank, nccl_id=ids[0], nccl_ctas=8)
+                           world_size=world, rank=rank, nccl_id=ids[0], nccl_ctas=8, dp_exchange=exchange)
         batch = tb.BatchData(mine["stm"], mine["nstm"], mine["nnz"], mine["score"], mine["wdl"], mine["bucket"])
         loss = tr.forward_backward(batch, 0.0, tb.LossKind.sigmoid())
         assert abs(loss - ref_loss) <= 1e-5 * (1 + abs(ref_loss)), (loss, ref_loss)    # the all-reduced loss
@@ -111,7 +113,7 @@ def main():
         ids = [tb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         tr = tb.GpuTrainer(B, F, L1, L2, NB, fs, optimizer="ranger", init=init, device=int(os.environ["LOCAL_RANK"]),
-                           world_size=world, rank=rank, nccl_id=ids[0], nccl_ctas=8)
+                           world_size=world, rank=rank, nccl_id=ids[0], nccl_ctas=8, dp_exchange=exchange)
         tr.forward_backward(batch, 0.0, tb.LossKind.sigmoid())
         tr.apply_optimizer(LR)
         for s in range(5):

@@ -28,8 +28,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_config_struct_matches_header_layout():
-    # 15 int32 + 6 float + 2 int32 + 128 bytes + 1 int32
-    assert C.sizeof(L.Config) == 15 * 4 + 6 * 4 + 2 * 4 + 128 + 4
+    # 15 int32 + 6 float + 2 int32 + 128 bytes + 2 int32
+    assert C.sizeof(L.Config) == 15 * 4 + 6 * 4 + 2 * 4 + 128 + 8
     assert C.sizeof(L.Loss) == 11 * 4
 
 

@@ -48,3 +48,12 @@ def test_dp_two_gpus_nccl():
         pytest.skip("needs 2 GPUs")
     r = _torchrun(2, ["gpu"])
     assert r.returncode == 0 and "DP_WORKER_OK gpu 2" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.gpu
+def test_dp_two_gpus_peer_copy():
+    # the same six steps, run-to-run and replica checks with the gradient parts summed by copy engines over peer mappings
+    if tb.load_library().tb_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _torchrun(2, ["gpu-peer"])
+    assert r.returncode == 0 and "DP_WORKER_OK gpu-peer 2" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
