@@ -55,7 +55,8 @@ FS_DIMS = {"halfkp": (81, 1548, 38), "halfka-hm-merged": (45, 1629, 40)}
 FALLBACK_HBM_GBS = 6650.0
 SMEM_BYTES_PER_CLK_PER_SM = 128.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel of each phase, from one ncu capture of
-# cfg3 at B = 65 536 on one GPU (summary: profiles/step_cfg3_launch_list.md).  Reported only for that exact case.
+# cfg3 at B = 65 536, fp32, on one GPU (its summary is the launch-list file under profiles/).  Reported only for that
+# exact case; any other batch, precision or GPU count prints null.
 NCU_TRAFFIC_BYTES = {
     ("cfg3", "ft_backward"): 1635.0e6, ("cfg3", "ft_forward"): 1750.2e6, ("cfg3", "opt_ft"): 4232.5e6,
     ("cfg3", "l1_dgrad_ftgrad"): 1583.3e6, ("cfg3", "l1_forward"): 404.8e6, ("cfg3", "l1_wgrad"): 411.2e6,
