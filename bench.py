@@ -515,9 +515,22 @@ def main():
         for k, v in NCCL_ENV.items():
             os.environ.setdefault(k, v)
         dist.init_process_group(backend="gloo", rank=rank, world_size=world)
-        ids = [tb.nccl_unique_id() if rank == 0 else None, tb.nccl_unique_id() if rank == 0 else None]
+        ids = [tb.nccl_unique_id() if rank == 0 else None for _ in range(3)]
         dist.broadcast_object_list(ids, src=0)
         nccl_id = ids[0]
+        if args.dp_exchange == "peer-copy":
+            # The peer exchange needs CUDA IPC between the ranks' processes.  Its set-up fails on every rank together when one
+            # rank cannot map a peer's memory; the benchmark then runs on NCCL all-reduces and says so in config.dp_exchange.
+            fs0 = tb.FEATURE_SETS["halfka-hm-merged"]
+            try:
+                probe = tb.GpuTrainer(256, 256, 16, 32, 9, fs0, optimizer="ranger", device=local_rank, world_size=world, rank=rank,
+                                      nccl_id=ids[2], dp_exchange="peer-copy")
+                dist.barrier()
+                probe.close()
+                dist.barrier()
+            except tb.TrainerError as e:
+                trace("peer exchange unavailable (%s): falling back to NCCL" % e)
+                args.dp_exchange = "nccl"
     device = local_rank
     B = args.batch
     dp_ok = dp_same_small = None

@@ -114,7 +114,14 @@ int px_create(PeerExchange** out, int rank, int world, float* arena, size_t redu
     PeerExchange* x = new PeerExchange;
     x->world = world; x->rank = rank; x->max_parts = max_parts; x->reduce_floats = reduce_floats; x->arena = arena; x->loss_acc = loss_acc;
     struct Guard { PeerExchange* x; bool keep = false; ~Guard() { if (!keep) px_destroy(x); } } guard{x};
-    {
+    // every rank's two IPC handles; ok = 0 tells the others that this rank could not get that far
+    struct Card { cudaIpcMemHandle_t arena, block; int ok; int pad[3]; };
+    std::vector<Card> cards(world);
+    Card mine;
+    memset(&mine, 0, sizeof mine);
+    // Both all-gathers below are reached by every rank whatever failed locally, and every rank leaves with the same
+    // verdict: a rank that gave up alone would leave the others waiting in a collective.
+    auto local_setup = [&]() -> int {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult st;
         PXC(cudaGetDriverEntryPoint("cuStreamWaitValue32", &fn, cudaEnableDefault, &st));
@@ -123,37 +130,46 @@ int px_create(PeerExchange** out, int rank, int world, float* arena, size_t redu
         PXC(cudaGetDriverEntryPoint("cuStreamWriteValue32", &fn, cudaEnableDefault, &st));
         if (st != cudaDriverEntryPointSuccess || !fn) { if (err) *err = "cuStreamWriteValue32 is not available in this driver"; return -1; }
         x->write_value = (StreamValue32Fn)fn;
-    }
-    const size_t flag_bytes = (size_t)2 * PX_MAX_RANKS * PX_MAX_PARTS * 4;
-    x->off_loss = (flag_bytes + 255) / 256 * 256;
-    x->off_recv = x->off_loss + (PX_MAX_RANKS * sizeof(double) + 255) / 256 * 256;
-    const size_t block_bytes = x->off_recv + (size_t)world * reduce_floats * 4;
-    PXC(cudaMalloc((void**)&x->block, block_bytes));
-    PXC(cudaMemset(x->block, 0, x->off_recv));  // flags (sequence 0 = nothing yet) and loss slots
-    PXC(cudaDeviceSynchronize());
-    // every rank's two IPC handles and its device ordinal
-    struct Card { cudaIpcMemHandle_t arena, block; int device; int pad[3]; };
-    std::vector<Card> cards(world);
-    Card mine;
-    memset(&mine, 0, sizeof mine);
-    PXC(cudaIpcGetMemHandle(&mine.arena, arena));
-    PXC(cudaIpcGetMemHandle(&mine.block, x->block));
-    PXC(cudaGetDevice(&mine.device));
+        const size_t flag_bytes = (size_t)2 * PX_MAX_RANKS * PX_MAX_PARTS * 4;
+        x->off_loss = (flag_bytes + 255) / 256 * 256;
+        x->off_recv = x->off_loss + (PX_MAX_RANKS * sizeof(double) + 255) / 256 * 256;
+        const size_t block_bytes = x->off_recv + (size_t)world * reduce_floats * 4;
+        PXC(cudaMalloc((void**)&x->block, block_bytes));
+        PXC(cudaMemset(x->block, 0, x->off_recv));  // flags (sequence 0 = nothing yet) and loss slots
+        PXC(cudaDeviceSynchronize());
+        PXC(cudaIpcGetMemHandle(&mine.arena, arena));
+        PXC(cudaIpcGetMemHandle(&mine.block, x->block));
+        int lo = 0, hi = 0;
+        PXC(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        PXC(cudaStreamCreateWithPriority(&x->push_stream, cudaStreamNonBlocking, hi));
+        PXC(cudaStreamCreateWithPriority(&x->publish_stream, cudaStreamNonBlocking, hi));
+        for (int p = 0; p < max_parts; ++p) PXC(cudaEventCreateWithFlags(&x->ev_reduced[p], cudaEventDisableTiming));
+        PXC(cudaEventCreateWithFlags(&x->ev_push_done, cudaEventDisableTiming));
+        PXC(cudaEventCreateWithFlags(&x->ev_publish_done, cudaEventDisableTiming));
+        return 0;
+    };
+    mine.ok = local_setup() == 0 ? 1 : 0;
     if (allgather(allgather_ctx, &mine, cards.data(), sizeof(Card)) != 0) { if (err) *err = "peer exchange: handle all-gather failed"; return -1; }
-    for (int q = 0; q < world; ++q) {
-        if (q == rank) { x->peer_arena[q] = arena; x->peer_block[q] = x->block; continue; }
-        PXC(cudaIpcOpenMemHandle((void**)&x->peer_arena[q], cards[q].arena, cudaIpcMemLazyEnablePeerAccess));
-        x->opened_arena[q] = true;
-        PXC(cudaIpcOpenMemHandle((void**)&x->peer_block[q], cards[q].block, cudaIpcMemLazyEnablePeerAccess));
-        x->opened_block[q] = true;
-    }
-    int lo = 0, hi = 0;
-    PXC(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    PXC(cudaStreamCreateWithPriority(&x->push_stream, cudaStreamNonBlocking, hi));
-    PXC(cudaStreamCreateWithPriority(&x->publish_stream, cudaStreamNonBlocking, hi));
-    for (int p = 0; p < max_parts; ++p) PXC(cudaEventCreateWithFlags(&x->ev_reduced[p], cudaEventDisableTiming));
-    PXC(cudaEventCreateWithFlags(&x->ev_push_done, cudaEventDisableTiming));
-    PXC(cudaEventCreateWithFlags(&x->ev_publish_done, cudaEventDisableTiming));
+    auto open_peers = [&]() -> int {
+        for (int q = 0; q < world; ++q)
+            if (!cards[q].ok) { if (err && q != rank) *err = "peer exchange: rank " + std::to_string(q) + " could not set up its buffers"; return -1; }
+        for (int q = 0; q < world; ++q) {
+            if (q == rank) { x->peer_arena[q] = arena; x->peer_block[q] = x->block; continue; }
+            PXC(cudaIpcOpenMemHandle((void**)&x->peer_arena[q], cards[q].arena, cudaIpcMemLazyEnablePeerAccess));
+            x->opened_arena[q] = true;
+            PXC(cudaIpcOpenMemHandle((void**)&x->peer_block[q], cards[q].block, cudaIpcMemLazyEnablePeerAccess));
+            x->opened_block[q] = true;
+        }
+        return 0;
+    };
+    struct Verdict { int ok; int pad[3]; } v{open_peers() == 0 ? 1 : 0, {0, 0, 0}};
+    std::vector<Verdict> all(world);
+    if (allgather(allgather_ctx, &v, all.data(), sizeof(Verdict)) != 0) { if (err) *err = "peer exchange: verdict all-gather failed"; return -1; }
+    for (int q = 0; q < world; ++q)
+        if (!all[q].ok) {
+            if (err && q != rank) *err = "peer exchange: rank " + std::to_string(q) + " could not map its peers' memory";
+            return -1;
+        }
     guard.keep = true;
     *out = x;
     return 0;

@@ -30,17 +30,17 @@
 #define N_SMA_THRESHOLD 5.0f
 #define FT_DFT_FP16_BASE_SCALE 16384.0f  // arch.rs:72-93: the fp16 dft rows carry gradient * 2^14 * batch
 #define DGRAD_CTAS (148 * 2)
-#define AR_PARTS_MAX 9
+#define AR_PARTS_MAX 6
 #define PEER_DEADLINE_S 120  // peer exchange: longest wait for a step before the peers are given up
 // Number of launches the FT weight gradient is cut into in data-parallel runs (each part's all-reduce and row updates
 // overlap the next part).  A part runs slices x strips blocks of one per SM: the count that wastes the fewest block
 // slots wins, a shorter last part (whose communication nothing hides) breaking near ties.  Measured on two B200s at
-// 45 slices x 48 strips: 5 parts 4.81 ms per step, 3 parts 4.97, 4 parts 4.99, 6 parts 4.95, 8 parts 5.05.
+// 45 slices x 48 strips (peer exchange, row updates at low priority): 5 parts 4.70 ms per step, 3 parts 4.78, 4 parts 4.87,
+// 6 parts 4.87, 9 parts 4.91; unequal parts with a short last one 4.67 at best.
 static int ar_parts_for(int n_slices, int strips, int n_sm) {
-    if (const char* dbg = getenv("TATARA_DBG_PARTS")) { const int v = atoi(dbg); if (v >= 2 && v <= AR_PARTS_MAX) return v; }
     int best = 1;
     double best_cost = 1e30;
-    for (int parts = 3; parts <= 6; ++parts) {
+    for (int parts = 3; parts <= AR_PARTS_MAX; ++parts) {
         if (n_slices < 2 * parts) break;
         double waves = 0, last = 0;
         for (int p = 0; p < parts; ++p) {
@@ -498,22 +498,13 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
           // first part, the loss with the last).  Whichever path wrote the rows (the gated generic kernels come first), they
           // are final when the part's event is recorded.
           const int n_slices = (N + rps - 1) / rps;
-          int parts = c.world_size > 1 ? ar_parts_for(n_slices, F / 32, t->n_sm) : 1;
-          int dbg_bounds[AR_PARTS_MAX] = {};
-          if (const char* dbg = getenv("TATARA_DBG_BOUNDS")) {
-              if (c.world_size > 1) {
-                  int np = 0; const char* q = dbg;
-                  while (*q && np < AR_PARTS_MAX) { dbg_bounds[np++] = atoi(q); while (*q && *q != ',') ++q; if (*q == ',') ++q; }
-                  if (np >= 2 && dbg_bounds[np - 1] == n_slices) parts = np; else dbg_bounds[0] = 0;
-              }
-          }
+          const int parts = c.world_size > 1 ? ar_parts_for(n_slices, F / 32, t->n_sm) : 1;
           const bool pipeline = parts > 1;
           const int64_t ft_off = t->groups[0].grad - t->grad_arena;
           int rc = 0;
           for (int part = 0; part < parts; ++part) {
               // equal parts: a smaller last part cost more than it hid
-              int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
-              if (dbg_bounds[0] > 0) { k0 = part == 0 ? 0 : dbg_bounds[part - 1]; k1 = dbg_bounds[part]; }
+              const int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
               n += launch_ft_backward_slice(t->stream, dft0, dft1, t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
                                             t->groups[0].grad, t->bwd_slabs, t->p_out16);
               if (!pipeline) continue;
@@ -535,7 +526,7 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                   const int rc2 = g_nccl.GroupEnd();
                   if (rc == 0) rc = rc2;
               }
-              if (rc == 0 && lr >= 0.0f && !getenv("TATARA_DBG_NO_ROWS_OPT")) {
+              if (rc == 0 && lr >= 0.0f) {
                   // consumer side of the pipeline: the optimizer of this part's real rows follows its all-reduce on the
                   // same stream, next to the gradient launch of the next part (and alone on the GPU behind the last)
                   // (a third stream: the next part's all-reduce does not wait for this part's optimizer)
@@ -853,7 +844,7 @@ int create_impl(tb_trainer* t) {
         // and the time the last part's exchange is in flight.
         int lo = 0, hi = 0;
         CU(t, cudaDeviceGetStreamPriorityRange(&lo, &hi));
-        const int mid = c.world_size > 1 && getenv("TATARA_DP_FLAT_PRIORITY") == nullptr ? (hi < lo ? lo - 1 : lo) : lo;
+        const int mid = c.world_size > 1 && hi < lo ? lo - 1 : lo;
         CU(t, cudaStreamCreateWithPriority(&t->stream, cudaStreamNonBlocking, mid));
     }
     CU(t, cudaStreamCreateWithFlags(&t->copy_stream, cudaStreamNonBlocking));
