@@ -466,8 +466,9 @@ def main():
     ap.add_argument("--no-microbench", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true")
     ap.add_argument("--trace", action="store_true", help="progress lines on stderr")
-    ap.add_argument("--dp-exchange", default="peer-copy", choices=["nccl", "peer-copy"],
-                    help="how the gradient parts are summed over the ranks: ncclAllReduce, or copy engines over peer mappings")
+    ap.add_argument("--dp-exchange", default="auto", choices=["auto", "nccl", "peer-copy", "peer-kernel"],
+                    help="how the gradient parts are summed over the ranks: ncclAllReduce, copy engines over peer mappings, or a "
+                         "kernel over peer mappings; auto = what measured fastest: peer-copy on two GPUs, nccl on more")
     ap.add_argument("--nccl-ctas", type=int, default=0, help="fixed CTA (channel) count of the library's communicator; 0: NCCL chooses")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -518,13 +519,16 @@ def main():
         ids = [tb.nccl_unique_id() if rank == 0 else None for _ in range(3)]
         dist.broadcast_object_list(ids, src=0)
         nccl_id = ids[0]
-        if args.dp_exchange == "peer-copy":
+        if args.dp_exchange == "auto":
+            # two B200s: peer-copy 4.69 ms per step, nccl 4.82; four: 4.98 / 5.00 / peer-kernel 5.17 (fp32, config 3)
+            args.dp_exchange = "peer-copy" if world == 2 else "nccl"
+        if args.dp_exchange != "nccl":
             # The peer exchange needs CUDA IPC between the ranks' processes.  Its set-up fails on every rank together when one
             # rank cannot map a peer's memory; the benchmark then runs on NCCL all-reduces and says so in config.dp_exchange.
             fs0 = tb.FEATURE_SETS["halfka-hm-merged"]
             try:
                 probe = tb.GpuTrainer(256, 256, 16, 32, 9, fs0, optimizer="ranger", device=local_rank, world_size=world, rank=rank,
-                                      nccl_id=ids[2], dp_exchange="peer-copy")
+                                      nccl_id=ids[2], dp_exchange=args.dp_exchange)
                 dist.barrier()
                 probe.close()
                 dist.barrier()

@@ -59,6 +59,7 @@ typedef struct tb_trainer tb_trainer;
  */
 #define TB_DP_NCCL 0
 #define TB_DP_PEER_COPY 1
+#define TB_DP_PEER_KERNEL 2
 
 typedef struct tb_config {
     int32_t struct_size;    /* sizeof(tb_config) of the caller */
@@ -88,7 +89,9 @@ typedef struct tb_config {
     int32_t dp_exchange;    /* TB_DP_NCCL (0): the gradient parts are summed by ncclAllReduce.  TB_DP_PEER_COPY (1): ranks of
                                one node, one process each: reduce-scatter and all-gather by the copy engines over peer
                                mappings (CUDA IPC) with stream memory operations as signals and a small summing kernel in
-                               rank order; NCCL then only carries the start-up handshake and batches off the fast path */
+                               rank order; NCCL then only carries the start-up handshake and batches off the fast path.
+                               TB_DP_PEER_KERNEL (2): the same signals, the data moved by one kernel per part that reads every
+                               rank's shard over the peer mappings, sums in rank order and stores the sum to every rank */
 } tb_config;
 
 /* nnue_train::trainer::LossKind, crates/nnue-train/src/trainer.rs:75-95 */

@@ -7,6 +7,9 @@
 
 #define PX_MAX_RANKS 16
 #define PX_MAX_PARTS 16
+#define PX_MODE_COPY 1      // reduce-scatter and all-gather by the copy engines, a summing kernel between them
+#define PX_MODE_KERNEL 2    // one kernel per part reads every rank's shard over the peer mappings and writes the sum back
+#define PX_KERNEL_BLOCKS 64 // blocks of 512 threads of that kernel: enough loads in flight for the link, few SMs taken
 
 struct PeerExchange;
 // all-gathers `bytes` bytes per rank between host buffers (recv holds world * bytes); 0 on success.  Collective.
@@ -14,7 +17,7 @@ typedef int (*px_allgather_fn)(void* ctx, const void* send, void* recv, size_t b
 
 // Collective over the ranks.  arena: the base of this rank's gradient arena allocation (cudaMalloc), of which the first
 // reduce_floats floats take part; loss_acc: the device double that holds this rank's loss sum.
-int px_create(PeerExchange** out, int rank, int world, float* arena, size_t reduce_floats, int max_parts, double* loss_acc,
+int px_create(PeerExchange** out, int mode, int rank, int world, float* arena, size_t reduce_floats, int max_parts, double* loss_acc,
               px_allgather_fn allgather, void* allgather_ctx, std::string* err);
 void px_destroy(PeerExchange* x);
 // a new round of exchanges (one per training step): every rank calls it the same number of times

@@ -198,6 +198,10 @@ struct tb_trainer {
     // data parallel
     void* comm = nullptr;
     PeerExchange* px = nullptr;  // TB_DP_PEER_COPY
+    // TATARA_DP_TRACE: timing events of the data-parallel pipeline of one step (diagnostics)
+    bool dp_trace = false;
+    int dp_trace_parts = 0;
+    cudaEvent_t tr_start = nullptr, tr_part[AR_PARTS_MAX] = {}, tr_red[AR_PARTS_MAX] = {}, tr_opt0[AR_PARTS_MAX] = {}, tr_opt1[AR_PARTS_MAX] = {}, tr_done = nullptr;
 };
 
 namespace {
@@ -498,17 +502,22 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
           // first part, the loss with the last).  Whichever path wrote the rows (the gated generic kernels come first), they
           // are final when the part's event is recorded.
           const int n_slices = (N + rps - 1) / rps;
-          const int parts = c.world_size > 1 ? ar_parts_for(n_slices, F / 32, t->n_sm) : 1;
+          const int strips = t->p_out16 ? F / 64 : F / 32;
+          const int parts = c.world_size > 1 ? ar_parts_for(n_slices, strips, t->n_sm) : 1;
           const bool pipeline = parts > 1;
           const int64_t ft_off = t->groups[0].grad - t->grad_arena;
           int rc = 0;
+          const bool trace = t->dp_trace && pipeline && t->step_count == 20;
+          if (trace) { t->dp_trace_parts = parts; CU(t, cudaEventRecord(t->tr_start, t->stream)); }
           for (int part = 0; part < parts; ++part) {
-              // equal parts: a smaller last part cost more than it hid
+              // equal parts: shorter last parts (tapered sizes, or whole waves with a one-wave last part) were measured slower
+              // on two and four GPUs, with NCCL and with the peer exchange
               const int k0 = (int)((int64_t)n_slices * part / parts), k1 = (int)((int64_t)n_slices * (part + 1) / parts);
               n += launch_ft_backward_slice(t->stream, dft0, dft1, t->fwd_work, t->bwd_slice, B, A, N, F, rps, 2, k0, k1 - k0,
                                             t->groups[0].grad, t->bwd_slabs, t->p_out16);
               if (!pipeline) continue;
               CU(t, cudaEventRecord(t->ev_part[part], t->stream));
+              if (trace) CU(t, cudaEventRecord(t->tr_part[part], t->stream));
               CU(t, cudaStreamWaitEvent(t->comm_stream, t->ev_part[part], 0));
               const int64_t e0 = part == 0 ? 0 : ft_off + (int64_t)(k0 * rps < N ? k0 * rps : N) * F;
               const int64_t e1 = ft_off + (int64_t)(k1 * rps < N ? k1 * rps : N) * F;
@@ -526,6 +535,7 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                   const int rc2 = g_nccl.GroupEnd();
                   if (rc == 0) rc = rc2;
               }
+              if (trace) { CU(t, cudaEventRecord(t->tr_red[part], t->comm_stream)); CU(t, cudaEventRecord(t->tr_opt0[part], t->opt_stream)); }
               if (rc == 0 && lr >= 0.0f) {
                   // consumer side of the pipeline: the optimizer of this part's real rows follows its all-reduce on the
                   // same stream, next to the gradient launch of the next part (and alone on the GPU behind the last)
@@ -546,6 +556,7 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                                         c.optimizer == TB_OPT_RANGER ? g.slow + e0r : g.slow, (int64_t)(r1 - r0) * F, sc, t->p_state16,
                                         t->p_ft16 ? (char*)t->table_h + e0r * 2 : nullptr);
                   t->ft_rows_updated = true;
+                  if (trace) CU(t, cudaEventRecord(t->tr_opt1[part], t->opt_stream));
               }
           }
           if (pipeline) {
@@ -559,6 +570,20 @@ int run_backward(tb_trainer* t, const DevBatch& d, float lr) {
                   if (px_join(t->px, t->comm_stream, &e) != 0) return fail(t, TB_ERR_CUDA, "%s", e.c_str());
               }
               CU(t, cudaEventRecord(t->ev_comm_done, t->comm_stream));
+              if (trace) {
+                  CU(t, cudaEventRecord(t->tr_done, t->comm_stream));
+                  CU(t, cudaEventSynchronize(t->tr_done));
+                  fprintf(stderr, "[dp trace rank %d] ms after the first gradient launch:", c.rank);
+                  for (int q = 0; q < parts; ++q) {
+                      float a = 0, b = 0, d0 = 0, d1 = 0;
+                      cudaEventElapsedTime(&a, t->tr_start, t->tr_part[q]); cudaEventElapsedTime(&b, t->tr_start, t->tr_red[q]);
+                      cudaEventElapsedTime(&d0, t->tr_start, t->tr_opt0[q]); cudaEventElapsedTime(&d1, t->tr_start, t->tr_opt1[q]);
+                      fprintf(stderr, "  part %d: gradient %.3f reduced %.3f published %.3f rows updated %.3f;", q, a, b, d0, d1);
+                  }
+                  float e2 = 0;
+                  cudaEventElapsedTime(&e2, t->tr_start, t->tr_done);
+                  fprintf(stderr, "  all done %.3f\n", e2);
+              }
               t->ar_pipelined = true;
           }
       }
@@ -992,9 +1017,9 @@ int create_impl(tb_trainer* t) {
             rc = g_nccl.CommInitRank(&t->comm, c.world_size, id, c.rank);
         }
         if (rc != 0) return fail(t, TB_ERR_NCCL, "ncclCommInitRank%s: %s", c.nccl_ctas > 0 ? "Config" : "", g_nccl.GetErrorString(rc));
-        if (c.dp_exchange == TB_DP_PEER_COPY) {
+        if (c.dp_exchange == TB_DP_PEER_COPY || c.dp_exchange == TB_DP_PEER_KERNEL) {
             std::string e2;
-            if (px_create(&t->px, c.rank, c.world_size, t->grad_arena, (size_t)t->arena_reduce_len, AR_PARTS_MAX, t->loss_acc,
+            if (px_create(&t->px, c.dp_exchange == TB_DP_PEER_COPY ? PX_MODE_COPY : PX_MODE_KERNEL, c.rank, c.world_size, t->grad_arena, (size_t)t->arena_reduce_len, AR_PARTS_MAX, t->loss_acc,
                           nccl_host_allgather, t, &e2) != 0)
                 return fail(t, TB_ERR_CUDA, "%s", e2.c_str());
         }
@@ -1008,6 +1033,14 @@ int create_impl(tb_trainer* t) {
         for (auto& e : t->ev_reduced) CU(t, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         CU(t, cudaEventCreateWithFlags(&t->ev_opt_done, cudaEventDisableTiming));
         CU(t, cudaEventCreateWithFlags(&t->ev_comm_done, cudaEventDisableTiming));
+        if (getenv("TATARA_DP_TRACE")) {
+            t->dp_trace = true;
+            CU(t, cudaEventCreate(&t->tr_start)); CU(t, cudaEventCreate(&t->tr_done));
+            for (int i = 0; i < AR_PARTS_MAX; ++i) {
+                CU(t, cudaEventCreate(&t->tr_part[i])); CU(t, cudaEventCreate(&t->tr_red[i]));
+                CU(t, cudaEventCreate(&t->tr_opt0[i])); CU(t, cudaEventCreate(&t->tr_opt1[i]));
+            }
+        }
     }
     CU(t, cudaDeviceSynchronize());
     return TB_OK;

@@ -354,7 +354,7 @@ class _Trainer:
         self._check(self._lib.tb_synchronize(self._h), "tb_synchronize")
 
 
-DP_EXCHANGE = {"nccl": 0, "peer-copy": 1}
+DP_EXCHANGE = {"nccl": 0, "peer-copy": 1, "peer-kernel": 2}
 
 
 def _dp(cfg: L.Config, world_size: int, rank: int, nccl_id: Optional[bytes], nccl_ctas: int = 0, dp_exchange: str = "nccl"):

@@ -20,7 +20,8 @@ import oracle_lib as O  # noqa: E402
 import tatara_b200 as tb  # noqa: E402
 from helpers import assert_close, assert_close_scaled  # noqa: E402
 
-F, L1, L2, NB, B = 256, 16, 32, 9, 256
+# DP_WORKER_F = 1536: the weight gradient is then cut into whole waves of blocks as at the benchmark size
+F, L1, L2, NB, B = int(os.environ.get("DP_WORKER_F", "256")), 16, 32, 9, 256
 LR = 1e-3
 
 
@@ -76,7 +77,7 @@ def main():
             dist.broadcast(w0, src=0)
             assert torch.equal(w, w0), "replicas diverged in " + n
     else:
-        exchange = "peer-copy" if mode == "gpu-peer" else "nccl"
+        exchange = {"gpu-peer": "peer-copy", "gpu-peer-kernel": "peer-kernel"}.get(mode, "nccl")
         ids = [tb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         # communicators with a fixed channel count (ncclCommInitRankConfig); the benchmark covers ncclCommInitRank

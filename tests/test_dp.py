@@ -19,10 +19,11 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _torchrun(n, args, timeout=900, script=WORKER):
+def _torchrun(n, args, timeout=900, script=WORKER, extra_env=None):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), script] + args
     env = dict(os.environ, OMP_NUM_THREADS="2", NCCL_NVLS_ENABLE="0")
+    env.update(extra_env or {})
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
 
 
@@ -57,3 +58,15 @@ def test_dp_two_gpus_peer_copy():
         pytest.skip("needs 2 GPUs")
     r = _torchrun(2, ["gpu-peer"])
     assert r.returncode == 0 and "DP_WORKER_OK gpu-peer 2" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+    # at the benchmark's FT width the weight gradient runs in whole waves with a one-wave last part
+    r = _torchrun(2, ["gpu-peer"], extra_env={"DP_WORKER_F": "1536", "OMP_NUM_THREADS": "8"})
+    assert r.returncode == 0 and "DP_WORKER_OK gpu-peer 2" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.gpu
+def test_dp_two_gpus_peer_kernel():
+    # the same checks with the parts summed by one kernel per part over the peer mappings
+    if tb.load_library().tb_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = _torchrun(2, ["gpu-peer-kernel"])
+    assert r.returncode == 0 and "DP_WORKER_OK gpu-peer-kernel 2" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
