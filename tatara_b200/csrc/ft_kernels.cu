@@ -6,6 +6,7 @@
 // every access below is a 128-bit vector.
 #include "common.cuh"
 #include "ft_slice.cuh"
+#include <stdlib.h>
 
 #define SORT_KEYS_MAX 128  // key limit of the small-key sorts (sort_kernels.cu)
 

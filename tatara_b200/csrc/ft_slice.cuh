@@ -2,7 +2,8 @@
 #pragma once
 #include "common.cuh"
 
-#define SLICE_IPC 2048           // items per block of the forward (a multiple of 128)
+#define SLICE_IPC 4096           // items per block of the forward (a multiple of 128): at 65 536 positions a slice of the
+                                 // benchmark (2 900 items) is one run, its strip is loaded once (2048: two runs, 0.03 ms slower)
 #define SORT_KEYS_LIMIT 128      // key limit of the small-key sorts (sort_kernels.cu): slices + 1
 #define SLICE_OUTSIDE 0xFFFFu    // row code: the feature's table row lies outside the item's slice
 #define SLICE_SLOW_BIT 0x40000000  // info[slot] bit: the item has such a row
