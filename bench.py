@@ -40,7 +40,7 @@ BATCH = 65536
 LR = 8.75e-4  # bins/nnue_train/src/cli.rs:260
 SYNTH_SEED = 0x7A7A2A
 WORKLOADS = {
-    # BASELINE.json configs[3] / [2] / [1]
+    # the headline configuration (cfg3) and the two smaller ones the same step is checked and timed on
     "cfg3": dict(arch="layerstack", fs="halfka-hm-merged", F=1536, l1=16, l2=32, nb=9, optimizer="ranger",
                  name="LayerStack ft1536 l1=16 l2=32 halfka-hm-merged kingrank9 fp32 ranger factorizer-on"),
     "cfg2": dict(arch="layerstack", fs="halfka-hm-merged", F=768, l1=8, l2=32, nb=9, optimizer="ranger",

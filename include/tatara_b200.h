@@ -45,7 +45,11 @@ enum { TB_ARCH_LAYERSTACK = 0, TB_ARCH_SIMPLE = 1 };
 enum { TB_ACT_CRELU = 0, TB_ACT_SCRELU = 1, TB_ACT_PAIRWISE = 2 };
 /* crates/nnue-train/src/optimizer.rs:32-37 OptimizerKind */
 enum { TB_OPT_RANGER = 0, TB_OPT_RADAM = 1, TB_OPT_ADAMW = 2 };
-/* bins/nnue_train/src/cli.rs:623-638 precision flags; --all-optim sets all four */
+/* bins/nnue_train/src/cli.rs:623-638 precision flags; --all-optim sets all four.  Accepted for LayerStack with l1_out of 8,
+ * 16 or 32 (TB_ERR_UNSUPPORTED otherwise).  TF32: the L1 forward product runs on the tensor cores with TF32 operands (the
+ * reference: cuBLAS TF32 tensor-op mode); FT_FP16: fp16 forward table; FT_FP16_OUT (needs FT_FP16): fp16 pre-activations and
+ * fp16 FT gradient rows scaled by 2^14 * batch and clamped to +-65504; FP16_OPT_STATE: fp16 moments of the FT table, scaled
+ * by 2^28 / 2^40 (bins/nnue_train/src/arch.rs:72-93).  Uploads and downloads stay fp32. */
 enum { TB_PREC_TF32 = 1, TB_PREC_FT_FP16 = 2, TB_PREC_FT_FP16_OUT = 4, TB_PREC_FP16_OPT_STATE = 8 };
 enum { TB_LOSS_SIGMOID = 0, TB_LOSS_WRM = 1 };
 
@@ -158,7 +162,8 @@ int tb_flush_pending_loss(tb_trainer* t, double* loss);
  * change; net_output receives n_pos values */
 int tb_validate_step(tb_trainer* t, const tb_batch* batch, float wdl_lambda, const tb_loss* loss,
                      double* sum_sq_err, float* net_output);
-/* read_fp16_clamp_count (trainer.rs:368-373) */
+/* read_fp16_clamp_count (trainer.rs:368-373): fp16 FT gradient elements that hit the clamp, and elements written, since
+ * the handle was created; both 0 without TB_PREC_FT_FP16_OUT */
 int tb_read_fp16_clamp_count(tb_trainer* t, uint64_t* clamps, uint64_t* elems);
 
 /* ---- device-resident batches -------------------------------------------------------
