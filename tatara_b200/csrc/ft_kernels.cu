@@ -598,10 +598,38 @@ __global__ void k_feat_fill(const int* __restrict__ idx_stm, const int* __restri
 
 // The ranked scatter above leaves every list in arrival order.  The two kernels below sort each list
 // ascending, so that the backward sums always run in position order (deterministic results).
-// Short lists (<= 64 entries): one warp ranks its entries against each other through shuffles.
+// Short lists (<= 32 * SORT_WARP_VALUES = 256 entries): one warp ranks its entries against each other through shuffles.
 // Long lists: queued, then one block per list marks the positions in a shared-memory bitmap and reads
 // the set bits back in order; a list that names a position twice (only possible when the caller's
 // index row repeats a feature) falls back to ranking by counting.
+#define SORT_WARP_VALUES 8  // list entries a lane holds in the warp-level sort
+// one warp sorts L[0 .. len), len <= 32 V: lane l holds entries l, l + 32, ..; every entry is ranked against all entries of
+// the list (ties by index: the bitmap kernel's fallback treats repeated positions the same way)
+template <int V>
+static __device__ __forceinline__ void warp_rank_sort(int* __restrict__ L, int len, int lane) {
+    int v[V], r[V];
+#pragma unroll
+    for (int m = 0; m < V; ++m) {
+        v[m] = lane + 32 * m < len ? L[lane + 32 * m] : 0x7fffffff;
+        r[m] = 0;
+    }
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        if (32 * k >= len) break;  // uniform over the warp
+        const int nj = min(32, len - 32 * k);
+        for (int l = 0; l < nj; ++l) {
+            const int u = __shfl_sync(0xffffffffu, v[k], l);
+            const int j = 32 * k + l;
+#pragma unroll
+            for (int m = 0; m < V; ++m) r[m] += (u < v[m]) || (u == v[m] && j < lane + 32 * m);
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int m = 0; m < V; ++m)
+        if (lane + 32 * m < len) L[r[m]] = v[m];
+}
+
 __global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict__ offsets, int N, int n_persp, int B, int A,
                                                            int* __restrict__ lists, int* __restrict__ long_queue,
                                                            int* __restrict__ long_count, const int* __restrict__ run_if) {
@@ -612,22 +640,13 @@ __global__ void __launch_bounds__(256) k_lists_sort_short(const int* __restrict_
     const int beg = offsets[(size_t)p * (N + 1) + f], end = offsets[(size_t)p * (N + 1) + f + 1];
     const int len = end - beg;
     if (len < 2) continue;
-    if (len > 64) {
+    if (len > 32 * SORT_WARP_VALUES) {
         if (lane == 0) long_queue[atomicAdd(long_count, 1)] = warp;
         continue;
     }
     int* L = lists + (size_t)p * B * A + beg;
-    const int v0 = lane < len ? L[lane] : 0x7fffffff;
-    const int v1 = lane + 32 < len ? L[lane + 32] : 0x7fffffff;
-    int r0 = 0, r1 = 0;
-    for (int j = 0; j < len; ++j) {
-        const int u = __shfl_sync(0xffffffffu, j < 32 ? v0 : v1, j & 31);
-        r0 += (u < v0) || (u == v0 && j < lane);
-        r1 += (u < v1) || (u == v1 && j < lane + 32);
-    }
-    __syncwarp();
-    if (lane < len) L[r0] = v0;
-    if (lane + 32 < len) L[r1] = v1;
+    if (len <= 64) warp_rank_sort<2>(L, len, lane);
+    else warp_rank_sort<SORT_WARP_VALUES>(L, len, lane);
     }
 }
 
